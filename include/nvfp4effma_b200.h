@@ -1,0 +1,39 @@
+/* nvfp4effma_b200.h -- entry points of this implementation that have no counterpart in the reference's C header.
+ * They never change what the reference-compatible entry points of nvfp4effma.h compute. */
+#ifndef NVFP4EFFMA_B200_H
+#define NVFP4EFFMA_B200_H
+#include "nvfp4effma.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Self-test of the hardware FP32 -> E2M1 / E4M3 conversions the quantizer uses (no counterpart in the reference, whose
+ * encoders are software; the reference proves its own exhaustively in tests/test_nvfp4effma.cu:487-495).  Adds to
+ * mismatches[0..2] (device, 3 x unsigned long long, zeroed by the caller) the number of FP32 bit patterns in
+ * [first, first + count) on which the hardware conversion differs from the software encoder: [0] E2M1 in the low
+ * nibble, [1] E2M1 in the high nibble, [2] E4M3.  NaN inputs are skipped. */
+nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long long count, unsigned long long *mismatches,
+                                         cudaStream_t stream);
+
+/* Kernel route of the GEMM entry points (no counterpart in the reference, which picks kernels from per-architecture
+ * tables): 0 = automatic (GEMV for n <= 8, tcgen05 GEMMs where the operand formats have a tensor-core form, CUDA cores
+ * otherwise), 1 = always the CUDA-core kernel, whose results are bit-identical to the reference's tiled kernels.
+ * Process-wide, not thread-safe; meant for tests and debugging.  Returns the previous value. */
+int nvfp4a_b200_set_route(int route);
+
+/* Health word of the tensor-core kernels (no counterpart in the reference, whose device-side waits are unbounded:
+ * src/tensors/mma.cuh:108-114, src/tensors/gemm_tc.cuh:555 there).  Every wait inside this library's kernels gives up
+ * after about a second; the kernel then records which wait it was (0x101 operands not delivered, 0x102 stage never
+ * released, 0x103 accumulator never completed, 0x104 accumulator never drained, 0x105 scale gather) and returns.
+ * This call SYNCHRONISES the device, copies the word to *status (0 = healthy) and clears it when reset != 0. */
+nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
+
+/* Pins the token-tile width of the W4A4 tcgen05 GEMM: 0 = by problem size, 128 (two accumulators in tensor memory, the
+ * epilogue overlaps the next tile) or 256 (one accumulator, less shared-memory traffic per flop).  Tuning / test aid, no
+ * counterpart in the reference.  Returns 0, or -1 for another value. */
+int nvfp4a_b200_set_tile_n(int bn);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,361 @@
+// NVFP4 x NVFP4 (W4A4) GEMM on the 5th-generation tensor cores: tcgen05.mma kind::mxf4nvf4 with 1 x 16 UE4M3 block scales
+// (scale_vec::4X), FP32 accumulators in tensor memory, operands fed by TMA through a multi-stage mbarrier ring, persistent
+// tile scheduling, epilogue (global scales, bias, beta * C, amax, output rounding) straight out of tensor memory.
+//
+// Tile: 128 rows of A (weight rows = MMA M) x BN rows of B (tokens = MMA N) x 256 values of k per stage.  A stage in shared
+// memory is [A nibbles 16 KiB | B nibbles BN * 128 B | A scales 2 KiB | B scales BN * 16 B]: one 128-byte row per operand
+// row (the TMA 128-byte swizzle), and the scales as 512-byte 128 x 4 tiles -- the cuBLASLt "swizzled" layout, which is what
+// tcgen05.cp.32x128b.warpx4 copies into the scale columns of tensor memory unchanged.
+//
+// Warp roles (320 threads): warp 0 lane 0 issues TMA / bulk copies; warp 1 lane 0 issues tcgen05.cp + tcgen05.mma and owns
+// the tensor memory allocation; warps 2-5 drain accumulators (one 32-lane quadrant each); warps 6-9 gather block scales
+// that are not stored as aligned 512-byte tiles (linear layout, or unaligned buffers) into the tile form, one stage each
+// in rotation.  Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
+//
+// Semantics (reference include/nvfp4effma.h:78-92): the reference's tiled kernels round once per 16-block in FP32; the
+// tensor cores accumulate the same exact block products in their own order, so results agree within the FP32
+// accumulation bound the reference applies to its own tensor-core path (tests/test_util.h:292-302 there).
+// Block scales are consumed as UNSIGNED E4M3: codes with the sign bit set are outside this kernel's contract (the
+// reference's quantizer never emits them).
+#include "operands.cuh"
+#include "sm100.cuh"
+
+namespace nvb {
+
+using namespace sm100;
+
+struct W4A4Args {
+  int m, n, k;
+  int a_image, b_image;        // operand is an image (3-D tensor map, scales inside the image)
+  const uint8_t *sa, *sb;      // plain: block scale base; image: image base
+  int sa_ld, sb_ld;            // plain: ScalePos ld
+  int sa_gather, sb_gather;    // 1: scale warps gather (linear layout / unaligned); 0: 512-byte tiles by bulk copy
+  int ktiles;                  // image: 256-k tiles per row tile
+  Epilogue e;
+  unsigned *status;
+};
+
+template <int BN, int ACC, int STAGES>
+struct W4A4Cfg {
+  static constexpr int kABytes = 128 * 128, kBBytes = BN * 128, kSfaBytes = 2048, kSfbBytes = BN * 16;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kSfCols = 16 + BN / 8;      // per scale buffer: A 4 groups x 4 columns, B 4 groups x BN / 32 columns
+  static constexpr int kSfBuffers = 2;
+  static constexpr int kAccCols = ACC * BN;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(kAccCols + kSfBuffers * kSfCols <= kTmemCols, "tensor memory budget");
+};
+
+constexpr int kThreads = 320;
+constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
+                   kStatusWaitGather = 0x105;
+
+template <int BN, int ACC, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const W4A4Args g) {
+  using Cfg = W4A4Cfg<BN, ACC, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = (uint64_t *)(smem + STAGES * Cfg::kStageBytes);
+  uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + ACC;
+  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 2 * ACC);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (g.m + 127) / 128, tiles_n = (g.n + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int nk = (g.k + 255) / 256;
+  const bool any_gather = g.sa_gather || g.sb_gather;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto give_up = [&](unsigned code) {
+    *abort_flag = 1;
+    atomicCAS(g.status, 0u, code);
+  };
+  // wait that also ends when another role has raised the abort flag
+  auto wait = [&](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+    if (*abort_flag) return false;
+    if (mbar_wait(bar, parity)) return true;
+    give_up(code);
+    return false;
+  };
+
+  if (warp == 0) {
+    // ---------------- producer: TMA for nibbles, bulk copies for tiled scales ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int tm = t % tiles_m, tn = t / tiles_m;
+        for (int ks = 0; ks < nk; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty)) goto done;
+          uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
+          uint8_t *sA = st, *sB = st + Cfg::kABytes, *sSfa = sB + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
+          const int ng = min(4, (g.k - ks * 256) / 64);  // 64-value groups of this stage inside k
+          uint32_t bytes = Cfg::kABytes + Cfg::kBBytes;
+          if (!g.sa_gather) bytes += g.a_image ? 2048 : ng * 512;
+          if (!g.sb_gather)
+            for (int h = 0; h < BN / 128; ++h)
+              if (tn * BN + h * 128 < g.n) bytes += g.b_image ? 2048 : ng * 512;
+          mbar_arrive_expect_tx(&full[s], bytes);
+          if (g.a_image) tma_load_3d(sA, &tmap_a, 0, 0, tm * g.ktiles + ks, &full[s]);
+          else tma_load_2d(sA, &tmap_a, ks * 128, tm * 128, &full[s]);
+          if (g.b_image) {
+            for (int h = 0; h < BN / 128; ++h) tma_load_3d(sB + h * 16384, &tmap_b, 0, 0, (tn * (BN / 128) + h) * g.ktiles + ks, &full[s]);
+          } else {
+            tma_load_2d(sB, &tmap_b, ks * 128, tn * BN, &full[s]);
+          }
+          if (!g.sa_gather) {
+            if (g.a_image) bulk_load(sSfa, g.sa + ((size_t)tm * g.ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
+            else bulk_load(sSfa, g.sa + ((size_t)tm * ((-g.sa_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
+          }
+          if (!g.sb_gather) {
+            for (int h = 0; h < BN / 128; ++h) {
+              const int rt = tn * (BN / 128) + h;
+              if (rt * 128 >= g.n) continue;
+              if (g.b_image) bulk_load(sSfb + h * 2048, g.sb + ((size_t)rt * g.ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
+              else bulk_load(sSfb + h * 2048, g.sb + ((size_t)rt * ((-g.sb_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_mxf4nvf4(128, BN);
+      uint32_t it = 0, tile_i = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+        const int acc = tile_i % ACC;
+        if (!wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int ks = 0; ks < nk; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!wait(&full[s], (it / STAGES) & 1, kStatusWaitFull)) goto done;
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
+          const uint32_t sA = st, sB = st + Cfg::kABytes, sSfa = sB + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;
+          const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + (it % Cfg::kSfBuffers) * Cfg::kSfCols;
+          const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
+          const int ng = min(4, (g.k - ks * 256) / 64);
+          for (int j = 0; j < ng; ++j) {
+            tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+          }
+          const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
+          for (int j = 0; j < ng; ++j)  // 64 values of k = 32 bytes further along each 128-byte row
+            mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+          tc_commit(&empty[s]);
+        }
+        tc_commit(&tmem_full[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int quad = warp & 3;
+    const Epilogue &e = g.e;
+    float amax = 0.f;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+      const int tm = t % tiles_m, tn = t / tiles_m, acc = tile_i % ACC;
+      const int i = tm * 128 + quad * 32 + lane;
+      const bool row_ok = i < g.m;
+      const float rowp = row_ok ? epi_row_part(e, i) : 0.f;
+      const float bias = (row_ok && e.bias) ? load_dense(e.bias_dtype, e.bias, i) : 0.f;
+      if (!wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull)) goto done;
+      tc_fence_after();
+      const float colp0 = (e.gb && !e.gb_stride) ? e.gb[0] : 1.f;
+      for (int c = 0; c < BN / 32; ++c) {
+        if (tn * BN + c * 32 >= g.n) break;  // whole chunk beyond n (uniform)
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int j = tn * BN + c * 32 + jj;
+            if (j < g.n) {
+              const float colp = e.gb_stride ? e.gb[j] : colp0;
+              float v = __fmul_rn(__uint_as_float(r[jj]), epi_scale(e, rowp, colp));
+              if (e.bias) v = __fadd_rn(v, bias);
+              if (e.beta != 0.f) v = __fmaf_rn(e.beta, load_dense(e.c_dtype, e.c, (size_t)j * e.ldc + i), v);
+              amax = fmaxf(amax, fabsf(v));
+              store_dense(e.d_dtype, e.d, (size_t)j * e.ldd + i, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+    if (e.amax) warp_amax_commit(e.amax, amax);
+  } else if (any_gather) {
+    // ---------------- scale gather: linear / unaligned block scales -> 512-byte tiles in shared memory ----------------
+    // Warp w of the four takes the pipeline iterations it % 4 == w, so four stages' loads are in flight together.
+    const int w = warp - 6;
+    const ScalePos pa{g.sa_ld}, pb{g.sb_ld};
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const int tm = t % tiles_m, tn = t / tiles_m;
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        if ((int)(it & 3) != w) continue;
+        const int s = it % STAGES;
+        if (!wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitGather)) goto done;
+        uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
+        uint8_t *sSfa = st + Cfg::kABytes + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
+        const int ng = min(4, (g.k - ks * 256) / 64);
+        // one 128-row tile: lane l owns rows l, l + 32, l + 64, l + 96; per 64-k group the four rows' words form 16 bytes
+        auto gather_tile = [&](const uint8_t *sc, const ScalePos &p, int row0, int rows, uint8_t *dst) {
+          uint32_t wd[4][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int r = min(row0 + 32 * q + lane, rows - 1);
+            const uint8_t *src = sc + p.row(r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wd[q][j] = j < ng ? __ldg((const uint32_t *)(src + p.col(16 * ks + 4 * j))) : 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *(uint4 *)(dst + j * 512 + lane * 16) = make_uint4(wd[0][j], wd[1][j], wd[2][j], wd[3][j]);
+        };
+        if (g.sa_gather) gather_tile(g.sa, pa, tm * 128, g.m, sSfa);
+        if (g.sb_gather)
+          for (int h = 0; h < BN / 128; ++h)
+            if (tn * BN + h * 128 < g.n) gather_tile(g.sb, pb, tn * BN + h * 128, g.n, sSfb + h * 2048);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host ------------------------------------------------------------------------------------------------------------------
+static __device__ unsigned int g_kernel_status;
+unsigned int *kernel_status_device_ptr() {
+  unsigned int *p = nullptr;
+  cudaGetSymbolAddress((void **)&p, g_kernel_status);
+  return p;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_rows,
+                     uint64_t tiles, uint64_t tile_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {row_bytes, rows, tiles ? tiles : 1};
+  cuuint64_t strides[2] = {stride, tile_stride ? tile_stride : stride * rows};
+  cuuint32_t box[3] = {128, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = tiles ? 3 : 2;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool gemm_w4a4_supports(const GemmArgs &g) {
+  return g.B.dtype == NVFP4A_NVFP4 && !g.A.ue && !g.B.q.ue && !g.x.mask && g.k >= 64 && encode_fn() != nullptr;
+}
+
+template <int BN, int ACC, int STAGES>
+static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const W4A4Args &a, cudaStream_t s) {
+  using Cfg = W4A4Cfg<BN, ACC, STAGES>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_kernel<BN, ACC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev & 63] = true;
+  }
+  const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
+  const int grid = tiles < device_sms() ? tiles : device_sms();
+  gemm_w4a4_kernel<BN, ACC, STAGES><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ta, tb, a);
+  return cudaGetLastError();
+}
+
+static int g_w4a4_bn = 0;  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
+void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
+
+cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
+  W4A4Args a;
+  memset(&a, 0, sizeof a);
+  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.e = g.e;
+  a.status = kernel_status_device_ptr();
+  a.ktiles = (g.k + kImgK - 1) / kImgK;
+  const int bn = g_w4a4_bn ? g_w4a4_bn : (g.n > 128 ? 256 : 128);
+  CUtensorMap ta, tb;
+  const Fp4Operand &A = g.A, &B = g.B.q;
+  a.a_image = A.image; a.b_image = B.image;
+  auto tiled_ok = [](const Fp4Operand &o) { return o.sld < 0 && ((uintptr_t)o.sc & 15) == 0; };
+  if (A.image) {
+    if (!make_tmap_bytes(&ta, A.data, 128, 128, 128, 128, (uint64_t)((g.m + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    a.sa = A.data; a.sa_gather = 0;
+  } else {
+    if (!make_tmap_bytes(&ta, A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)A.ld / 2, 128)) return cudaErrorInvalidValue;
+    a.sa = A.sc; a.sa_ld = A.sld; a.sa_gather = tiled_ok(A) ? 0 : 1;
+  }
+  if (B.image) {
+    if (!make_tmap_bytes(&tb, B.data, 128, 128, 128, 128, (uint64_t)((g.n + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    a.sb = B.data; a.sb_gather = 0;
+  } else {
+    if (!make_tmap_bytes(&tb, B.data, (uint64_t)g.k / 2, (uint64_t)g.n, (uint64_t)B.ld / 2, bn)) return cudaErrorInvalidValue;
+    a.sb = B.sc; a.sb_ld = B.sld; a.sb_gather = tiled_ok(B) ? 0 : 1;
+  }
+  if (bn == 256) return launch_cfg<256, 1, 4>(ta, tb, a, s);
+  return launch_cfg<128, 2, 6>(ta, tb, a, s);
+}
+
+}  // namespace nvb
+
+extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset) {
+  using namespace nvb;
+  clear_error();
+  if (!status) return fail(NVFP4A_INVALID_VALUE, "nvfp4a_b200_kernel_status: status is NULL");
+  if (nvfp4a_status st = check_device()) return st;
+  unsigned int *p = kernel_status_device_ptr();
+  cudaError_t e = cudaMemcpy(status, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && reset) e = cudaMemset(p, 0, sizeof(unsigned int));
+  return cuda_fail(e, "nvfp4a_b200_kernel_status");
+}
+
+extern "C" int nvfp4a_b200_set_tile_n(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return -1;
+  nvb::set_w4a4_tile_n(bn);
+  return 0;
+}

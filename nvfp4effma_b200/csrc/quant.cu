@@ -1,0 +1,608 @@
+// Quantization side of the C ABI: nvfp4a_quantize_ex, nvfp4a_quantize (NVFP4 and INT8 destinations), nvfp4a_dequantize,
+// nvfp4a_swizzle_scales, nvfp4a_transpose.
+//
+// All of these are HBM-bandwidth-bound byte shuffles with a little FP32 arithmetic.  The arithmetic is Transformer
+// Engine's, bit for bit, as the reference states it (include/nvfp4effma.h:118-132, src/quant_nvfp4effma.cuh:39-48 and
+// :147-169 there); the kernels are organised for B200: 16-byte loads with every thread owning one 16-value block, grid
+// sized in multiples of the SM count, and -- when the global amax has to be computed first -- the second pass walking
+// the matrix backwards so that it starts on the bytes the first pass left in the 126 MB L2.
+#include <stdio.h>
+#include <type_traits>
+#include "common.cuh"
+
+namespace nvb {
+
+#ifndef NVB_HW_CVT
+#define NVB_HW_CVT 1  // FP32 -> E2M1 / E4M3 through cvt.rn.satfinite (equal to the software encoders on all finite inputs)
+#endif
+
+// ---- element packing ---------------------------------------------------------------------------------------------------
+// 8 FP32 -> 8 E2M1 nibbles, value 0 in bits 0..3.  cvt packs its first source into the high nibble.
+__device__ __forceinline__ uint32_t e2m1_pack8(const float *v) {
+#if NVB_HW_CVT
+  uint32_t out;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(out)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return out;
+#else
+  uint32_t out = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out |= f32_to_e2m1_sw(v[e]) << (4 * e);
+  return out;
+#endif
+}
+__device__ __forceinline__ uint32_t e4m3_encode(float d) {
+#if NVB_HW_CVT
+  uint32_t out;
+  asm("{\n\t.reg .b16 h;\n\tcvt.rn.satfinite.e4m3x2.f32 h, %1, %2;\n\tcvt.u32.u16 %0, h;\n\t}" : "=r"(out) : "f"(0.f), "f"(d));
+  return out & 0xFFu;
+#else
+  return f32_to_e4m3_sw(d);
+#endif
+}
+__device__ __forceinline__ uint32_t scale_encode(float d, bool ue) { return ue ? f32_to_ue5m3_sw(d) : e4m3_encode(d); }
+
+// 16 consecutive dense values (16-byte aligned start) -> FP32
+template <int T>
+__device__ __forceinline__ void load16(const uint8_t *p, float v[16]) {
+  if (T == NVFP4A_FP32) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 f = __ldg((const float4 *)p + q);
+      v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 w = __ldg((const uint4 *)p + q);
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (T == NVFP4A_BF16) {
+          v[8 * q + 2 * i] = __uint_as_float(ws[i] << 16);
+          v[8 * q + 2 * i + 1] = __uint_as_float(ws[i] & 0xFFFF0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ws[i]));
+          v[8 * q + 2 * i] = f.x; v[8 * q + 2 * i + 1] = f.y;
+        }
+      }
+    }
+  }
+}
+template <int T> struct ElemBytes { static constexpr int value = T == NVFP4A_FP32 ? 4 : 2; };
+
+// Encode / decode factors of one global value (reference src/quant_nvfp4effma.cuh:39-48).
+struct QGlobal { float gv, s_enc, s_dec; };
+__device__ __forceinline__ QGlobal make_global(float gv, float smax, bool amax) {
+  if (amax) {
+    float s_enc = fminf(__fdiv_rn(__fmul_rn(smax, 6.f), gv), kFltMax);
+    if (gv == 0.f || s_enc == 0.f) s_enc = 1.f;
+    return {gv, s_enc, __fdiv_rn(1.f, s_enc)};
+  }
+  return {gv, fminf(__fdiv_rn(1.f, gv), kFltMax), gv};
+}
+
+// Destination as the kernels see it.
+struct QOut {
+  uint8_t *data; int ld;      // nibbles, ld values per row
+  uint8_t *sc; int sld;       // scales: > 0 linear, < 0 swizzled (ScalePos)
+  const float *g;             // global(s), NULL = 1
+  float smax;
+  int amax_mode, per_row, ue;
+};
+
+// ---- pass 1: global amax ----------------------------------------------------------------------------------------------
+// One 16-value block per thread and iteration, ascending; one atomicMax per warp.  a1 (optional) receives the same value.
+template <int T>
+__global__ void __launch_bounds__(256) amax_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, float *a0, float *a1) {
+  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+  float m = 0.f;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += stride) {
+    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
+    float v[16];
+    load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  }
+  warp_amax_commit(a0, m);
+  if (a1 && a1 != a0) warp_amax_commit(a1, m);
+}
+// per-row amax: one warp per row
+template <int T>
+__global__ void __launch_bounds__(256) amax_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, float *a0) {
+  const int lane = threadIdx.x & 31, wpb = blockDim.x / 32;
+  for (int r = blockIdx.x * wpb + threadIdx.x / 32; r < rows; r += gridDim.x * wpb) {
+    float m = 0.f;
+    for (int c = lane; c < bpr; c += 32) {
+      float v[16];
+      load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0) a0[r] = m;
+  }
+}
+
+// ---- pass 2, fast path: rowwise 1 x 16 blocks, one global per tensor, no 4over6 --------------------------------------------
+// Thread per block, consecutive threads on consecutive blocks of a row (1 KiB of BF16 per warp and load pair).  Blocks
+// are visited from the END of the matrix: after an amax pass the tail of the matrix is what L2 still holds.
+// SWZ: swizzled scale layout; a quad of lanes owns the 4 scales of one 64-value group, which are contiguous there, so
+// lane 0 of the quad stores them as one word (needs bpr % 4 == 0, else bytes).
+template <int T, bool SWZ>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
+  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+  const QGlobal G = make_global(o.g ? o.g[0] : 1.f, o.smax, o.amax_mode != 0);
+  const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f);
+  const ScalePos sp{o.sld};
+  const bool quad_store = SWZ && (bpr & 3) == 0;
+  float mx = 0.f;
+  // every lane of a warp runs the same number of iterations (shuffles below): round the trip count up per warp
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long long u = first - (threadIdx.x & 31); u < total; u += stride) {
+    const long long mine = u + (threadIdx.x & 31);
+    const bool live = mine < total;
+    const long long b = total - 1 - (live ? mine : u);
+    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
+    float v[16];
+    load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
+    float bmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
+    const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), o.ue != 0);
+    const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, o.ue != 0), G.s_dec)), kFltMax);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], inv);
+    const uint2 q = make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
+    if (live) {
+      mx = fmaxf(mx, bmax);
+      *(uint2 *)(o.data + (size_t)r * (o.ld / 2) + 8 * c) = q;
+    }
+    if (quad_store) {
+      // blocks descend with the lane: lanes 4t..4t+3 hold columns c, c-1, c-2, c-3 with c % 4 == 3 at the quad's first lane
+      // only when (total - 1 - u) % 4 == 3, which holds because total and the warp's base u are multiples of 4
+      uint32_t w = live ? code << (8 * (c & 3)) : 0u;
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+      if (live && (c & 3) == 0) *(uint32_t *)(o.sc + sp.at(r, c)) = w;
+    } else if (live) {
+      o.sc[sp.at(r, c)] = (uint8_t)code;
+    }
+  }
+  if (stat) warp_amax_commit(stat, mx);
+}
+
+// ---- pass 2, general path ----------------------------------------------------------------------------------------------
+// 16 consecutive lanes own one 16 x 16 tile of the OUTPUT matrix (lane i its row 16 t + i): rowwise or columnwise
+// (COL: output row = source column), 1 x 16 blocks or 16 x 16 tiles, 4over6, per-row globals, either scale type.
+__device__ __forceinline__ float group16_max(float v, unsigned mask) {
+#pragma unroll
+  for (int o = 8; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(mask, v, o, 16));
+  return v;
+}
+// Transformer Engine's 16-lane tree: shfl_down by 8, 4, 2, 1, the result of lane 0
+__device__ __forceinline__ float group16_tree(float v, unsigned mask) {
+#pragma unroll
+  for (int o = 8; o; o >>= 1) v = __fadd_rn(v, __shfl_down_sync(mask, v, o, 16));
+  return __shfl_sync(mask, v, 0, 16);
+}
+__device__ __forceinline__ uint2 pack16_scaled(const float *x, float inv) {
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(x[i], inv);
+  return make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
+}
+// error of one 4over6 candidate, element order; d = ((e2m1 * sf) * amax) / (6 M) - x with an IEEE division
+__device__ __forceinline__ float fos_error(const float *x, uint2 q, float sf, float amax, float denom, int fos) {
+  float err = 0.f;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const uint32_t nib = ((e < 8 ? q.x : q.y) >> (4 * (e & 7))) & 15u;
+    const float val = __fdiv_rn(__fmul_rn(__fmul_rn(e2m1_to_f32(nib), sf), amax), denom);
+    const float d = __fsub_rn(val, x[e]);
+    err = __fadd_rn(err, fos == NVFP4A_4OVER6_MSE ? __fmul_rn(d, d) : fabsf(d));
+  }
+  return err;
+}
+template <int T, bool COL>
+__global__ void __launch_bounds__(256) quant_general_kernel(const uint8_t *__restrict__ src, int lds, int rows, int cols, QOut o, int tile,
+                                                            int fos, float *stat) {
+  const int orows = COL ? cols : rows, ocols = COL ? rows : cols;
+  const int ocb = (ocols + 15) / 16, tiles = (orows + 15) / 16;
+  const long long units = (long long)tiles * ocb;
+  const int lane = threadIdx.x & 15;
+  const unsigned gmask = 0xFFFFu << (threadIdx.x & 16);
+  const ScalePos sp{o.sld};
+  const bool ue = o.ue != 0;
+  QGlobal G0 = {};
+  if (!o.per_row) G0 = make_global(o.g ? o.g[0] : 1.f, o.smax, o.amax_mode != 0);
+  const float denom = __fmul_rn(6.f, o.smax);
+  float mx = 0.f;
+  for (long long u = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / 16; u < units; u += (long long)gridDim.x * blockDim.x / 16) {
+    const int t = (int)(u / ocb), c = (int)(u - (long long)t * ocb), orow = 16 * t + lane;
+    const bool live = orow < orows;
+    float x[16];
+    if (!COL) {
+      if (live) load16<T>(src + ((size_t)orow * lds + 16 * c) * ElemBytes<T>::value, x);
+      else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) x[e] = 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int sr = 16 * c + e;
+        x[e] = live && sr < rows ? load_dense(T, src, (size_t)sr * lds + orow) : 0.f;
+      }
+    }
+    float bmax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) bmax = fmaxf(bmax, fabsf(x[e]));
+    mx = fmaxf(mx, bmax);
+    if (tile == 16) bmax = group16_max(bmax, gmask);
+    const QGlobal G = o.per_row ? make_global(o.g[live ? orow : 0], o.smax, o.amax_mode != 0) : G0;
+    uint32_t code; uint2 q;
+    if (fos == NVFP4A_4OVER6_OFF) {
+      code = scale_encode(fminf(__fmul_rn(bmax, __fmul_rn(G.s_enc, 1.f / 6.f)), kFltMax), ue);
+      q = pack16_scaled(x, fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, ue), G.s_dec)), kFltMax));
+    } else {
+      const float base = __fmul_rn(__fdiv_rn(bmax, 6.f), G.s_enc);
+      const uint32_t c4 = e4m3_encode(fminf(__fmul_rn(base, 1.5f), 448.f)), c6 = e4m3_encode(fminf(base, 448.f));
+      const float sf4 = e4m3_to_f32(c4), sf6 = e4m3_to_f32(c6);
+      const uint2 q4 = pack16_scaled(x, fminf(__fdiv_rn(1.f, __fmul_rn(sf4, G.s_dec)), kFltMax));
+      const uint2 q6 = pack16_scaled(x, fminf(__fdiv_rn(1.f, __fmul_rn(sf6, G.s_dec)), kFltMax));
+      float e4 = fos_error(x, q4, sf4, G.gv, denom, fos), e6 = fos_error(x, q6, sf6, G.gv, denom, fos);
+      if (tile == 16) { e4 = group16_tree(e4, gmask); e6 = group16_tree(e6, gmask); }
+      const bool pick4 = e4 < e6;  // ties keep map-to-6
+      code = pick4 ? c4 : c6;
+      q = pick4 ? q4 : q6;
+    }
+    if (live) {
+      *(uint2 *)(o.data + (size_t)orow * (o.ld / 2) + 8 * c) = q;
+      o.sc[sp.at(orow, c)] = (uint8_t)code;
+    }
+  }
+  if (stat) warp_amax_commit(stat, mx);
+}
+
+// ---- INT8 destination (W4A8 activations): sb = bmax / 127, q = clamp(rint(x / sb), +-127), 0 where sb == 0 -------------------
+template <int T>
+__global__ void __launch_bounds__(256) quant_int8_kernel(const uint8_t *__restrict__ src, int lds, int8_t *__restrict__ dst, int ldd,
+                                                         float *__restrict__ scales, int ld_scale, int rows, int bpr, float *stat) {
+  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+  float mx = 0.f;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += stride) {
+    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
+    float v[16];
+    load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
+    float bmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
+    mx = fmaxf(mx, bmax);
+    const float sb = __fdiv_rn(bmax, 127.f);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int q = sb > 0.f ? (int)fminf(fmaxf(rintf(__fdiv_rn(v[i], sb)), -127.f), 127.f) : 0;
+      w[i >> 2] |= (uint32_t)(uint8_t)(int8_t)q << (8 * (i & 3));
+    }
+    *(uint4 *)(dst + (size_t)r * ldd + 16 * c) = make_uint4(w[0], w[1], w[2], w[3]);
+    scales[(size_t)r * ld_scale + c] = sb;
+  }
+  if (stat) warp_amax_commit(stat, mx);
+}
+
+// ---- dequantize: (e * sb) * g, or e * ((sb * amax) * (1 / (6 M))) -------------------------------------------------------------
+template <int T>
+__global__ void __launch_bounds__(256) dequant_kernel(QOut q, uint8_t *__restrict__ dst, int ldd, int rows, int bpr, float *stat) {
+  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+  const ScalePos sp{q.sld};
+  const float finv = 1.0f / (6.f * q.smax);
+  const float g0 = q.g ? q.g[0] : (q.amax_mode ? 6.f * q.smax : 1.f);
+  float mx = 0.f;
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += stride) {
+    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
+    const uint2 w = *(const uint2 *)(q.data + (size_t)r * (q.ld / 2) + 8 * c);
+    const float sb = scale_to_f32(q.sc[sp.at(r, c)], q.ue != 0);
+    const float gv = q.per_row ? q.g[r] : g0;
+    const float fin = q.amax_mode ? __fmul_rn(__fmul_rn(sb, gv), finv) : 0.f;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float e = e2m1_to_f32(((i < 8 ? w.x : w.y) >> (4 * (i & 7))) & 15u);
+      v[i] = q.amax_mode ? __fmul_rn(e, fin) : __fmul_rn(__fmul_rn(e, sb), gv);
+      mx = fmaxf(mx, fabsf(v[i]));
+    }
+    uint8_t *p = dst + ((size_t)r * ldd + 16 * c) * ElemBytes<T>::value;
+    if (T == NVFP4A_FP32) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ((float4 *)p)[k] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+    } else {
+      uint32_t h[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (T == NVFP4A_BF16) h[k] = f32_to_bf16_bits(v[2 * k]) | (f32_to_bf16_bits(v[2 * k + 1]) << 16);
+        else { const __half2 t = __floats2half2_rn(v[2 * k], v[2 * k + 1]); h[k] = *reinterpret_cast<const uint32_t *>(&t); }
+      }
+      ((uint4 *)p)[0] = make_uint4(h[0], h[1], h[2], h[3]);
+      ((uint4 *)p)[1] = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+  }
+  if (stat) warp_amax_commit(stat, mx);
+}
+
+// ---- scale layout conversion: one thread per scale of the padded swizzled matrix ----------------------------------------------
+__global__ void swizzle_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int ld, int rows, int cols16, int sc, int to_swz) {
+  const ScalePos sp{-sc};
+  const long long n = (long long)((rows + 127) / 128 * 128) * sc;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / sc), c = (int)(i - (long long)r * sc);
+    const bool inside = r < rows && c < cols16;
+    if (to_swz) dst[sp.at(r, c)] = inside ? src[(size_t)r * ld + c] : (uint8_t)0;
+    else if (inside) dst[(size_t)r * ld + c] = src[sp.at(r, c)];
+  }
+}
+
+// ---- transpose of a 16 x 16-tiled matrix: one thread per tile ------------------------------------------------------------------
+__global__ void transpose_kernel(QOut s, QOut d, int rows, int cols) {
+  const int tr = rows / 16, tc = cols / 16;
+  const ScalePos ss{s.sld}, ds{d.sld};
+  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < (long long)tr * tc; u += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(u / tc), c = (int)(u - (long long)t * tc);
+    uint2 in[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) in[i] = *(const uint2 *)(s.data + (size_t)(16 * t + i) * (s.ld / 2) + 8 * c);
+    const uint8_t code = s.sc[ss.at(16 * t, c)];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t w[2] = {0, 0};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i >> 3] |= (((j < 8 ? in[i].x : in[i].y) >> (4 * (j & 7))) & 15u) << (4 * (i & 7));
+      *(uint2 *)(d.data + (size_t)(16 * c + j) * (d.ld / 2) + 8 * t) = make_uint2(w[0], w[1]);
+      d.sc[ds.at(16 * c + j, t)] = code;
+    }
+  }
+}
+
+// ---- host helpers ---------------------------------------------------------------------------------------------------------------
+static int grid_for(long long threads, int per_sm = 8) {
+  const long long want = (threads + 255) / 256;
+  const long long cap = (long long)device_sms() * per_sm;  // a whole number of CTAs per SM
+  return (int)(want < 1 ? 1 : want < cap ? want : cap);
+}
+template <class F> static void by_dense(int t, F f) {
+  if (t == NVFP4A_BF16) f(std::integral_constant<int, NVFP4A_BF16>());
+  else if (t == NVFP4A_FP16) f(std::integral_constant<int, NVFP4A_FP16>());
+  else f(std::integral_constant<int, NVFP4A_FP32>());
+}
+static bool is_dense(nvfp4a_dtype t) { return t == NVFP4A_BF16 || t == NVFP4A_FP16 || t == NVFP4A_FP32; }
+
+// Checks shared by quantize / dequantize: q is the NVFP4 side ([rows][qcols]), x the dense one ([rows][cols]).
+static nvfp4a_status check_convert(const char *fn, const nvfp4a_tensor *q, int ldq, const nvfp4a_tensor *x, int ldx, int rows,
+                                   int cols, int qcols = -1) {
+  if (qcols < 0) qcols = cols;
+  if (!q || !x || !q->data || !x->data) return fail(NVFP4A_INVALID_VALUE, "%s: a tensor or its data pointer is NULL", fn);
+  if (q->dtype != NVFP4A_NVFP4) return fail(NVFP4A_INVALID_VALUE, "%s: the quantized side must be NVFP4 (dtype %d)", fn, (int)q->dtype);
+  if (!is_dense(x->dtype)) return fail(NVFP4A_INVALID_VALUE, "%s: the dense side must be BF16, FP16 or FP32 (dtype %d)", fn, (int)x->dtype);
+  if (!q->block_scale) return fail(NVFP4A_INVALID_VALUE, "%s: block_scale is NULL", fn);
+  if (rows < 0 || cols < 0) return fail(NVFP4A_INVALID_VALUE, "%s: negative size (rows = %d, cols = %d)", fn, rows, cols);
+  if (cols % 16 || ldq % 16 || ldx % 16)
+    return fail(NVFP4A_INVALID_VALUE, "%s: cols (%d) and both leading dimensions (%d, %d) must be multiples of 16", fn, cols, ldq, ldx);
+  if (ldq < qcols || ldx < cols) return fail(NVFP4A_INVALID_VALUE, "%s: a leading dimension is below its row length (%d, %d)", fn, qcols, cols);
+  if (((uintptr_t)q->data & 7) || ((uintptr_t)x->data & 15))
+    return fail(NVFP4A_INVALID_VALUE, "%s: NVFP4 data must be 8-byte and dense data 16-byte aligned", fn);
+  return NVFP4A_OK;
+}
+static QOut make_qout(const nvfp4a_tensor *t, int ld, int sld) {
+  QOut o;
+  o.data = (uint8_t *)t->data; o.ld = ld; o.sc = (uint8_t *)t->block_scale; o.sld = sld; o.g = t->global_scale;
+  o.smax = scale_max_of(t);
+  o.amax_mode = (t->flags & NVFP4A_GLOBAL_AMAX) ? 1 : 0;
+  o.per_row = (t->flags & NVFP4A_GLOBAL_PER_ROW) ? 1 : 0;
+  o.ue = (t->flags & NVFP4A_SCALES_UE5M3) ? 1 : 0;
+  return o;
+}
+
+}  // namespace nvb
+
+using namespace nvb;
+
+extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, int rows, int cols, const nvfp4a_tensor *rowwise,
+                                            int ld_row, const nvfp4a_tensor *columnwise, int ld_col, const nvfp4a_quant_config *cfg,
+                                            cudaStream_t stream) {
+  clear_error();
+  const char *fn = "nvfp4a_quantize_ex";
+  nvfp4a_quant_config c = {1, NVFP4A_4OVER6_OFF, 0};
+  if (cfg) c = *cfg;
+  if (!src || !src->data) return fail(NVFP4A_INVALID_VALUE, "%s: src or src->data is NULL", fn);
+  if (!rowwise && !columnwise) return fail(NVFP4A_INVALID_VALUE, "%s: neither a rowwise nor a columnwise destination", fn);
+  if (c.tile_rows != 1 && c.tile_rows != 16) return fail(NVFP4A_INVALID_VALUE, "%s: tile_rows = %d (must be 1 or 16)", fn, c.tile_rows);
+  if (c.four_over_six < NVFP4A_4OVER6_OFF || c.four_over_six > NVFP4A_4OVER6_MSE)
+    return fail(NVFP4A_INVALID_VALUE, "%s: four_over_six = %d is not a valid mode", fn, (int)c.four_over_six);
+  const int rows16 = (rows + 15) / 16 * 16;
+  int sld[2] = {0, 0};
+  for (int col = 0; col < 2; ++col) {
+    const nvfp4a_tensor *d = col ? columnwise : rowwise;
+    if (!d) continue;
+    const char *name = col ? "columnwise" : "rowwise";
+    const int ld = col ? ld_col : ld_row, orows = col ? cols : rows, ocols = col ? rows16 : cols;
+    if (nvfp4a_status st = check_convert(fn, d, ld, src, lds, rows, cols, ocols)) return st;
+    if (nvfp4a_status st = check_scales(fn, name, d, orows, ocols, &sld[col])) return st;
+    if (col && (d->flags & NVFP4A_GLOBAL_PER_ROW))
+      return fail(NVFP4A_INVALID_VALUE, "%s: per-row globals exist for the rowwise destination only", fn);
+    if ((d->flags & NVFP4A_GLOBAL_PER_ROW) && c.tile_rows != 1)
+      return fail(NVFP4A_INVALID_VALUE, "%s: per-row globals need 1 x 16 blocks", fn);
+    if (c.four_over_six && (!(d->flags & NVFP4A_GLOBAL_AMAX) || (d->flags & NVFP4A_SCALES_UE5M3)))
+      return fail(NVFP4A_INVALID_VALUE, "%s: 4over6 needs an amax global and E4M3 scales (%s)", fn, name);
+    if (c.compute_amax && (!(d->flags & NVFP4A_GLOBAL_AMAX) || !d->global_scale))
+      return fail(NVFP4A_INVALID_VALUE, "%s: compute_amax needs NVFP4A_GLOBAL_AMAX and global_scale storage (%s)", fn, name);
+  }
+  if (cols % 16) return fail(NVFP4A_INVALID_VALUE, "%s: cols = %d is not a multiple of 16", fn, cols);
+  if ((long long)rows * cols == 0) return NVFP4A_OK;
+  if (nvfp4a_status st = check_device()) return st;
+
+  const uint8_t *s = (const uint8_t *)src->data;
+  const int bpr = cols / 16;
+  const long long blocks = (long long)rows * bpr;
+  if (c.compute_amax) {
+    float *ar = rowwise ? (float *)rowwise->global_scale : nullptr, *ac = columnwise ? (float *)columnwise->global_scale : nullptr;
+    const bool row_per_row = rowwise && (rowwise->flags & NVFP4A_GLOBAL_PER_ROW);
+    by_dense(src->dtype, [&](auto tc) {
+      constexpr int T = decltype(tc)::value;
+      if (row_per_row) {
+        amax_rows_kernel<T><<<grid_for((long long)rows * 32), 256, 0, stream>>>(s, lds, rows, bpr, ar);
+        ar = nullptr;
+      }
+      if (ar || ac) {
+        float *p0 = ar ? ar : ac, *p1 = ar ? ac : nullptr;
+        cudaMemsetAsync(p0, 0, 4, stream);
+        if (p1 && p1 != p0) cudaMemsetAsync(p1, 0, 4, stream);
+        amax_kernel<T><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, p0, p1);
+      }
+    });
+  }
+  for (int col = 0; col < 2; ++col) {
+    const nvfp4a_tensor *d = col ? columnwise : rowwise;
+    if (!d) continue;
+    const QOut o = make_qout(d, col ? ld_col : ld_row, sld[col]);
+    const bool fast = !col && c.tile_rows == 1 && c.four_over_six == NVFP4A_4OVER6_OFF && !o.per_row;
+    by_dense(src->dtype, [&](auto tc) {
+      constexpr int T = decltype(tc)::value;
+      if (fast) {
+        if (o.sld < 0) quant_rows_kernel<T, true><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
+        else quant_rows_kernel<T, false><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
+      } else {
+        const int orows = col ? cols : rows, ocols = col ? rows : cols;
+        const long long units = (long long)((orows + 15) / 16) * ((ocols + 15) / 16);
+        if (col) quant_general_kernel<T, true><<<grid_for(units * 16), 256, 0, stream>>>(s, lds, rows, cols, o, c.tile_rows, (int)c.four_over_six, d->amax);
+        else quant_general_kernel<T, false><<<grid_for(units * 16), 256, 0, stream>>>(s, lds, rows, cols, o, c.tile_rows, (int)c.four_over_six, d->amax);
+      }
+    });
+  }
+  return cuda_fail(cudaGetLastError(), "nvfp4a_quantize_ex: kernel launch");
+}
+
+extern "C" nvfp4a_status nvfp4a_quantize(const nvfp4a_tensor *src, int lds, const nvfp4a_tensor *dst, int ldd, int rows, int cols,
+                                         cudaStream_t stream) {
+  clear_error();
+  const char *fn = "nvfp4a_quantize";
+  if (dst && dst->dtype == NVFP4A_INT8) {
+    nvfp4a_tensor q = *dst;
+    q.dtype = NVFP4A_NVFP4;  // the shared checks, then the INT8 specifics
+    if (nvfp4a_status st = check_convert(fn, &q, ldd, src, lds, rows, cols)) return st;
+    if (dst->flags) return fail(NVFP4A_INVALID_VALUE, "%s: flags apply to NVFP4 destinations only", fn);
+    if (dst->ld_scale && dst->ld_scale < cols / 16)
+      return fail(NVFP4A_INVALID_VALUE, "%s: ld_scale = %d is below cols / 16 = %d", fn, dst->ld_scale, cols / 16);
+    if (((uintptr_t)dst->data & 15) || ((uintptr_t)dst->block_scale & 3))
+      return fail(NVFP4A_INVALID_VALUE, "%s: INT8 data must be 16-byte and its FP32 scales 4-byte aligned", fn);
+    if ((long long)rows * cols == 0) return NVFP4A_OK;
+    if (nvfp4a_status st = check_device()) return st;
+    const int bpr = cols / 16, lsc = dst->ld_scale ? dst->ld_scale : bpr;
+    by_dense(src->dtype, [&](auto tc) {
+      quant_int8_kernel<decltype(tc)::value><<<grid_for((long long)rows * bpr), 256, 0, stream>>>(
+          (const uint8_t *)src->data, lds, (int8_t *)dst->data, ldd, (float *)dst->block_scale, lsc, rows, bpr, dst->amax);
+    });
+    return cuda_fail(cudaGetLastError(), "nvfp4a_quantize: kernel launch");
+  }
+  const nvfp4a_status st = nvfp4a_quantize_ex(src, lds, rows, cols, dst, ldd, nullptr, 0, nullptr, stream);
+  if (st != NVFP4A_OK) {  // report under this entry's name
+    char msg[512];
+    snprintf(msg, sizeof msg, "%s", nvfp4a_last_error());
+    const char *tag = "nvfp4a_quantize_ex";
+    if (strncmp(msg, tag, strlen(tag)) == 0) fail(st, "nvfp4a_quantize%s", msg + strlen(tag));
+  }
+  return st;
+}
+
+extern "C" nvfp4a_status nvfp4a_dequantize(const nvfp4a_tensor *src, int lds, const nvfp4a_tensor *dst, int ldd, int rows, int cols,
+                                           cudaStream_t stream) {
+  clear_error();
+  const char *fn = "nvfp4a_dequantize";
+  if (nvfp4a_status st = check_convert(fn, src, lds, dst, ldd, rows, cols)) return st;
+  int sld = 0;
+  if (nvfp4a_status st = check_scales(fn, "src", src, rows, cols, &sld)) return st;
+  if (dst->flags) return fail(NVFP4A_INVALID_VALUE, "%s: flags apply to NVFP4 tensors only (dst)", fn);
+  if ((long long)rows * cols == 0) return NVFP4A_OK;
+  if (nvfp4a_status st = check_device()) return st;
+  const QOut q = make_qout(src, lds, sld);
+  const int bpr = cols / 16;
+  by_dense(dst->dtype, [&](auto tc) {
+    dequant_kernel<decltype(tc)::value><<<grid_for((long long)rows * bpr), 256, 0, stream>>>(q, (uint8_t *)dst->data, ldd, rows, bpr, dst->amax);
+  });
+  return cuda_fail(cudaGetLastError(), "nvfp4a_dequantize: kernel launch");
+}
+
+extern "C" nvfp4a_status nvfp4a_swizzle_scales(const void *src, void *dst, int ld_linear, int rows, int cols, int to_swizzled,
+                                               cudaStream_t stream) {
+  clear_error();
+  const char *fn = "nvfp4a_swizzle_scales";
+  if (!src || !dst) return fail(NVFP4A_INVALID_VALUE, "%s: src or dst is NULL", fn);
+  if (rows < 0 || cols < 0 || cols % 16) return fail(NVFP4A_INVALID_VALUE, "%s: rows = %d, cols = %d (cols must be a multiple of 16)", fn, rows, cols);
+  if (ld_linear < cols / 16) return fail(NVFP4A_INVALID_VALUE, "%s: ld_linear = %d is below cols / 16 = %d", fn, ld_linear, cols / 16);
+  if ((long long)rows * cols == 0) return NVFP4A_OK;
+  if (nvfp4a_status st = check_device()) return st;
+  const int sc = (cols / 16 + 3) / 4 * 4;
+  swizzle_kernel<<<grid_for((long long)((rows + 127) / 128 * 128) * sc), 256, 0, stream>>>((const uint8_t *)src, (uint8_t *)dst, ld_linear,
+                                                                                          rows, cols / 16, sc, to_swizzled != 0);
+  return cuda_fail(cudaGetLastError(), "nvfp4a_swizzle_scales: kernel launch");
+}
+
+extern "C" nvfp4a_status nvfp4a_transpose(const nvfp4a_tensor *src, int lds, const nvfp4a_tensor *dst, int ldd, int rows, int cols,
+                                          cudaStream_t stream) {
+  clear_error();
+  const char *fn = "nvfp4a_transpose";
+  if (!src || !dst || !src->data || !dst->data || !src->block_scale || !dst->block_scale)
+    return fail(NVFP4A_INVALID_VALUE, "%s: a tensor, its data or its block scales are NULL", fn);
+  if (src->dtype != NVFP4A_NVFP4 || dst->dtype != NVFP4A_NVFP4) return fail(NVFP4A_INVALID_VALUE, "%s: both tensors must be NVFP4", fn);
+  if (rows < 0 || cols < 0 || rows % 16 || cols % 16)
+    return fail(NVFP4A_INVALID_VALUE, "%s: rows = %d and cols = %d must be multiples of 16", fn, rows, cols);
+  if (lds % 16 || ldd % 16 || lds < cols || ldd < rows)
+    return fail(NVFP4A_INVALID_VALUE, "%s: lds = %d (>= cols) and ldd = %d (>= rows) must be multiples of 16", fn, lds, ldd);
+  if (((uintptr_t)src->data & 7) || ((uintptr_t)dst->data & 7)) return fail(NVFP4A_INVALID_VALUE, "%s: data must be 8-byte aligned", fn);
+  if ((src->flags ^ dst->flags) & NVFP4A_SCALES_UE5M3) return fail(NVFP4A_INVALID_VALUE, "%s: src and dst use different scale types", fn);
+  int sls = 0, sld = 0;
+  if (nvfp4a_status st = check_scales(fn, "src", src, rows, cols, &sls)) return st;
+  if (nvfp4a_status st = check_scales(fn, "dst", dst, cols, rows, &sld)) return st;
+  if ((src->flags | dst->flags) & NVFP4A_GLOBAL_PER_ROW) return fail(NVFP4A_INVALID_VALUE, "%s: per-row globals cannot be transposed", fn);
+  if ((long long)rows * cols == 0) return NVFP4A_OK;
+  if (nvfp4a_status st = check_device()) return st;
+  transpose_kernel<<<grid_for((long long)(rows / 16) * (cols / 16)), 256, 0, stream>>>(make_qout(src, lds, sls), make_qout(dst, ldd, sld), rows, cols);
+  return cuda_fail(cudaGetLastError(), "nvfp4a_transpose: kernel launch");
+}
+
+// ---- self-test of the hardware conversions -------------------------------------------------------------------------------------
+// Counts, over FP32 bit patterns [first, first + count), the inputs on which cvt.rn.satfinite.{e2m1x2,e4m3x2}.f32 and the
+// software encoders disagree (NaN inputs excluded: outside the quantizer's contract).  out[0]: E2M1 as the low nibble,
+// out[1]: E2M1 as the high nibble, out[2]: E4M3.
+__global__ void codec_selftest_kernel(unsigned long long first, unsigned long long count, unsigned long long *out) {
+  unsigned long long bad0 = 0, bad1 = 0, bad2 = 0;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+       i += (unsigned long long)gridDim.x * blockDim.x) {
+    const uint32_t u = (uint32_t)(first + i);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) continue;
+    const float x = __uint_as_float(u);
+    float v[8] = {x, 1.0f, -3.0f, x, 0.f, 0.f, 0.f, 0.f};
+    const uint32_t p = nvb::e2m1_pack8(v), want = nvb::f32_to_e2m1_sw(x);
+    bad0 += (p & 15u) != want || ((p >> 4) & 15u) != 2u;
+    bad1 += ((p >> 12) & 15u) != want || ((p >> 8) & 15u) != 13u;
+    bad2 += nvb::e4m3_encode(x) != nvb::f32_to_e4m3_sw(x);
+  }
+  if (bad0) atomicAdd(out, bad0);
+  if (bad1) atomicAdd(out + 1, bad1);
+  if (bad2) atomicAdd(out + 2, bad2);
+}
+extern "C" nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long long count, unsigned long long *mismatches,
+                                                    cudaStream_t stream) {
+  clear_error();
+  if (!mismatches) return fail(NVFP4A_INVALID_VALUE, "nvfp4a_b200_codec_selftest: mismatches is NULL");
+  if (nvfp4a_status st = check_device()) return st;
+  codec_selftest_kernel<<<device_sms() * 8, 256, 0, stream>>>(first, count, mismatches);
+  return cuda_fail(cudaGetLastError(), "nvfp4a_b200_codec_selftest: kernel launch");
+}

@@ -146,7 +146,7 @@ class Fp4:
         self.data = np.full(max(rows, 1) * self.ld // 2, fill, dtype=np.uint8)
         self.scales = np.full(max(scale_bytes(self.swz, self.ld_scale, rows, cols), 1), fill, dtype=np.uint8)
         n = rows if flags & PER_ROW else 1
-        self.glob = None if glob is None else np.ascontiguousarray(np.broadcast_to(np.asarray(glob, np.float32), (max(n, 1),)))
+        self.glob = None if glob is None else np.array(np.broadcast_to(np.asarray(glob, np.float32), (max(n, 1),)), dtype=np.float32, copy=True)
 
     def tensor(self):
         return Tensor(_p(self.data), NVFP4, _p(self.scales), self.ld_scale, _p(self.glob), self.flags, self.scale_max)

@@ -1,0 +1,97 @@
+"""The C-ABI library loads and exports every symbol the headers declare; the host-side validation rejects bad arguments
+before touching a device (none of these calls reaches a kernel launch).  No GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from nvfp4effma_b200 import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return set(re.findall(r"\b(nvfp4a_[a-z0-9_]+)\s*\(", text))
+
+
+def test_every_declared_symbol_is_exported():
+    names = _declared("nvfp4effma.h") | _declared("nvfp4effma_b200.h")
+    assert len(names) >= 21
+    for n in sorted(names):
+        assert hasattr(L.lib, n), f"{n} is declared but not exported"
+        assert n in L.EXPORTS, f"{n} has no ctypes prototype"
+
+
+def test_struct_layouts_match_the_reference_abi():
+    # field order / offsets of nvfp4a_tensor on LP64 (reference include/nvfp4effma.h:46-57)
+    T = L.Tensor
+    assert [f[0] for f in T._fields_] == ["data", "dtype", "block_scale", "ld_scale", "global_scale", "amax", "flags", "scale_max"]
+    assert (T.data.offset, T.dtype.offset, T.block_scale.offset, T.ld_scale.offset, T.global_scale.offset, T.amax.offset,
+            T.flags.offset, T.scale_max.offset) == (0, 8, 16, 24, 32, 40, 48, 52)
+    assert ctypes.sizeof(T) == 56
+    assert ctypes.sizeof(L.QuantConfig) == 12
+    E = L.Epilogue
+    assert (E.norm_parts.offset, E.swiglu.offset, E.d2.offset, E.w2.offset, E.sq.offset, E.ld_sq.offset) == (0, 24, 32, 48, 64, 72)
+
+
+def test_status_strings_and_error_text():
+    assert L.lib.nvfp4a_status_string(0) == b"NVFP4A_OK"
+    assert L.lib.nvfp4a_status_string(2) == b"NVFP4A_NOT_SUPPORTED"
+    st = L.lib.nvfp4a_swizzle_scales(None, None, 4, 16, 64, 1, None)
+    assert st == L.INVALID_VALUE and b"NULL" in L.lib.nvfp4a_last_error()
+    # a successful call clears the text: rows == 0 is a no-op that needs no device
+    buf = (ctypes.c_uint8 * 16)()
+    assert L.lib.nvfp4a_swizzle_scales(buf, buf, 4, 0, 64, 1, None) == L.OK
+    assert L.lib.nvfp4a_last_error() == b""
+
+
+def _fake(dtype, flags=0, scale_max=0, ld_scale=0, with_scales=True, addr=0x1000):
+    return L.Tensor(addr, dtype, addr + 0x100000 if with_scales else None, ld_scale, None, None, flags, scale_max)
+
+
+def test_gemm_argument_checks():
+    A, B, D = _fake(L.NVFP4), _fake(L.BF16, with_scales=False), _fake(L.BF16, with_scales=False)
+    call = lambda *a: L.lib.nvfp4a_gemm(*a)
+    assert call(16, 4, 100, 1.0, A, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE  # k % 64
+    assert call(16, 4, 128, 1.0, A, 96, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE   # lda % 64
+    assert call(16, 4, 128, 1.0, A, 128, B, 128, 0.0, None, 0, D, 8, None, None) == L.INVALID_VALUE   # ldd < m
+    assert call(-1, 4, 128, 1.0, A, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
+    assert call(0, 4, 128, 1.0, A, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.OK              # empty: no-op
+    notfp4 = _fake(L.BF16, with_scales=False)
+    assert call(16, 4, 128, 1.0, notfp4, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.NOT_SUPPORTED
+    bad = _fake(L.NVFP4, scale_max=100)
+    assert call(16, 4, 128, 1.0, bad, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
+    assert b"scale_max" in L.lib.nvfp4a_last_error()
+    mis = _fake(L.NVFP4, addr=0x1008)
+    assert call(16, 4, 128, 1.0, mis, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
+    swz = _fake(L.NVFP4, flags=L.SCALES_SWIZZLED, ld_scale=12)
+    assert call(16, 4, 128, 1.0, swz, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
+    assert L.lib.nvfp4a_gemm_grouped(1, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, None, None) == L.NOT_SUPPORTED
+
+
+def test_quantize_and_epilogue_argument_checks():
+    src, dst = _fake(L.BF16, with_scales=False), _fake(L.NVFP4)
+    q = lambda *a: L.lib.nvfp4a_quantize_ex(*a)
+    assert q(src, 64, 4, 60, dst, 64, None, 0, None, None) == L.INVALID_VALUE       # cols % 16
+    cfg = L.QuantConfig(8, 0, 0)
+    assert q(src, 64, 4, 64, dst, 64, None, 0, ctypes.byref(cfg), None) == L.INVALID_VALUE  # tile_rows
+    cfg = L.QuantConfig(1, 1, 0)
+    assert q(src, 64, 4, 64, dst, 64, None, 0, ctypes.byref(cfg), None) == L.INVALID_VALUE  # 4over6 without amax global
+    cfg = L.QuantConfig(1, 0, 1)
+    assert q(src, 64, 4, 64, dst, 64, None, 0, ctypes.byref(cfg), None) == L.INVALID_VALUE  # compute_amax without storage
+    assert q(src, 64, 4, 64, None, 64, None, 0, None, None) == L.INVALID_VALUE
+    assert q(src, 64, 0, 64, dst, 64, None, 0, None, None) == L.OK
+    A, B, D = _fake(L.NVFP4), _fake(L.BF16, with_scales=False), _fake(L.BF16, with_scales=False)
+    ex = L.Epilogue()
+    ex.swiglu = 1
+    st = L.lib.nvfp4a_gemm_ex(24, 4, 128, 1.0, A, 128, B, 128, 0.0, None, 0, D, 24, None, ctypes.byref(ex), None)
+    assert st == L.INVALID_VALUE and b"swiglu" in L.lib.nvfp4a_last_error()
+    assert L.lib.nvfp4a_tc_image_bytes(L.TC_A16, L.NVFP4, 4096, 4096) == 32 * 16 * 18432
+    assert L.lib.nvfp4a_tc_image_bytes(L.TC_A8, L.NVFP4, 129, 320) == 2 * 2 * 18432
+    assert L.lib.nvfp4a_tc_image_bytes(L.TC_A16, L.BF16, 128, 256) == 0
+    assert L.check(L.OK) is None
+    with pytest.raises(ValueError):
+        L.check(L.lib.nvfp4a_swizzle_scales(None, None, 4, 16, 64, 1, None))
