@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|gemv|quant]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+Prints ONE JSON line.  Headline metric: W4A4 GEMM M = N = K = 4096 (NVFP4 x NVFP4 -> BF16) in TFLOP/s; a "step" is one
+``nvfp4a_gemm`` call on operands already resident in HBM.  Successive steps rotate over buffer sets larger than L2 in
+total.  ``extra`` carries the two bandwidth-bound workloads of the same metric (GEMV 8192^2 batch 1, quantization 8192^2)
+with their own roofline objects.  ``e2e`` is the same GEMM through the C ABI with HOST operands: pinned host -> device
+copies of the quantized operands and the device -> host read of D are inside the timed region.  At N > 1 every rank runs
+the same workload on its own GPU (independent GEMMs, no collective on the data path: weak scaling); the time is the
+maximum over ranks and ``value`` the sum of all ranks' work divided by it.
+
+``--impl reference`` times the reference's CPU implementation of the path: its host block-sum emulation, restated in
+``oracle/`` (the reference ships no CPU library), on all host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 4096
+GEMV_M = GEMV_K = 8192
+QUANT_R = QUANT_C = 8192
+NOMINAL_FP4_TFLOPS = 9000.0
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_traffic():
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    return json.load(open(p)) if os.path.exists(p) else {}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) >= 6:
+                self.rows.append(f)
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        mx = max([int(r[1]) for r in self.rows if r[1].isdigit()] or [0])
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None, "reasons": reasons, "samples": len(mhz)}
+
+
+# ---- the reference arm: CPU block-sum emulation -----------------------------------------------------------------------------
+def cpu_gemm_sample(cols, threads):
+    """One bounded sample of the W4A4 4096^3 GEMM on the host: `cols` output columns x all 4096 rows, k = 4096, through the
+    oracle (the reference's host emulation restated).  Returns seconds."""
+    import numpy as np
+    import oracle as O
+    rng = np.random.default_rng(2)
+    A = O.Fp4(M, K, glob=np.array([0.01], np.float32))
+    B = O.Fp4(cols, K, glob=np.array([0.01], np.float32))
+    for t in (A, B):
+        t.data[:] = rng.integers(0, 256, t.data.size, dtype=np.uint8)
+        t.scales[:] = rng.integers(0x20, 0x50, t.scales.size).astype(np.uint8)
+    t0 = time.perf_counter()
+    O.gemm(M, cols, K, A, B, D_dtype=O.BF16, nthreads=threads)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    cols = 32
+    for _ in range(min(args.warmup, 1)):
+        cpu_gemm_sample(cols, threads)
+    ts = [cpu_gemm_sample(cols, threads) for _ in range(args.steps)]
+    t = sum(ts) / len(ts)
+    tflops = 2.0 * M * cols * K / t / 1e12
+    sample = f"{cols} of {N} output columns x {M} rows x k {K} per step (exact block sums), scaled linearly"
+    line = {"impl": "reference", "metric": "w4a4_gemm_4096_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3 * (N / cols), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp4 x fp4 -> int32 block sums, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "w4a4_gemm_m4096_n4096_k4096", "l2": "n/a (host)"},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---- our arm ------------------------------------------------------------------------------------------------------------------
+def time_steps(fn, steps, warmup, stream, dist, world):
+    """W untimed + K timed calls of fn(i); device time by CUDA events on `stream`; returns the max over ranks in ms."""
+    import torch
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    return ms
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from nvfp4effma_b200 import _lib as L
+    from nvfp4effma_b200 import workloads as W
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.current_stream()
+    peaks = load_peaks()
+    traffic = load_traffic()
+
+    # ---- GEMM W4A4 4096^3: rotating sets (inputs 18.9 MB + D 33.6 MB each; 3 sets > 126 MB of L2) ----
+    nsets = 3
+    sets = []
+    for s in range(nsets):
+        A = W.quantize_decode_factor(W.randn_bf16(M, K, 1.0, 200 + 2 * s + 1000 * rank, dev))
+        B = W.quantize_decode_factor(W.randn_bf16(N, K, 1.0, 201 + 2 * s + 1000 * rank, dev))
+        D = torch.empty(N * M, dtype=torch.bfloat16, device=dev)
+        sets.append((A, B, D, A.tensor(), B.tensor()))
+    torch.cuda.synchronize()
+
+    def gemm_step(i):
+        A, B, D, tA, tB = sets[i % nsets]
+        W.gemm(M, N, K, tA, tB, D)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(gemm_step, args.steps, args.warmup, stream, dist, world)
+    clocks = sampler.stop() if rank == 0 else None
+    status = W.kernel_status()
+    if status:
+        raise RuntimeError(f"a tensor-core kernel gave up a wait (status 0x{status:x})")
+    ms_step = ms / args.steps
+    tflops = 2.0 * M * N * K * world / (ms_step * 1e-3) / 1e12
+    peak_fp4 = 4.0 * peaks["bf16_tflops"]
+    per_gpu = tflops / world
+    roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak_fp4, "unit": "TFLOP/s", "frac": per_gpu / peak_fp4,
+                "traffic": traffic.get("w4a4_gemm_4096_dram_bytes"),
+                "peak_note": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']:.0f} TF/s): no fp4 figure is measured; "
+                             f"of nominal 9000 TF/s: {per_gpu / NOMINAL_FP4_TFLOPS:.3f}"}
+
+    # ---- e2e: host operands, copies inside the timed region ----
+    A, B, D, tA, tB = sets[0]
+    hA = [t.cpu().pin_memory() for t in (A.data, A.scales, A.glob)]
+    hB = [t.cpu().pin_memory() for t in (B.data, B.scales, B.glob)]
+    hD = torch.empty(N * M, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in hA + hB)
+    d2h = hD.numel() * 2
+
+    def e2e_step(i):
+        for h, d in zip(hA, (A.data, A.scales, A.glob)):
+            d.copy_(h, non_blocking=True)
+        for h, d in zip(hB, (B.data, B.scales, B.glob)):
+            d.copy_(h, non_blocking=True)
+        W.gemm(M, N, K, tA, tB, D)
+        hD.copy_(D, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = time_steps(e2e_step, e2e_steps, 3, stream, dist, world) / e2e_steps
+    e2e = {"value": 2.0 * M * N * K * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": ms_e2e}
+
+    extra = {}
+    launches = args.steps
+    if rank == 0 or True:
+        # ---- GEMV 8192^2 batch 1 (W4A16): 8 distinct weights = 302 MB > L2 ----
+        nw = 8
+        ws = [W.quantize_decode_factor(W.randn_bf16(GEMV_M, GEMV_K, 0.02, 300 + s + 1000 * rank, dev)) for s in range(nw)]
+        x = W.randn_bf16(1, GEMV_K, 1.0, 400 + rank, dev)
+        y = torch.empty(GEMV_M, dtype=torch.bfloat16, device=dev)
+        tws, tx, ty = [w.tensor() for w in ws], W.tensor(x, L.BF16), W.tensor(y, L.BF16)
+
+        def gemv_step(i):
+            L.check(L.lib.nvfp4a_gemm(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(tws[i % nw]), GEMV_K, ctypes.byref(tx), GEMV_K, 0.0, None, 0,
+                                      ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
+
+        gsteps = max(args.steps, 40)
+        ms_gemv = time_steps(gemv_step, gsteps, 8, stream, dist, world) / gsteps
+        gbytes = GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16
+        gbs = gbytes / (ms_gemv * 1e-3) / 1e9
+        extra["gemv_8192_b1"] = {"metric": "gemv_w4a16_8192x8192_b1_gbs", "value": gbs * world, "unit": "GB/s", "us_per_call": ms_gemv * 1e3,
+                                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                              "frac": gbs / peaks["hbm_gbs"], "traffic": traffic.get("gemv_8192_dram_bytes")},
+                                 "config": {"workload": "gemv_w4a16_m8192_k8192_n1", "l2": "8 rotating weights (302 MB) > L2"}}
+        del ws, tws
+        # ---- quantization 8192^2 BF16 -> NVFP4, swizzled scales, amax computed: 3 inputs = 403 MB > L2 ----
+        nx = 3
+        xs = [W.outlier_input(QUANT_R, QUANT_C, 500 + s + 1000 * rank, dev) for s in range(nx)]
+        out = W.QuantizedMatrix(QUANT_R, QUANT_C, True, dev)
+
+        def quant_step(i):
+            W.quantize_amax_swizzled(xs[i % nx], out)
+
+        qsteps = max(args.steps, 20)
+        ms_q = time_steps(quant_step, qsteps, 5, stream, dist, world) / qsteps
+        qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
+        qgbs = qbytes / (ms_q * 1e-3) / 1e9
+        extra["quant_8192"] = {"metric": "quantize_bf16_nvfp4_8192x8192_gbs", "value": qgbs * world, "unit": "GB/s", "us_per_call": ms_q * 1e3,
+                               "roofline": {"bound": "hbm", "achieved": qgbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                            "frac": qgbs / peaks["hbm_gbs"], "traffic": traffic.get("quant_8192_dram_bytes")},
+                               "config": {"workload": "quantize_ex_8192x8192_bf16_swizzled_amax", "l2": "3 rotating inputs (403 MB) > L2"}}
+        del xs
+
+    # ---- CPU baseline beside it (rank 0, N = 1 only): bounded sample of the same GEMM through the oracle ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        cols = 32
+        cpu_gemm_sample(4, threads)
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+            cpu_gemm_sample(cols, threads)
+            reps += 1
+        t = (time.perf_counter() - t0) / reps
+        cpu = {"value": 2.0 * M * cols * K / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"{reps} x ({cols} of {N} output columns x {M} rows x k {K}) through the oracle's exact block sums, incl. operand set-up"}
+
+    if rank == 0:
+        line = {"metric": "w4a4_gemm_4096_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "fp4 (e2m1, ue4m3 block scales) -> fp32 accumulate -> bf16", "data": "synthetic",
+                "config": {"workload": "w4a4_gemm_m4096_n4096_k4096", "entry": "nvfp4a_gemm", "scales": "linear E4M3 1x16, FP32 decode-factor globals",
+                           "l2": f"{nsets} rotating operand/output sets (157 MB) > L2", "per_rank": "independent GEMMs, no collective"},
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "extra": extra}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline beside the GPU number")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,6 +33,7 @@ struct W4A4Args {
   int ktiles;                  // image: 256-k tiles per row tile
   Epilogue e;
   unsigned *status;
+  int dbg;                     // debugging: 1 skip tcgen05.cp, 2 skip mma, 4 skip stores, 8 skip epilogue tmem loads
 };
 
 template <int BN, int ACC, int STAGES>
@@ -152,14 +153,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + (it % Cfg::kSfBuffers) * Cfg::kSfCols;
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
           const int ng = min(4, (g.k - ks * 256) / 64);
-          for (int j = 0; j < ng; ++j) {
+          for (int j = 0; j < ng && !(g.dbg & 1); ++j) {
             tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
 #pragma unroll
             for (int h = 0; h < BN / 128; ++h)
               tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
           }
           const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
-          for (int j = 0; j < ng; ++j)  // 64 values of k = 32 bytes further along each 128-byte row
+          for (int j = 0; j < ng && !(g.dbg & 2); ++j)  // 64 values of k = 32 bytes further along each 128-byte row
             mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
           tc_commit(&empty[s]);
         }
@@ -184,9 +185,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int c = 0; c < BN / 32; ++c) {
         if (tn * BN + c * 32 >= g.n) break;  // whole chunk beyond n (uniform)
         uint32_t r[32];
+        if (g.dbg & 8) break;
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
-        if (row_ok) {
+        if (row_ok && !(g.dbg & 4)) {
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) {
             const int j = tn * BN + c * 32 + jj;
@@ -308,6 +310,8 @@ static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, cons
   return cudaGetLastError();
 }
 
+static int g_w4a4_dbg = 0;
+void set_w4a4_dbg(int d) { g_w4a4_dbg = d; }
 static int g_w4a4_bn = 0;  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
 void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
 
@@ -318,6 +322,7 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   a.e = g.e;
   a.status = kernel_status_device_ptr();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
+  a.dbg = g_w4a4_dbg;
   const int bn = g_w4a4_bn ? g_w4a4_bn : (g.n > 128 ? 256 : 128);
   CUtensorMap ta, tb;
   const Fp4Operand &A = g.A, &B = g.B.q;
@@ -353,6 +358,8 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
   if (e == cudaSuccess && reset) e = cudaMemset(p, 0, sizeof(unsigned int));
   return cuda_fail(e, "nvfp4a_b200_kernel_status");
 }
+
+extern "C" void nvfp4a_b200_debug(int d) { nvb::set_w4a4_dbg(d); }
 
 extern "C" int nvfp4a_b200_set_tile_n(int bn) {
   if (bn != 0 && bn != 128 && bn != 256) return -1;

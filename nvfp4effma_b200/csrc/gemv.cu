@@ -1,5 +1,198 @@
+// Streaming GEMV for decoding: D[m x n] = A[m x k] (NVFP4) * B[n x k]^T with 1 <= n <= 8 and BF16 activations (W4A16).
+//
+// The kernel is bound by reading A once from HBM (0.5625 bytes per weight), so it is built around 16-byte loads and as
+// few instructions per weight as an exact decode allows:
+//   * one CTA owns 16 consecutive rows (one m16 slice), its warps split k in steps of 128 values; per step a lane loads
+//     16 bytes of nibbles for two rows (a quad of lanes covers 64 contiguous bytes of a row) and the two scale bytes of its
+//     32 values;
+//   * nibbles are decoded to exact BF16 pairs with shifts and masks (value * 2^-126, the subnormal trick), multiplied by
+//     the block scale in BF16 (exact: 2 x 4 significant bits) and fed to mma.sync.m16n8k16 (BF16 in, FP32 accumulate),
+//     whose 8 columns are the n <= 8 activation vectors.  The order of k inside a step is permuted the same way for A
+//     and B, which a dot product allows;
+//   * the warps' partial sums are added in warp order through shared memory (deterministic, no atomics), then the plain
+//     or extended epilogue runs on the slice.
+// Accumulation is FP32 in the tensor cores' order: results agree with the reference's exact definition
+// (include/nvfp4effma.h:82-92 there) within the FP32 accumulation bound, as its own tensor-core GEMV does
+// (src/tensors/gemv_tc.cuh there).  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for
+// E4M3, 16 for UE5M3 scales) and the sum is multiplied by 2^Z at the end; this is exact unless a product is below
+// 2^-118 in magnitude.
+#include <cuda_bf16.h>
 #include "operands.cuh"
+
 namespace nvb {
-bool gemv_supports(const GemmArgs &) { return false; }
-cudaError_t launch_gemv(const GemmArgs &, cudaStream_t) { return cudaErrorNotSupported; }
+
+constexpr int kGemvWarps = 8;
+
+struct GemvArgs {
+  int m, n, k;
+  Fp4Operand A;
+  const uint16_t *x; int ldx;   // BF16 activations [n][ldx]
+  Epilogue e;
+  EpilogueEx ex;
+};
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// nibbles p and p + 4 of w -> BF16 pair (low half: nibble p), each value * 2^-126: magnitude bits to [6, 9), sign to 15
+template <int P>
+__device__ __forceinline__ uint32_t decode_pair(uint32_t w) {
+  const uint32_t mag = (P < 2 ? w << (6 - 4 * P) : w >> (4 * P - 6)) & 0x01C001C0u;
+  const uint32_t sgn = (w << (12 - 4 * P)) & 0x80008000u;
+  return mag | sgn;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+__global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g) {
+  __shared__ uint32_t lut[256];                       // scale code -> BF16 pair (sa * 2^(126 - Z), twice)
+  __shared__ float part[kGemvWarps][16][8];
+  __shared__ float vtile[8][16];
+  __shared__ float colscale[8];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
+  const int i0 = blockIdx.x * 16;
+  const bool ue = g.A.ue != 0;
+  const int Z = ue ? 16 : 8;
+  {
+    const float s = scale_to_f32((uint32_t)tid, ue) * (ue ? 0x1p110f : 0x1p118f);  // exact: 4 significant bits
+    const uint32_t h = __float_as_uint(s) >> 16;
+    lut[tid] = h | (h << 16);
+  }
+  if ((g.ex.mask & kExNorm) && warp < g.n) {
+    const float s = warp_norm_scale(g.ex, warp, lane);
+    if (lane == 0) colscale[warp] = s;
+  }
+  __syncthreads();
+
+  // rows of this lane (clamped for the loads; rows past m are never stored)
+  const int r0 = min(i0 + gq, g.m - 1), r1 = min(i0 + gq + 8, g.m - 1);
+  const bool has_col = gq < g.n;
+  const uint16_t *xrow = g.x + (size_t)(has_col ? gq : 0) * g.ldx;
+  const ScalePos sp{g.A.sld};
+  const uint8_t *a0p, *a1p, *s0p, *s1p;
+  if (!g.A.image) {
+    a0p = g.A.data + (size_t)r0 * (g.A.ld >> 1); a1p = g.A.data + (size_t)r1 * (g.A.ld >> 1);
+    s0p = g.A.sc + sp.row(r0); s1p = g.A.sc + sp.row(r1);
+  } else {
+    a0p = g.A.data + (size_t)(r0 >> 7) * g.A.ktiles * kImgTileBytes + (r0 & 127) * 128;
+    a1p = g.A.data + (size_t)(r1 >> 7) * g.A.ktiles * kImgTileBytes + (r1 & 127) * 128;
+    s0p = g.A.data + (size_t)(r0 >> 7) * g.A.ktiles * kImgTileBytes + kImgDataBytes + (r0 & 31) * 16 + ((r0 & 127) >> 5) * 4;
+    s1p = g.A.data + (size_t)(r1 >> 7) * g.A.ktiles * kImgTileBytes + kImgDataBytes + (r1 & 31) * 16 + ((r1 & 127) >> 5) * 4;
+  }
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int chunks = g.k >> 5;  // 32-value chunks; a step is 4 of them (one per lane of a quad)
+  const int nsteps = (chunks + 3) >> 2;
+  for (int st = warp; st < nsteps; st += kGemvWarps) {
+    const int c = 4 * st + q;          // this lane's chunk: k in [32 c, 32 c + 32)
+    const bool in = c < chunks;
+    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+    uint32_t sc0 = 0, sc1 = 0;         // two scale codes per row (blocks 2 c, 2 c + 1)
+    if (in) {
+      if (!g.A.image) {
+        w0 = __ldg((const uint4 *)(a0p + 16 * c));
+        w1 = __ldg((const uint4 *)(a1p + 16 * c));
+        sc0 = __ldg((const uint16_t *)(s0p + sp.col(2 * c)));
+        sc1 = __ldg((const uint16_t *)(s1p + sp.col(2 * c)));
+      } else {
+        const size_t t = (size_t)(c >> 3) * kImgTileBytes;  // 256-k tile = 8 chunks
+        const int cc = c & 7;
+        w0 = __ldg((const uint4 *)(a0p + t + 16 * cc));
+        w1 = __ldg((const uint4 *)(a1p + t + 16 * cc));
+        const int off = (cc >> 1) * 512 + (cc & 1) * 2;     // 64-k group, then block pair inside it
+        sc0 = __ldg((const uint16_t *)(s0p + t + off));
+        sc1 = __ldg((const uint16_t *)(s1p + t + off));
+      }
+    }
+    uint4 xv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xv[i] = (in && has_col) ? __ldg((const uint4 *)(xrow + 32 * c) + i) : make_uint4(0, 0, 0, 0);
+
+    const uint32_t S0[2] = {lut[sc0 & 0xFF], lut[(sc0 >> 8) & 0xFF]}, S1[2] = {lut[sc1 & 0xFF], lut[(sc1 >> 8) & 0xFF]};
+    const uint32_t ww0[4] = {w0.x, w0.y, w0.z, w0.w}, ww1[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // word i: 8 values, k = 32 c + 8 i ..; block i / 2 of the chunk
+      const uint32_t a = ww0[i], b = ww1[i], sa = S0[i >> 1], sb = S1[i >> 1];
+      // B pairs (x[p], x[p + 4]) to match the decode's pairing
+      const uint32_t x04 = prmt(xv[i].x, xv[i].z, 0x5410), x15 = prmt(xv[i].x, xv[i].z, 0x7632);
+      const uint32_t x26 = prmt(xv[i].y, xv[i].w, 0x5410), x37 = prmt(xv[i].y, xv[i].w, 0x7632);
+      mma_bf16_16816(acc, bf16x2_mul(decode_pair<0>(a), sa), bf16x2_mul(decode_pair<0>(b), sb), bf16x2_mul(decode_pair<1>(a), sa),
+                     bf16x2_mul(decode_pair<1>(b), sb), x04, x15);
+      mma_bf16_16816(acc, bf16x2_mul(decode_pair<2>(a), sa), bf16x2_mul(decode_pair<2>(b), sb), bf16x2_mul(decode_pair<3>(a), sa),
+                     bf16x2_mul(decode_pair<3>(b), sb), x26, x37);
+    }
+  }
+  // partial sums of this warp: c0, c1 -> (row gq, columns 2 q, 2 q + 1); c2, c3 -> row gq + 8
+  part[warp][gq][2 * q] = acc[0]; part[warp][gq][2 * q + 1] = acc[1];
+  part[warp][gq + 8][2 * q] = acc[2]; part[warp][gq + 8][2 * q + 1] = acc[3];
+  __syncthreads();
+
+  // ---- epilogue on the slice: thread t < 128 owns (row t % 16, column t / 16) ----
+  const Epilogue &e = g.e;
+  const int ri = tid & 15, cj = tid >> 4, i = i0 + ri;
+  const bool live = tid < 128 && i < g.m && cj < g.n;
+  float v = 0.f, amax = 0.f;
+  if (live) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGemvWarps; ++w) s = __fadd_rn(s, part[w][ri][cj]);
+    s = __fmul_rn(s, ue ? 65536.f : 256.f);
+    float colp = epi_col_part(e, cj);
+    if (g.ex.mask & kExNorm) colp = __fmul_rn(colp, colscale[cj]);
+    v = epi_value(e, i, cj, s, epi_scale(e, epi_row_part(e, i), colp));
+  }
+  (void)Z;
+  if (!(g.ex.mask & (kExSwiglu | kExOut2))) {
+    if (live) { store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + i, v); amax = fabsf(v); }
+  } else {
+    if (tid < 128) vtile[cj][ri] = v;
+    __syncthreads();
+    if (g.ex.mask & kExSwiglu) {
+      if (live && ri < 8) {
+        const float h = silu_mul(vtile[cj][ri], vtile[cj][ri + 8]);
+        store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + (i0 >> 1) + ri, h);
+        amax = fabsf(h);
+      }
+    } else if (live) {
+      store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + i, v);
+      amax = fabsf(v);
+    }
+    if (g.ex.mask & kExOut2) {
+      if (live) store_dense(g.ex.d2_dtype, g.ex.d2, (size_t)cj * g.ex.ldd2 + i, __fmul_rn(v, load_dense(g.ex.w2_dtype, g.ex.w2, i)));
+      if (live && ri == 0) {
+        float sq = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) sq = __fadd_rn(sq, __fmul_rn(vtile[cj][r], vtile[cj][r]));
+        g.ex.sq[(size_t)cj * g.ex.ld_sq + (i0 >> 4)] = sq;
+      }
+    }
+  }
+  if (e.amax && tid < 128) warp_amax_commit(e.amax, amax);
+}
+
+bool gemv_supports(const GemmArgs &g) {
+  return g.n >= 1 && g.n <= 8 && g.B.dtype == NVFP4A_BF16 && g.k > 0 && ((uintptr_t)g.B.data & 15) == 0 &&
+         (g.A.image || ((uintptr_t)g.A.sc & 1) == 0);
+}
+
+cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
+  GemvArgs a;
+  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.A = g.A;
+  a.x = (const uint16_t *)g.B.data; a.ldx = g.B.ld;
+  a.e = g.e; a.ex = g.x;
+  gemv_kernel<<<(g.m + 15) / 16, kGemvWarps * 32, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace nvb
