@@ -33,6 +33,7 @@ struct W4A4Args {
   int ktiles;                  // image: 256-k tiles per row tile
   Epilogue e;
   unsigned *status;
+  int d_tma;                   // D is stored by TMA from a shared-memory staging tile (needs 16-byte aligned D and column stride)
   int dbg;                     // debugging: 1 skip tcgen05.cp, 2 skip mma, 4 skip stores, 8 skip epilogue tmem loads
 };
 
@@ -44,17 +45,21 @@ struct W4A4Cfg {
   static constexpr int kSfBuffers = 2;
   static constexpr int kAccCols = ACC * BN;
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kStagingBytes = 8192;       // epilogue staging: 128 rows x 32 (16-bit) or 16 (32-bit) columns
+  static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kStagingBytes;
   static_assert(kAccCols + kSfBuffers * kSfCols <= kTmemCols, "tensor memory budget");
 };
 
 constexpr int kThreads = 320;
+__device__ unsigned long long g_dbg_times[16];  // debugging (dbg & 32): cycles per role phase, summed over CTAs
+#define DBG_T(slot, expr) do { if (dbg & 32) { const long long t0_ = clock64(); expr; atomicAdd(&g_dbg_times[slot], (unsigned long long)(clock64() - t0_)); } else { expr; } } while (0)
 constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
                    kStatusWaitGather = 0x105;
 
 template <int BN, int ACC, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const W4A4Args g) {
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_d, const W4A4Args g) {
   using Cfg = W4A4Cfg<BN, ACC, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -62,11 +67,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + ACC;
   uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 2 * ACC);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  uint8_t *staging = smem + STAGES * Cfg::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (g.m + 127) / 128, tiles_n = (g.n + BN - 1) / BN, ntiles = tiles_m * tiles_n;
-  const int nk = (g.k + 255) / 256;
-  const bool any_gather = g.sa_gather || g.sb_gather;
+  const int gm = g.m, gn = g.n, gk = g.k, dbg = g.dbg, ktiles = g.ktiles;
+  const bool a_image = g.a_image, b_image = g.b_image, sa_gather = g.sa_gather, sb_gather = g.sb_gather, d_tma = g.d_tma;
+  const uint8_t *const sa_base = g.sa, *const sb_base = g.sb;
+  const int sa_ld = g.sa_ld, sb_ld = g.sb_ld;
+  const int tiles_m = (gm + 127) / 128, tiles_n = (gn + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int nk = (gk + 255) / 256;
+  const bool any_gather = sa_gather || sb_gather;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); }
@@ -82,15 +92,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto give_up = [&](unsigned code) {
-    *abort_flag = 1;
-    atomicCAS(g.status, 0u, code);
-  };
+  // Kernel parameters are copied into registers here: a parameter struct whose members are reached through references
+  // is re-read from parameter memory (hundreds of cycles) at every use inside the loops below.
+  unsigned *const status_word = g.status;
   // wait that also ends when another role has raised the abort flag
-  auto wait = [&](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
-    give_up(code);
+    *abort_flag = 1;
+    atomicCAS(status_word, 0u, code);
     return false;
   };
 
@@ -102,33 +112,35 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int tm = t % tiles_m, tn = t / tiles_m;
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % STAGES;
-          if (!wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty)) goto done;
+          bool okw;
+          DBG_T(0, okw = wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty));
+          if (!okw) goto done;
           uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
           uint8_t *sA = st, *sB = st + Cfg::kABytes, *sSfa = sB + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
-          const int ng = min(4, (g.k - ks * 256) / 64);  // 64-value groups of this stage inside k
+          const int ng = min(4, (gk - ks * 256) / 64);  // 64-value groups of this stage inside k
           uint32_t bytes = Cfg::kABytes + Cfg::kBBytes;
-          if (!g.sa_gather) bytes += g.a_image ? 2048 : ng * 512;
-          if (!g.sb_gather)
+          if (!sa_gather) bytes += a_image ? 2048 : ng * 512;
+          if (!sb_gather)
             for (int h = 0; h < BN / 128; ++h)
-              if (tn * BN + h * 128 < g.n) bytes += g.b_image ? 2048 : ng * 512;
+              if (tn * BN + h * 128 < gn) bytes += b_image ? 2048 : ng * 512;
           mbar_arrive_expect_tx(&full[s], bytes);
-          if (g.a_image) tma_load_3d(sA, &tmap_a, 0, 0, tm * g.ktiles + ks, &full[s]);
+          if (a_image) tma_load_3d(sA, &tmap_a, 0, 0, tm * ktiles + ks, &full[s]);
           else tma_load_2d(sA, &tmap_a, ks * 128, tm * 128, &full[s]);
-          if (g.b_image) {
-            for (int h = 0; h < BN / 128; ++h) tma_load_3d(sB + h * 16384, &tmap_b, 0, 0, (tn * (BN / 128) + h) * g.ktiles + ks, &full[s]);
+          if (b_image) {
+            for (int h = 0; h < BN / 128; ++h) tma_load_3d(sB + h * 16384, &tmap_b, 0, 0, (tn * (BN / 128) + h) * ktiles + ks, &full[s]);
           } else {
             tma_load_2d(sB, &tmap_b, ks * 128, tn * BN, &full[s]);
           }
-          if (!g.sa_gather) {
-            if (g.a_image) bulk_load(sSfa, g.sa + ((size_t)tm * g.ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-            else bulk_load(sSfa, g.sa + ((size_t)tm * ((-g.sa_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
+          if (!sa_gather) {
+            if (a_image) bulk_load(sSfa, sa_base + ((size_t)tm * ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
+            else bulk_load(sSfa, sa_base + ((size_t)tm * ((-sa_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
           }
-          if (!g.sb_gather) {
+          if (!sb_gather) {
             for (int h = 0; h < BN / 128; ++h) {
               const int rt = tn * (BN / 128) + h;
-              if (rt * 128 >= g.n) continue;
-              if (g.b_image) bulk_load(sSfb + h * 2048, g.sb + ((size_t)rt * g.ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-              else bulk_load(sSfb + h * 2048, g.sb + ((size_t)rt * ((-g.sb_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
+              if (rt * 128 >= gn) continue;
+              if (b_image) bulk_load(sSfb + h * 2048, sb_base + ((size_t)rt * ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
+              else bulk_load(sSfb + h * 2048, sb_base + ((size_t)rt * ((-sb_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
             }
           }
         }
@@ -141,78 +153,174 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0, tile_i = 0;
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
         const int acc = tile_i % ACC;
-        if (!wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty)) goto done;
+        bool okw;
+        DBG_T(1, okw = wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty));
+        if (!okw) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % STAGES;
-          if (!wait(&full[s], (it / STAGES) & 1, kStatusWaitFull)) goto done;
+          DBG_T(2, okw = wait(&full[s], (it / STAGES) & 1, kStatusWaitFull));
+          if (!okw) goto done;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
           const uint32_t sA = st, sB = st + Cfg::kABytes, sSfa = sB + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;
           const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + (it % Cfg::kSfBuffers) * Cfg::kSfCols;
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
-          const int ng = min(4, (g.k - ks * 256) / 64);
-          for (int j = 0; j < ng && !(g.dbg & 1); ++j) {
-            tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
-          }
+          const int ng = min(4, (gk - ks * 256) / 64);
           const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
-          for (int j = 0; j < ng && !(g.dbg & 2); ++j)  // 64 values of k = 32 bytes further along each 128-byte row
-            mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+          if (dbg & 256) {  // experiment: all scale copies of the stage first, then its MMAs
+            for (int j = 0; j < ng && !(dbg & 1); ++j) {
+              tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
+#pragma unroll
+              for (int h = 0; h < BN / 128; ++h)
+                tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+            }
+            for (int j = 0; j < ng && !(dbg & 2); ++j)
+              mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+          } else {
+            // per 64 values of k: the scale tiles of that group, then its MMA (32 bytes further along each 128-byte row)
+            for (int j = 0; j < ng; ++j) {
+              if (!(dbg & 1)) {
+                tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
+#pragma unroll
+                for (int h = 0; h < BN / 128; ++h)
+                  tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+              }
+              if (!(dbg & 2))
+                mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+            }
+          }
           tc_commit(&empty[s]);
         }
         tc_commit(&tmem_full[acc]);
       }
     }
   } else if (warp < 6) {
-    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    // ---------------- epilogue: TMEM -> registers -> (staging tile -> TMA store | direct stores) ----------------
+    // Everything the loops need is held in plain locals (see the note on kernel parameters above).
     const int quad = warp & 3;
-    const Epilogue &e = g.e;
+    const float *const ga = g.e.ga, *const gb = g.e.gb;
+    const int ga_stride = g.e.ga_stride, gb_stride = g.e.gb_stride;
+    const float gf = g.e.gf, alpha = g.e.alpha, beta = g.e.beta;
+    const void *const cptr = g.e.c, *const biasptr = g.e.bias;
+    const int ldc = g.e.ldc, c_dtype = g.e.c_dtype, bias_dtype = g.e.bias_dtype;
+    uint8_t *const dptr = (uint8_t *)g.e.d;
+    const int ldd = g.e.ldd, d_dtype = g.e.d_dtype;
+    float *const amax_out = g.e.amax;
+    const int esz = dense_bytes(d_dtype);
+    const int cw = esz == 2 ? 32 : 16;          // columns per staging round: 128 rows x cw columns = 8 KiB
+    const bool leader = warp == 2 && lane == 0; // issues and tracks the TMA stores
+    const bool fast = beta == 0.f && gb_stride == 0;  // one scale per lane, no C: the common case
+    const float colp0 = (gb && !gb_stride) ? gb[0] : 1.f;
     float amax = 0.f;
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
       const int tm = t % tiles_m, tn = t / tiles_m, acc = tile_i % ACC;
       const int i = tm * 128 + quad * 32 + lane;
-      const bool row_ok = i < g.m;
-      const float rowp = row_ok ? epi_row_part(e, i) : 0.f;
-      const float bias = (row_ok && e.bias) ? load_dense(e.bias_dtype, e.bias, i) : 0.f;
-      if (!wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull)) goto done;
+      const bool row_ok = i < gm;
+      const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
+      const float bias = (row_ok && biasptr) ? load_dense(bias_dtype, biasptr, i) : 0.f;
+      const float s_lane = __fmul_rn(__fmul_rn(rowp, colp0), gf);
+      // the four epilogue warps decide together whether to go on: none may be left alone at a named barrier
+      bool okw;
+      DBG_T(3, okw = wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull));
+      if (!okw) *abort_flag = 1;
+      const long long tep0 = clock64();
+      named_barrier(1, 128);
+      if (*abort_flag) goto done;
       tc_fence_after();
-      const float colp0 = (e.gb && !e.gb_stride) ? e.gb[0] : 1.f;
-      for (int c = 0; c < BN / 32; ++c) {
-        if (tn * BN + c * 32 >= g.n) break;  // whole chunk beyond n (uniform)
+      const int nchunks = min(BN / 32, (gn - tn * BN + 31) / 32);
+      for (int c = 0; c < nchunks; ++c) {
         uint32_t r[32];
-        if (g.dbg & 8) break;
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
-        if (row_ok && !(g.dbg & 4)) {
+        if (c == nchunks - 1) {  // accumulator drained into registers: the MMA warp may start the next tile on it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+        if (dbg & 4) continue;
+        const int j0 = tn * BN + c * 32;
+        const int nvalid = min(32, gn - j0);
+        // values before rounding, kept in r[] as FP32 bits
+        if (fast) {
+          if (biasptr) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(__fadd_rn(__fmul_rn(__uint_as_float(r[jj]), s_lane), bias));
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(__fmul_rn(__uint_as_float(r[jj]), s_lane));
+          }
+        } else {
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) {
-            const int j = tn * BN + c * 32 + jj;
-            if (j < g.n) {
-              const float colp = e.gb_stride ? e.gb[j] : colp0;
-              float v = __fmul_rn(__uint_as_float(r[jj]), epi_scale(e, rowp, colp));
-              if (e.bias) v = __fadd_rn(v, bias);
-              if (e.beta != 0.f) v = __fmaf_rn(e.beta, load_dense(e.c_dtype, e.c, (size_t)j * e.ldc + i), v);
-              amax = fmaxf(amax, fabsf(v));
-              store_dense(e.d_dtype, e.d, (size_t)j * e.ldd + i, v);
+            const int j = j0 + jj;
+            const bool ok = row_ok && jj < nvalid;
+            const float colp = (gb_stride && jj < nvalid) ? gb[j] : colp0;
+            float v = __fmul_rn(__uint_as_float(r[jj]), __fmul_rn(__fmul_rn(rowp, colp), gf));
+            if (biasptr) v = __fadd_rn(v, bias);
+            if (beta != 0.f && ok) v = __fmaf_rn(beta, load_dense(c_dtype, cptr, (size_t)j * ldc + i), v);
+            r[jj] = __float_as_uint(v);
+          }
+        }
+        if (amax_out && row_ok) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            if (jj < nvalid) amax = fmaxf(amax, fabsf(__uint_as_float(r[jj])));
+        }
+        // rounding to the output type (in place, low bits of r[])
+        if (d_dtype == NVFP4A_BF16) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = f32_to_bf16_bits(__uint_as_float(r[jj]));
+        } else if (d_dtype == NVFP4A_FP16) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(r[jj])));
+        }
+        if (!d_tma) {  // plain stores: any alignment, any ldd
+          if (row_ok) {
+            if (esz == 2) {
+              uint16_t *d16 = (uint16_t *)dptr + (size_t)j0 * ldd + i;
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (jj < nvalid) d16[(size_t)jj * ldd] = (uint16_t)r[jj];
+            } else {
+              uint32_t *d32 = (uint32_t *)dptr + (size_t)j0 * ldd + i;
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (jj < nvalid) d32[(size_t)jj * ldd] = r[jj];
             }
+          }
+          continue;
+        }
+        for (int half = 0; half < 32 / cw; ++half) {
+          if (leader) bulk_wait_read_all();   // the previous store has finished reading the staging tile
+          named_barrier(1, 128);
+          const int rr = quad * 32 + lane;
+          if (esz == 2) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) ((uint16_t *)staging)[jj * 128 + rr] = (uint16_t)r[jj];
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) ((uint32_t *)staging)[jj * 128 + rr] = half ? r[16 + jj] : r[jj];
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (leader) {
+            tma_store_2d(&tmap_d, staging, tm * 128, j0 + half * cw);
+            bulk_commit();
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if ((dbg & 32) && warp == 2 && lane == 0) atomicAdd(&g_dbg_times[4], (unsigned long long)(clock64() - tep0));
     }
-    if (e.amax) warp_amax_commit(e.amax, amax);
+    if (leader) bulk_wait_all();
+    if (amax_out) warp_amax_commit(amax_out, amax);
   } else if (any_gather) {
     // ---------------- scale gather: linear / unaligned block scales -> 512-byte tiles in shared memory ----------------
     // Warp w of the four takes the pipeline iterations it % 4 == w, so four stages' loads are in flight together.
     const int w = warp - 6;
-    const ScalePos pa{g.sa_ld}, pb{g.sb_ld};
+    const ScalePos pa{sa_ld}, pb{sb_ld};
     uint32_t it = 0;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
       const int tm = t % tiles_m, tn = t / tiles_m;
@@ -222,7 +330,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitGather)) goto done;
         uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
         uint8_t *sSfa = st + Cfg::kABytes + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
-        const int ng = min(4, (g.k - ks * 256) / 64);
+        const int ng = min(4, (gk - ks * 256) / 64);
         // one 128-row tile: lane l owns rows l, l + 32, l + 64, l + 96; per 64-k group the four rows' words form 16 bytes
         auto gather_tile = [&](const uint8_t *sc, const ScalePos &p, int row0, int rows, uint8_t *dst) {
           uint32_t wd[4][4];
@@ -236,10 +344,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 4; ++j) *(uint4 *)(dst + j * 512 + lane * 16) = make_uint4(wd[0][j], wd[1][j], wd[2][j], wd[3][j]);
         };
-        if (g.sa_gather) gather_tile(g.sa, pa, tm * 128, g.m, sSfa);
-        if (g.sb_gather)
+        if (sa_gather) gather_tile(sa_base, pa, tm * 128, gm, sSfa);
+        if (sb_gather)
           for (int h = 0; h < BN / 128; ++h)
-            if (tn * BN + h * 128 < g.n) gather_tile(g.sb, pb, tn * BN + h * 128, g.n, sSfb + h * 2048);
+            if (tn * BN + h * 128 < gn) gather_tile(sb_base, pb, tn * BN + h * 128, gn, sSfb + h * 2048);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);
@@ -289,12 +397,25 @@ bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uin
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t stride,
+                     uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {stride};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool gemm_w4a4_supports(const GemmArgs &g) {
   return g.B.dtype == NVFP4A_NVFP4 && !g.A.ue && !g.B.q.ue && !g.x.mask && g.k >= 64 && encode_fn() != nullptr;
 }
 
 template <int BN, int ACC, int STAGES>
-static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const W4A4Args &a, cudaStream_t s) {
+static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &td, const W4A4Args &a, cudaStream_t s) {
   using Cfg = W4A4Cfg<BN, ACC, STAGES>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -306,7 +427,7 @@ static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, cons
   }
   const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
   const int grid = tiles < device_sms() ? tiles : device_sms();
-  gemm_w4a4_kernel<BN, ACC, STAGES><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ta, tb, a);
+  gemm_w4a4_kernel<BN, ACC, STAGES><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ta, tb, td, a);
   return cudaGetLastError();
 }
 
@@ -342,8 +463,14 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
     if (!make_tmap_bytes(&tb, B.data, (uint64_t)g.k / 2, (uint64_t)g.n, (uint64_t)B.ld / 2, bn)) return cudaErrorInvalidValue;
     a.sb = B.sc; a.sb_ld = B.sld; a.sb_gather = tiled_ok(B) ? 0 : 1;
   }
-  if (bn == 256) return launch_cfg<256, 1, 4>(ta, tb, a, s);
-  return launch_cfg<128, 2, 6>(ta, tb, a, s);
+  // D through TMA when its base and column stride are 16-byte aligned; otherwise plain stores from registers
+  CUtensorMap td;
+  memset(&td, 0, sizeof td);
+  const int esz = dense_bytes(g.e.d_dtype);
+  a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 && !(g_w4a4_dbg & 16) &&
+            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
+  if (bn == 256) return launch_cfg<256, 1, 4>(ta, tb, td, a, s);
+  return launch_cfg<128, 2, 6>(ta, tb, td, a, s);
 }
 
 }  // namespace nvb
@@ -360,6 +487,11 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
 }
 
 extern "C" void nvfp4a_b200_debug(int d) { nvb::set_w4a4_dbg(d); }
+extern "C" void nvfp4a_b200_debug_times(unsigned long long *out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, nvb::g_dbg_times, sizeof(unsigned long long) * 16);
+  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(nvb::g_dbg_times, z, sizeof z); }
+}
 
 extern "C" int nvfp4a_b200_set_tile_n(int bn) {
   if (bn != 0 && bn != 128 && bn != 256) return -1;

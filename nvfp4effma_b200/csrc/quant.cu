@@ -98,17 +98,32 @@ struct QOut {
 };
 
 // ---- pass 1: global amax ----------------------------------------------------------------------------------------------
-// One 16-value block per thread and iteration, ascending; one atomicMax per warp.  a1 (optional) receives the same value.
+// A warp takes units of 128 consecutive 16-value blocks of one row, ascending; each lane has four blocks (eight 16-byte
+// loads) in flight.  One atomicMax per warp at the end.  a1 (optional) receives the same value.
+constexpr int kAmaxU = 4;
 template <int T>
 __global__ void __launch_bounds__(256) amax_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, float *a0, float *a1) {
-  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int upr = (bpr + 32 * kAmaxU - 1) / (32 * kAmaxU);  // units per row
+  const long long units = (long long)rows * upr, wstride = (long long)gridDim.x * (blockDim.x >> 5);
   float m = 0.f;
-  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += stride) {
-    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
-    float v[16];
-    load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
+  for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < units; u += wstride) {
+    const int r = (int)(u / upr), seg = (int)(u - (long long)r * upr);
+    const uint8_t *rowp = src + (size_t)r * lds * ElemBytes<T>::value;
+    float v[kAmaxU][16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    for (int k = 0; k < kAmaxU; ++k) {
+      const int c = (seg * kAmaxU + k) * 32 + lane;
+      if (c < bpr) load16<T>(rowp + (size_t)c * 16 * ElemBytes<T>::value, v[k]);
+      else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[k][i] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kAmaxU; ++k)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[k][i]));
   }
   warp_amax_commit(a0, m);
   if (a1 && a1 != a0) warp_amax_commit(a1, m);
@@ -132,48 +147,61 @@ __global__ void __launch_bounds__(256) amax_rows_kernel(const uint8_t *__restric
 }
 
 // ---- pass 2, fast path: rowwise 1 x 16 blocks, one global per tensor, no 4over6 --------------------------------------------
-// Thread per block, consecutive threads on consecutive blocks of a row (1 KiB of BF16 per warp and load pair).  Blocks
-// are visited from the END of the matrix: after an amax pass the tail of the matrix is what L2 still holds.
-// SWZ: swizzled scale layout; a quad of lanes owns the 4 scales of one 64-value group, which are contiguous there, so
-// lane 0 of the quad stores them as one word (needs bpr % 4 == 0, else bytes).
-template <int T, bool SWZ>
-__global__ void __launch_bounds__(256) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
-  const long long total = (long long)rows * bpr, stride = (long long)gridDim.x * blockDim.x;
+// A warp takes units of 64 consecutive blocks of one row; a lane owns blocks lane and lane + 32 of the unit (two 16-byte
+// loads each, all four in flight), writes 8 bytes of nibbles per block (256 contiguous bytes per warp and store) and
+// contributes its scale byte to a 4-byte word that every fourth lane stores -- the same code for the linear and the
+// swizzled layout, where the four scales of a 64-value group are contiguous too (needs bpr % 4 == 0, else bytes).
+// Units are visited from the END of the matrix: after an amax pass the tail of the matrix is what L2 still holds.
+constexpr int kQuantU = 2;
+template <int T>
+__global__ void __launch_bounds__(256, 3) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
+  const int lane = threadIdx.x & 31;
+  const int upr = (bpr + 32 * kQuantU - 1) / (32 * kQuantU);
+  const long long units = (long long)rows * upr, wstride = (long long)gridDim.x * (blockDim.x >> 5);
   const QGlobal G = make_global(o.g ? o.g[0] : 1.f, o.smax, o.amax_mode != 0);
-  const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f);
+  const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f), s_dec = G.s_dec;
   const ScalePos sp{o.sld};
-  const bool quad_store = SWZ && (bpr & 3) == 0;
+  // 4-byte scale stores need 4-byte aligned words: always true in the swizzled layout, in the linear one only for an aligned base and row pitch
+  const bool ue = o.ue != 0, words = (bpr & 3) == 0 && (o.sld < 0 || ((o.sld & 3) == 0 && ((uintptr_t)o.sc & 3) == 0));
+  uint8_t *const data = o.data, *const sc = o.sc;
+  const int ldq = o.ld >> 1;
   float mx = 0.f;
-  // every lane of a warp runs the same number of iterations (shuffles below): round the trip count up per warp
-  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  for (long long u = first - (threadIdx.x & 31); u < total; u += stride) {
-    const long long mine = u + (threadIdx.x & 31);
-    const bool live = mine < total;
-    const long long b = total - 1 - (live ? mine : u);
-    const int r = (int)(b / bpr), c = (int)(b - (long long)r * bpr);
-    float v[16];
-    load16<T>(src + ((size_t)r * lds + 16 * c) * ElemBytes<T>::value, v);
-    float bmax = 0.f;
+  for (long long uu = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); uu < units; uu += wstride) {
+    const long long u = units - 1 - uu;
+    const int r = (int)(u / upr), seg = (int)(u - (long long)r * upr);
+    const uint8_t *rowp = src + (size_t)r * lds * ElemBytes<T>::value;
+    float v[kQuantU][16];
+    int c[kQuantU];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
-    const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), o.ue != 0);
-    const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, o.ue != 0), G.s_dec)), kFltMax);
+    for (int k = 0; k < kQuantU; ++k) {
+      c[k] = (seg * kQuantU + k) * 32 + lane;
+      if (c[k] < bpr) load16<T>(rowp + (size_t)c[k] * 16 * ElemBytes<T>::value, v[k]);
+      else {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], inv);
-    const uint2 q = make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
-    if (live) {
-      mx = fmaxf(mx, bmax);
-      *(uint2 *)(o.data + (size_t)r * (o.ld / 2) + 8 * c) = q;
+        for (int i = 0; i < 16; ++i) v[k][i] = 0.f;
+      }
     }
-    if (quad_store) {
-      // blocks descend with the lane: lanes 4t..4t+3 hold columns c, c-1, c-2, c-3 with c % 4 == 3 at the quad's first lane
-      // only when (total - 1 - u) % 4 == 3, which holds because total and the warp's base u are multiples of 4
-      uint32_t w = live ? code << (8 * (c & 3)) : 0u;
-      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-      if (live && (c & 3) == 0) *(uint32_t *)(o.sc + sp.at(r, c)) = w;
-    } else if (live) {
-      o.sc[sp.at(r, c)] = (uint8_t)code;
+#pragma unroll
+    for (int k = 0; k < kQuantU; ++k) {
+      const bool live = c[k] < bpr;
+      float bmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[k][i]));
+      mx = fmaxf(mx, bmax);
+      const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), ue);
+      const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, ue), s_dec)), kFltMax);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[k][i] = __fmul_rn(v[k][i], inv);
+      const uint2 q = make_uint2(e2m1_pack8(v[k]), e2m1_pack8(v[k] + 8));
+      if (live) *(uint2 *)(data + (size_t)r * ldq + 8 * c[k]) = q;
+      if (words) {  // lanes 4 t .. 4 t + 3 hold the columns 4 t' .. 4 t' + 3 of one 64-value group (bpr % 4 == 0: all live or none)
+        uint32_t w = live ? code << (8 * (lane & 3)) : 0u;
+        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+        if (live && (lane & 3) == 0) *(uint32_t *)(sc + sp.at(r, c[k])) = w;
+      } else if (live) {
+        sc[sp.at(r, c[k])] = (uint8_t)code;
+      }
     }
   }
   if (stat) warp_amax_commit(stat, mx);
@@ -464,7 +492,7 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
         float *p0 = ar ? ar : ac, *p1 = ar ? ac : nullptr;
         cudaMemsetAsync(p0, 0, 4, stream);
         if (p1 && p1 != p0) cudaMemsetAsync(p1, 0, 4, stream);
-        amax_kernel<T><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, p0, p1);
+        amax_kernel<T><<<grid_for(blocks * 8, 4), 256, 0, stream>>>(s, lds, rows, bpr, p0, p1);
       }
     });
   }
@@ -476,8 +504,7 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
     by_dense(src->dtype, [&](auto tc) {
       constexpr int T = decltype(tc)::value;
       if (fast) {
-        if (o.sld < 0) quant_rows_kernel<T, true><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
-        else quant_rows_kernel<T, false><<<grid_for(blocks), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
+        quant_rows_kernel<T><<<grid_for(blocks * 16, 3), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
       } else {
         const int orows = col ? cols : rows, ocols = col ? rows : cols;
         const long long units = (long long)((orows + 15) / 16) * ((ocols + 15) / 16);

@@ -59,6 +59,16 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// shared -> global tile store (elements outside the tensor are clipped), tracked by bulk async-groups
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// barrier among `threads` threads of the CTA (id 1..15; 0 is __syncthreads)
+__device__ __forceinline__ void named_barrier(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -138,6 +148,10 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
 // box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside.  Returns false if the driver refuses.
 bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_rows,
                      uint64_t tiles = 0, uint64_t tile_stride = 0);
+// dense matrix [outer][inner] of 2- or 4-byte elements, `stride` bytes between outer indices, box = box_inner x box_outer,
+// no swizzle (the epilogue's store of D)
+bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t stride,
+                     uint32_t box_inner, uint32_t box_outer);
 // kernel status word: 0 = healthy; kernels that gave up a wait write a non-zero code (see nvfp4a_b200_kernel_status)
 unsigned int *kernel_status_device_ptr();
 
