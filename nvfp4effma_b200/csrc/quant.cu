@@ -98,33 +98,46 @@ struct QOut {
 };
 
 // ---- pass 1: global amax ----------------------------------------------------------------------------------------------
-// A warp takes units of 128 consecutive 16-value blocks of one row, ascending; each lane has four blocks (eight 16-byte
-// loads) in flight.  One atomicMax per warp at the end.  a1 (optional) receives the same value.
-constexpr int kAmaxU = 4;
+// Pure streaming read.  A warp takes units of 256 consecutive 16-byte words of one row (4 KiB), ascending; a lane has
+// eight 16-byte loads in flight.  BF16 / FP16 stay packed: |x| is a mask and the maximum a two-lane max (one instruction
+// per two values; the bit patterns of non-negative floats order like the floats).  One atomicMax per warp at the end.
 template <int T>
-__global__ void __launch_bounds__(256) amax_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, float *a0, float *a1) {
+__device__ __forceinline__ uint32_t packed_absmax(uint32_t m, uint32_t w) {
+  const uint32_t a = w & 0x7FFF7FFFu;
+  uint32_t d;
+  if (T == NVFP4A_BF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(a));
+  else asm("max.f16x2 %0, %1, %2;" : "=r"(d) : "r"(m), "r"(a));
+  return d;
+}
+template <int T>
+__global__ void __launch_bounds__(256, 4) amax_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, float *a0, float *a1) {
   const int lane = threadIdx.x & 31;
-  const int upr = (bpr + 32 * kAmaxU - 1) / (32 * kAmaxU);  // units per row
+  const int wpr = bpr * (T == NVFP4A_FP32 ? 4 : 2);        // 16-byte words per row
+  const int upr = (wpr + 255) / 256;                        // units per row
   const long long units = (long long)rows * upr, wstride = (long long)gridDim.x * (blockDim.x >> 5);
   float m = 0.f;
+  uint32_t pm = 0;
   for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < units; u += wstride) {
     const int r = (int)(u / upr), seg = (int)(u - (long long)r * upr);
-    const uint8_t *rowp = src + (size_t)r * lds * ElemBytes<T>::value;
-    float v[kAmaxU][16];
+    const uint4 *rowp = (const uint4 *)(src + (size_t)r * lds * ElemBytes<T>::value) + seg * 256;
+    uint4 w[8];
 #pragma unroll
-    for (int k = 0; k < kAmaxU; ++k) {
-      const int c = (seg * kAmaxU + k) * 32 + lane;
-      if (c < bpr) load16<T>(rowp + (size_t)c * 16 * ElemBytes<T>::value, v[k]);
-      else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[k][i] = 0.f;
-      }
+    for (int k = 0; k < 8; ++k) {
+      const int c = k * 32 + lane;
+      w[k] = seg * 256 + c < wpr ? __ldg(rowp + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int k = 0; k < kAmaxU; ++k)
-#pragma unroll
-      for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[k][i]));
+    for (int k = 0; k < 8; ++k) {
+      if (T == NVFP4A_FP32) {
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(w[k].x)), fabsf(__uint_as_float(w[k].y))),
+                           fmaxf(fabsf(__uint_as_float(w[k].z)), fabsf(__uint_as_float(w[k].w)))));
+      } else {
+        pm = packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(pm, w[k].x), w[k].y), w[k].z), w[k].w);
+      }
+    }
   }
+  if (T == NVFP4A_BF16) m = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xFFFF0000u));
+  else if (T == NVFP4A_FP16) { const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pm)); m = fmaxf(f.x, f.y); }
   warp_amax_commit(a0, m);
   if (a1 && a1 != a0) warp_amax_commit(a1, m);
 }
@@ -147,17 +160,51 @@ __global__ void __launch_bounds__(256) amax_rows_kernel(const uint8_t *__restric
 }
 
 // ---- pass 2, fast path: rowwise 1 x 16 blocks, one global per tensor, no 4over6 --------------------------------------------
-// A warp takes units of 64 consecutive blocks of one row; a lane owns blocks lane and lane + 32 of the unit (two 16-byte
-// loads each, all four in flight), writes 8 bytes of nibbles per block (256 contiguous bytes per warp and store) and
-// contributes its scale byte to a 4-byte word that every fourth lane stores -- the same code for the linear and the
-// swizzled layout, where the four scales of a 64-value group are contiguous too (needs bpr % 4 == 0, else bytes).
-// Units are visited from the END of the matrix: after an amax pass the tail of the matrix is what L2 still holds.
-constexpr int kQuantU = 2;
+// A warp takes units of 32 consecutive blocks of one row, a lane one block (two 16-byte loads for 16-bit sources).  The
+// loads of the next two units are already in flight while a unit is processed (register double buffering), so a warp
+// keeps 3 x 1 KiB outstanding.  A lane writes 8 bytes of nibbles (256 contiguous bytes per warp) and contributes its scale
+// byte to a 4-byte word that every fourth lane stores -- the same code for the linear and the swizzled layout, where the
+// four scales of a 64-value group are contiguous too.  Units are visited from the END of the matrix: after an amax pass
+// the tail of the matrix is what L2 still holds.
+template <int T> struct PackedBlock { uint4 w[T == NVFP4A_FP32 ? 4 : 2]; };
 template <int T>
-__global__ void __launch_bounds__(256, 3) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
+__device__ __forceinline__ PackedBlock<T> load_block(const uint8_t *p, bool live) {
+  PackedBlock<T> b;
+#pragma unroll
+  for (int q = 0; q < (T == NVFP4A_FP32 ? 4 : 2); ++q) b.w[q] = live ? __ldg((const uint4 *)p + q) : make_uint4(0, 0, 0, 0);
+  return b;
+}
+template <int T>
+__device__ __forceinline__ void unpack_block(const PackedBlock<T> &b, float v[16]) {
+  if (T == NVFP4A_FP32) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      v[4 * q] = __uint_as_float(b.w[q].x); v[4 * q + 1] = __uint_as_float(b.w[q].y);
+      v[4 * q + 2] = __uint_as_float(b.w[q].z); v[4 * q + 3] = __uint_as_float(b.w[q].w);
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint32_t ws[4] = {b.w[q].x, b.w[q].y, b.w[q].z, b.w[q].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (T == NVFP4A_BF16) {
+          v[8 * q + 2 * i] = __uint_as_float(ws[i] << 16);
+          v[8 * q + 2 * i + 1] = __uint_as_float(ws[i] & 0xFFFF0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ws[i]));
+          v[8 * q + 2 * i] = f.x; v[8 * q + 2 * i + 1] = f.y;
+        }
+      }
+    }
+  }
+}
+template <int T>
+__global__ void __launch_bounds__(256, 4) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
   const int lane = threadIdx.x & 31;
-  const int upr = (bpr + 32 * kQuantU - 1) / (32 * kQuantU);
-  const long long units = (long long)rows * upr, wstride = (long long)gridDim.x * (blockDim.x >> 5);
+  const int upr = (bpr + 31) >> 5;                 // units (of 32 blocks) per row
+  const long long units = (long long)rows * upr;
+  const int nwarps = gridDim.x * (blockDim.x >> 5), wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const QGlobal G = make_global(o.g ? o.g[0] : 1.f, o.smax, o.amax_mode != 0);
   const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f), s_dec = G.s_dec;
   const ScalePos sp{o.sld};
@@ -165,44 +212,46 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(const uint8_t *__res
   const bool ue = o.ue != 0, words = (bpr & 3) == 0 && (o.sld < 0 || ((o.sld & 3) == 0 && ((uintptr_t)o.sc & 3) == 0));
   uint8_t *const data = o.data, *const sc = o.sc;
   const int ldq = o.ld >> 1;
+  const size_t row_bytes = (size_t)lds * ElemBytes<T>::value;
   float mx = 0.f;
-  for (long long uu = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); uu < units; uu += wstride) {
-    const long long u = units - 1 - uu;
-    const int r = (int)(u / upr), seg = (int)(u - (long long)r * upr);
-    const uint8_t *rowp = src + (size_t)r * lds * ElemBytes<T>::value;
-    float v[kQuantU][16];
-    int c[kQuantU];
+  if (wid >= units) { if (stat) warp_amax_commit(stat, mx); return; }
+  const long long cnt = (units - wid + nwarps - 1) / nwarps;  // units of this warp: units - 1 - wid - i * nwarps, i < cnt
+  // (row, segment) of the warp's first unit and the step between its units
+  long long u0 = units - 1 - wid;
+  int r = (int)(u0 / upr), seg = (int)(u0 - (long long)r * upr);
+  const int dr = nwarps / upr, dseg = nwarps - dr * upr;
+  auto addr = [&](int rr, int ss) { return src + (size_t)rr * row_bytes + ((size_t)(ss * 32 + lane) * 16) * ElemBytes<T>::value; };
+  auto step = [&](int &rr, int &ss) { rr -= dr; ss -= dseg; if (ss < 0) { ss += upr; --rr; } };
+  int r1 = r, s1 = seg; step(r1, s1);
+  int r2 = r1, s2 = s1; step(r2, s2);
+  PackedBlock<T> p0 = load_block<T>(addr(r, seg), seg * 32 + lane < bpr);
+  PackedBlock<T> p1 = load_block<T>(addr(r1 < 0 ? 0 : r1, s1), cnt > 1 && s1 * 32 + lane < bpr);
+  for (long long i = 0; i < cnt; ++i) {
+    PackedBlock<T> p2 = load_block<T>(addr(r2 < 0 ? 0 : r2, s2), i + 2 < cnt && s2 * 32 + lane < bpr);
+    const int c = seg * 32 + lane;
+    const bool live = c < bpr;
+    float v[16];
+    unpack_block<T>(p0, v);
+    float bmax = 0.f;
 #pragma unroll
-    for (int k = 0; k < kQuantU; ++k) {
-      c[k] = (seg * kQuantU + k) * 32 + lane;
-      if (c[k] < bpr) load16<T>(rowp + (size_t)c[k] * 16 * ElemBytes<T>::value, v[k]);
-      else {
+    for (int k = 0; k < 16; ++k) bmax = fmaxf(bmax, fabsf(v[k]));
+    mx = fmaxf(mx, bmax);
+    const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), ue);
+    const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, ue), s_dec)), kFltMax);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[k][i] = 0.f;
-      }
+    for (int k = 0; k < 16; ++k) v[k] = __fmul_rn(v[k], inv);
+    const uint2 q = make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
+    if (live) *(uint2 *)(data + (size_t)r * ldq + 8 * c) = q;
+    if (words) {  // lanes 4 t .. 4 t + 3 hold the four scales of one 64-value group (bpr % 4 == 0: all live or none)
+      uint32_t w = live ? code << (8 * (lane & 3)) : 0u;
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+      if (live && (lane & 3) == 0) *(uint32_t *)(sc + sp.at(r, c)) = w;
+    } else if (live) {
+      sc[sp.at(r, c)] = (uint8_t)code;
     }
-#pragma unroll
-    for (int k = 0; k < kQuantU; ++k) {
-      const bool live = c[k] < bpr;
-      float bmax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[k][i]));
-      mx = fmaxf(mx, bmax);
-      const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), ue);
-      const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, ue), s_dec)), kFltMax);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[k][i] = __fmul_rn(v[k][i], inv);
-      const uint2 q = make_uint2(e2m1_pack8(v[k]), e2m1_pack8(v[k] + 8));
-      if (live) *(uint2 *)(data + (size_t)r * ldq + 8 * c[k]) = q;
-      if (words) {  // lanes 4 t .. 4 t + 3 hold the columns 4 t' .. 4 t' + 3 of one 64-value group (bpr % 4 == 0: all live or none)
-        uint32_t w = live ? code << (8 * (lane & 3)) : 0u;
-        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-        w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-        if (live && (lane & 3) == 0) *(uint32_t *)(sc + sp.at(r, c[k])) = w;
-      } else if (live) {
-        sc[sp.at(r, c[k])] = (uint8_t)code;
-      }
-    }
+    p0 = p1; p1 = p2;
+    r = r1; seg = s1; r1 = r2; s1 = s2; step(r2, s2);
   }
   if (stat) warp_amax_commit(stat, mx);
 }
@@ -492,7 +541,7 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
         float *p0 = ar ? ar : ac, *p1 = ar ? ac : nullptr;
         cudaMemsetAsync(p0, 0, 4, stream);
         if (p1 && p1 != p0) cudaMemsetAsync(p1, 0, 4, stream);
-        amax_kernel<T><<<grid_for(blocks * 8, 4), 256, 0, stream>>>(s, lds, rows, bpr, p0, p1);
+        amax_kernel<T><<<device_sms() * 4, 256, 0, stream>>>(s, lds, rows, bpr, p0, p1);
       }
     });
   }
@@ -504,7 +553,7 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
     by_dense(src->dtype, [&](auto tc) {
       constexpr int T = decltype(tc)::value;
       if (fast) {
-        quant_rows_kernel<T><<<grid_for(blocks * 16, 3), 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
+        quant_rows_kernel<T><<<device_sms() * 4, 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);  // 4 CTAs of <= 64 registers per SM: one wave
       } else {
         const int orows = col ? cols : rows, ocols = col ? rows : cols;
         const long long units = (long long)((orows + 15) / 16) * ((ocols + 15) / 16);
