@@ -53,6 +53,16 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return d;
 }
 
+// One step of one lane: 32 values of k (one 16-byte word of nibbles) for rows gq and gq + 8, two scale codes per row,
+// and -- for the lanes that carry an activation column -- the 32 matching activations.
+struct GemvStep {
+  uint4 w0, w1;
+  uint32_t sc0, sc1;
+  uint4 x[4];
+};
+
+// LAYOUT 0: plain operand, linear scales; 1: plain operand, swizzled scales; 2: image
+template <int LAYOUT>
 __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g) {
   __shared__ uint32_t lut[256];                       // scale code -> BF16 pair (sa * 2^(126 - Z), twice)
   __shared__ float part[kGemvWarps][16][8];
@@ -61,71 +71,74 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
   const int i0 = blockIdx.x * 16;
+  const int gm = g.m, gn = g.n, gk = g.k;
   const bool ue = g.A.ue != 0;
-  const int Z = ue ? 16 : 8;
   {
     const float s = scale_to_f32((uint32_t)tid, ue) * (ue ? 0x1p110f : 0x1p118f);  // exact: 4 significant bits
     const uint32_t h = __float_as_uint(s) >> 16;
     lut[tid] = h | (h << 16);
   }
-  if ((g.ex.mask & kExNorm) && warp < g.n) {
+  if ((g.ex.mask & kExNorm) && warp < gn) {
     const float s = warp_norm_scale(g.ex, warp, lane);
     if (lane == 0) colscale[warp] = s;
   }
   __syncthreads();
 
   // rows of this lane (clamped for the loads; rows past m are never stored)
-  const int r0 = min(i0 + gq, g.m - 1), r1 = min(i0 + gq + 8, g.m - 1);
-  const bool has_col = gq < g.n;
-  const uint16_t *xrow = g.x + (size_t)(has_col ? gq : 0) * g.ldx;
-  const ScalePos sp{g.A.sld};
+  const int r0 = min(i0 + gq, gm - 1), r1 = min(i0 + gq + 8, gm - 1);
+  const bool has_col = gq < gn;
+  const uint4 *xrow = (const uint4 *)(g.x + (size_t)(has_col ? gq : 0) * g.ldx);
   const uint8_t *a0p, *a1p, *s0p, *s1p;
-  if (!g.A.image) {
+  if (LAYOUT != 2) {
+    const ScalePos sp{g.A.sld};
     a0p = g.A.data + (size_t)r0 * (g.A.ld >> 1); a1p = g.A.data + (size_t)r1 * (g.A.ld >> 1);
     s0p = g.A.sc + sp.row(r0); s1p = g.A.sc + sp.row(r1);
   } else {
-    a0p = g.A.data + (size_t)(r0 >> 7) * g.A.ktiles * kImgTileBytes + (r0 & 127) * 128;
-    a1p = g.A.data + (size_t)(r1 >> 7) * g.A.ktiles * kImgTileBytes + (r1 & 127) * 128;
-    s0p = g.A.data + (size_t)(r0 >> 7) * g.A.ktiles * kImgTileBytes + kImgDataBytes + (r0 & 31) * 16 + ((r0 & 127) >> 5) * 4;
-    s1p = g.A.data + (size_t)(r1 >> 7) * g.A.ktiles * kImgTileBytes + kImgDataBytes + (r1 & 31) * 16 + ((r1 & 127) >> 5) * 4;
+    const size_t t0 = (size_t)(r0 >> 7) * g.A.ktiles * kImgTileBytes, t1 = (size_t)(r1 >> 7) * g.A.ktiles * kImgTileBytes;
+    a0p = g.A.data + t0 + (r0 & 127) * 128;
+    a1p = g.A.data + t1 + (r1 & 127) * 128;
+    s0p = g.A.data + t0 + kImgDataBytes + (r0 & 31) * 16 + ((r0 & 127) >> 5) * 4;
+    s1p = g.A.data + t1 + kImgDataBytes + (r1 & 31) * 16 + ((r1 & 127) >> 5) * 4;
   }
-
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int chunks = g.k >> 5;  // 32-value chunks; a step is 4 of them (one per lane of a quad)
+  const int chunks = gk >> 5;  // 32-value chunks; a step is 4 of them (one per lane of a quad)
   const int nsteps = (chunks + 3) >> 2;
-  for (int st = warp; st < nsteps; st += kGemvWarps) {
+
+  auto load_step = [&](int st) {
+    GemvStep v;
     const int c = 4 * st + q;          // this lane's chunk: k in [32 c, 32 c + 32)
     const bool in = c < chunks;
-    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-    uint32_t sc0 = 0, sc1 = 0;         // two scale codes per row (blocks 2 c, 2 c + 1)
+    v.w0 = v.w1 = make_uint4(0, 0, 0, 0);
+    v.sc0 = v.sc1 = 0;
     if (in) {
-      if (!g.A.image) {
-        w0 = __ldg((const uint4 *)(a0p + 16 * c));
-        w1 = __ldg((const uint4 *)(a1p + 16 * c));
-        sc0 = __ldg((const uint16_t *)(s0p + sp.col(2 * c)));
-        sc1 = __ldg((const uint16_t *)(s1p + sp.col(2 * c)));
-      } else {
+      size_t doff, soff;
+      if (LAYOUT == 0) { doff = 16 * (size_t)c; soff = 2 * (size_t)c; }
+      else if (LAYOUT == 1) { doff = 16 * (size_t)c; soff = (size_t)(c >> 1) * 512 + (c & 1) * 2; }
+      else {
         const size_t t = (size_t)(c >> 3) * kImgTileBytes;  // 256-k tile = 8 chunks
         const int cc = c & 7;
-        w0 = __ldg((const uint4 *)(a0p + t + 16 * cc));
-        w1 = __ldg((const uint4 *)(a1p + t + 16 * cc));
-        const int off = (cc >> 1) * 512 + (cc & 1) * 2;     // 64-k group, then block pair inside it
-        sc0 = __ldg((const uint16_t *)(s0p + t + off));
-        sc1 = __ldg((const uint16_t *)(s1p + t + off));
+        doff = t + 16 * cc; soff = t + (cc >> 1) * 512 + (cc & 1) * 2;
       }
+      v.w0 = __ldg((const uint4 *)(a0p + doff));
+      v.w1 = __ldg((const uint4 *)(a1p + doff));
+      v.sc0 = __ldg((const uint16_t *)(s0p + soff));
+      v.sc1 = __ldg((const uint16_t *)(s1p + soff));
     }
-    uint4 xv[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) xv[i] = (in && has_col) ? __ldg((const uint4 *)(xrow + 32 * c) + i) : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < 4; ++i) v.x[i] = (in && has_col) ? __ldg(xrow + 4 * c + i) : make_uint4(0, 0, 0, 0);
+    return v;
+  };
 
-    const uint32_t S0[2] = {lut[sc0 & 0xFF], lut[(sc0 >> 8) & 0xFF]}, S1[2] = {lut[sc1 & 0xFF], lut[(sc1 >> 8) & 0xFF]};
-    const uint32_t ww0[4] = {w0.x, w0.y, w0.z, w0.w}, ww1[4] = {w1.x, w1.y, w1.z, w1.w};
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int st = warp; st < nsteps; st += kGemvWarps) {
+    const GemvStep cur = load_step(st);
+    const uint32_t S0[2] = {lut[cur.sc0 & 0xFF], lut[(cur.sc0 >> 8) & 0xFF]}, S1[2] = {lut[cur.sc1 & 0xFF], lut[(cur.sc1 >> 8) & 0xFF]};
+    const uint32_t ww0[4] = {cur.w0.x, cur.w0.y, cur.w0.z, cur.w0.w}, ww1[4] = {cur.w1.x, cur.w1.y, cur.w1.z, cur.w1.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // word i: 8 values, k = 32 c + 8 i ..; block i / 2 of the chunk
       const uint32_t a = ww0[i], b = ww1[i], sa = S0[i >> 1], sb = S1[i >> 1];
       // B pairs (x[p], x[p + 4]) to match the decode's pairing
-      const uint32_t x04 = prmt(xv[i].x, xv[i].z, 0x5410), x15 = prmt(xv[i].x, xv[i].z, 0x7632);
-      const uint32_t x26 = prmt(xv[i].y, xv[i].w, 0x5410), x37 = prmt(xv[i].y, xv[i].w, 0x7632);
+      const uint32_t x04 = prmt(cur.x[i].x, cur.x[i].z, 0x5410), x15 = prmt(cur.x[i].x, cur.x[i].z, 0x7632);
+      const uint32_t x26 = prmt(cur.x[i].y, cur.x[i].w, 0x5410), x37 = prmt(cur.x[i].y, cur.x[i].w, 0x7632);
       mma_bf16_16816(acc, bf16x2_mul(decode_pair<0>(a), sa), bf16x2_mul(decode_pair<0>(b), sb), bf16x2_mul(decode_pair<1>(a), sa),
                      bf16x2_mul(decode_pair<1>(b), sb), x04, x15);
       mma_bf16_16816(acc, bf16x2_mul(decode_pair<2>(a), sa), bf16x2_mul(decode_pair<2>(b), sb), bf16x2_mul(decode_pair<3>(a), sa),
@@ -140,7 +153,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
   // ---- epilogue on the slice: thread t < 128 owns (row t % 16, column t / 16) ----
   const Epilogue &e = g.e;
   const int ri = tid & 15, cj = tid >> 4, i = i0 + ri;
-  const bool live = tid < 128 && i < g.m && cj < g.n;
+  const bool live = tid < 128 && i < gm && cj < gn;
   float v = 0.f, amax = 0.f;
   if (live) {
     float s = 0.f;
@@ -151,7 +164,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
     if (g.ex.mask & kExNorm) colp = __fmul_rn(colp, colscale[cj]);
     v = epi_value(e, i, cj, s, epi_scale(e, epi_row_part(e, i), colp));
   }
-  (void)Z;
   if (!(g.ex.mask & (kExSwiglu | kExOut2))) {
     if (live) { store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + i, v); amax = fabsf(v); }
   } else {
@@ -191,7 +203,10 @@ cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
   a.A = g.A;
   a.x = (const uint16_t *)g.B.data; a.ldx = g.B.ld;
   a.e = g.e; a.ex = g.x;
-  gemv_kernel<<<(g.m + 15) / 16, kGemvWarps * 32, 0, s>>>(a);
+  const int grid = (g.m + 15) / 16;
+  if (a.A.image) gemv_kernel<2><<<grid, kGemvWarps * 32, 0, s>>>(a);
+  else if (a.A.sld < 0) gemv_kernel<1><<<grid, kGemvWarps * 32, 0, s>>>(a);
+  else gemv_kernel<0><<<grid, kGemvWarps * 32, 0, s>>>(a);
   return cudaGetLastError();
 }
 

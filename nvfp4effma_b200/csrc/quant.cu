@@ -48,6 +48,24 @@ __device__ __forceinline__ uint32_t e4m3_encode(float d) {
 }
 __device__ __forceinline__ uint32_t scale_encode(float d, bool ue) { return ue ? f32_to_ue5m3_sw(d) : e4m3_encode(d); }
 
+// 16-byte read-only loads with an L2 eviction priority: the amax pass asks L2 to keep what it reads (evict_last), the
+// encode pass that follows releases it as it goes (evict_first).
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ldg16_hint(const uint4 *ptr, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr), "l"(policy));
+  return v;
+}
 // 16 consecutive dense values (16-byte aligned start) -> FP32
 template <int T>
 __device__ __forceinline__ void load16(const uint8_t *p, float v[16]) {
@@ -117,6 +135,7 @@ __global__ void __launch_bounds__(256, 4) amax_kernel(const uint8_t *__restrict_
   const long long units = (long long)rows * upr, wstride = (long long)gridDim.x * (blockDim.x >> 5);
   float m = 0.f;
   uint32_t pm = 0;
+  const uint64_t keep = l2_policy_evict_last();
   for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < units; u += wstride) {
     const int r = (int)(u / upr), seg = (int)(u - (long long)r * upr);
     const uint4 *rowp = (const uint4 *)(src + (size_t)r * lds * ElemBytes<T>::value) + seg * 256;
@@ -124,7 +143,7 @@ __global__ void __launch_bounds__(256, 4) amax_kernel(const uint8_t *__restrict_
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int c = k * 32 + lane;
-      w[k] = seg * 256 + c < wpr ? __ldg(rowp + c) : make_uint4(0, 0, 0, 0);
+      w[k] = seg * 256 + c < wpr ? ldg16_hint(rowp + c, keep) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -168,10 +187,10 @@ __global__ void __launch_bounds__(256) amax_rows_kernel(const uint8_t *__restric
 // the tail of the matrix is what L2 still holds.
 template <int T> struct PackedBlock { uint4 w[T == NVFP4A_FP32 ? 4 : 2]; };
 template <int T>
-__device__ __forceinline__ PackedBlock<T> load_block(const uint8_t *p, bool live) {
+__device__ __forceinline__ PackedBlock<T> load_block(const uint8_t *p, bool live, uint64_t policy) {
   PackedBlock<T> b;
 #pragma unroll
-  for (int q = 0; q < (T == NVFP4A_FP32 ? 4 : 2); ++q) b.w[q] = live ? __ldg((const uint4 *)p + q) : make_uint4(0, 0, 0, 0);
+  for (int q = 0; q < (T == NVFP4A_FP32 ? 4 : 2); ++q) b.w[q] = live ? ldg16_hint((const uint4 *)p + q, policy) : make_uint4(0, 0, 0, 0);
   return b;
 }
 template <int T>
@@ -199,59 +218,77 @@ __device__ __forceinline__ void unpack_block(const PackedBlock<T> &b, float v[16
     }
   }
 }
-template <int T>
-__global__ void __launch_bounds__(256, 4) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
+// One block: 16 values -> scale code and 16 nibbles.  1 / y is the correctly rounded reciprocal (rcp.rn), the same value
+// as the IEEE division 1 / y of the reference.
+template <bool UE>
+__device__ __forceinline__ uint2 quant_block16(float v[16], float enc6, float s_dec, uint32_t &code, float &bmax) {
+  bmax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) bmax = fmaxf(bmax, fabsf(v[k]));
+  code = UE ? f32_to_ue5m3_sw(fminf(__fmul_rn(bmax, enc6), kFltMax)) : e4m3_encode(fminf(__fmul_rn(bmax, enc6), kFltMax));
+  const float inv = fminf(__frcp_rn(__fmul_rn(UE ? ue5m3_to_f32(code) : e4m3_to_f32(code), s_dec)), kFltMax);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) v[k] = __fmul_rn(v[k], inv);
+  return make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
+}
+// Warps sit side by side along a row (64 blocks = 2 KiB of BF16 each: a lane owns blocks lane and lane + 32 of its
+// segment) and walk UP the matrix from its last rows, `rstep` rows per iteration, with the next iteration's loads in flight.
+template <int T, bool UE>
+__global__ void __launch_bounds__(256, 3) quant_rows_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *stat) {
   const int lane = threadIdx.x & 31;
-  const int upr = (bpr + 31) >> 5;                 // units (of 32 blocks) per row
-  const long long units = (long long)rows * upr;
+  const int upr = (bpr + 63) >> 6;                 // 64-block segments per row
   const int nwarps = gridDim.x * (blockDim.x >> 5), wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int wps = upr < nwarps ? upr : nwarps, rstep = nwarps / wps;
   const QGlobal G = make_global(o.g ? o.g[0] : 1.f, o.smax, o.amax_mode != 0);
   const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f), s_dec = G.s_dec;
   const ScalePos sp{o.sld};
   // 4-byte scale stores need 4-byte aligned words: always true in the swizzled layout, in the linear one only for an aligned base and row pitch
-  const bool ue = o.ue != 0, words = (bpr & 3) == 0 && (o.sld < 0 || ((o.sld & 3) == 0 && ((uintptr_t)o.sc & 3) == 0));
+  const bool words = (bpr & 3) == 0 && (o.sld < 0 || ((o.sld & 3) == 0 && ((uintptr_t)o.sc & 3) == 0));
   uint8_t *const data = o.data, *const sc = o.sc;
   const int ldq = o.ld >> 1;
   const size_t row_bytes = (size_t)lds * ElemBytes<T>::value;
+  constexpr int kBlockBytes = 16 * ElemBytes<T>::value;
+  const uint64_t drop = l2_policy_evict_first();
   float mx = 0.f;
-  if (wid >= units) { if (stat) warp_amax_commit(stat, mx); return; }
-  const long long cnt = (units - wid + nwarps - 1) / nwarps;  // units of this warp: units - 1 - wid - i * nwarps, i < cnt
-  // (row, segment) of the warp's first unit and the step between its units
-  long long u0 = units - 1 - wid;
-  int r = (int)(u0 / upr), seg = (int)(u0 - (long long)r * upr);
-  const int dr = nwarps / upr, dseg = nwarps - dr * upr;
-  auto addr = [&](int rr, int ss) { return src + (size_t)rr * row_bytes + ((size_t)(ss * 32 + lane) * 16) * ElemBytes<T>::value; };
-  auto step = [&](int &rr, int &ss) { rr -= dr; ss -= dseg; if (ss < 0) { ss += upr; --rr; } };
-  int r1 = r, s1 = seg; step(r1, s1);
-  int r2 = r1, s2 = s1; step(r2, s2);
-  PackedBlock<T> p0 = load_block<T>(addr(r, seg), seg * 32 + lane < bpr);
-  PackedBlock<T> p1 = load_block<T>(addr(r1 < 0 ? 0 : r1, s1), cnt > 1 && s1 * 32 + lane < bpr);
-  for (long long i = 0; i < cnt; ++i) {
-    PackedBlock<T> p2 = load_block<T>(addr(r2 < 0 ? 0 : r2, s2), i + 2 < cnt && s2 * 32 + lane < bpr);
-    const int c = seg * 32 + lane;
-    const bool live = c < bpr;
-    float v[16];
-    unpack_block<T>(p0, v);
-    float bmax = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) bmax = fmaxf(bmax, fabsf(v[k]));
-    mx = fmaxf(mx, bmax);
-    const uint32_t code = scale_encode(fminf(__fmul_rn(bmax, enc6), kFltMax), ue);
-    const float inv = fminf(__fdiv_rn(1.f, __fmul_rn(scale_to_f32(code, ue), s_dec)), kFltMax);
-#pragma unroll
-    for (int k = 0; k < 16; ++k) v[k] = __fmul_rn(v[k], inv);
-    const uint2 q = make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
-    if (live) *(uint2 *)(data + (size_t)r * ldq + 8 * c) = q;
-    if (words) {  // lanes 4 t .. 4 t + 3 hold the four scales of one 64-value group (bpr % 4 == 0: all live or none)
-      uint32_t w = live ? code << (8 * (lane & 3)) : 0u;
-      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-      if (live && (lane & 3) == 0) *(uint32_t *)(sc + sp.at(r, c)) = w;
-    } else if (live) {
-      sc[sp.at(r, c)] = (uint8_t)code;
+  if (wid < wps * rstep) {
+    for (int seg = wid % wps; seg < upr; seg += wps) {
+      const int c0 = seg * 64 + lane, c1 = c0 + 32;
+      const bool live0 = c0 < bpr, live1 = c1 < bpr;
+      const uint8_t *p = src + (size_t)c0 * kBlockBytes;
+      int r = rows - 1 - wid / wps;
+      PackedBlock<T> a0 = load_block<T>(p + (size_t)(r < 0 ? 0 : r) * row_bytes, live0 && r >= 0, drop);
+      PackedBlock<T> a1 = load_block<T>(p + (size_t)(r < 0 ? 0 : r) * row_bytes + 32 * kBlockBytes, live1 && r >= 0, drop);
+      for (; r >= 0; r -= rstep) {
+        const int rn = r - rstep;
+        const PackedBlock<T> n0 = load_block<T>(p + (size_t)(rn < 0 ? 0 : rn) * row_bytes, live0 && rn >= 0, drop);
+        const PackedBlock<T> n1 = load_block<T>(p + (size_t)(rn < 0 ? 0 : rn) * row_bytes + 32 * kBlockBytes, live1 && rn >= 0, drop);
+        float v[16], bmax;
+        uint32_t code0, code1;
+        unpack_block<T>(a0, v);
+        const uint2 q0 = quant_block16<UE>(v, enc6, s_dec, code0, bmax);
+        mx = fmaxf(mx, bmax);
+        unpack_block<T>(a1, v);
+        const uint2 q1 = quant_block16<UE>(v, enc6, s_dec, code1, bmax);
+        mx = fmaxf(mx, bmax);
+        uint8_t *drow = data + (size_t)r * ldq;
+        if (live0) __stcs((uint2 *)(drow + 8 * c0), q0);   // streaming stores: the output is not read again here
+        if (live1) __stcs((uint2 *)(drow + 8 * c1), q1);
+        if (words) {  // lanes 4 t .. 4 t + 3 hold the four scales of one 64-value group (bpr % 4 == 0: all live or none)
+          uint32_t w0 = live0 ? code0 << (8 * (lane & 3)) : 0u, w1 = live1 ? code1 << (8 * (lane & 3)) : 0u;
+          w0 |= __shfl_xor_sync(0xFFFFFFFFu, w0, 1); w1 |= __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
+          w0 |= __shfl_xor_sync(0xFFFFFFFFu, w0, 2); w1 |= __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
+          if ((lane & 3) == 0) {
+            const size_t rowpos = sp.row(r);
+            if (live0) *(uint32_t *)(sc + rowpos + sp.col(c0)) = w0;
+            if (live1) *(uint32_t *)(sc + rowpos + sp.col(c1)) = w1;
+          }
+        } else {
+          if (live0) sc[sp.at(r, c0)] = (uint8_t)code0;
+          if (live1) sc[sp.at(r, c1)] = (uint8_t)code1;
+        }
+        a0 = n0; a1 = n1;
+      }
     }
-    p0 = p1; p1 = p2;
-    r = r1; seg = s1; r1 = r2; s1 = s2; step(r2, s2);
   }
   if (stat) warp_amax_commit(stat, mx);
 }
@@ -553,7 +590,9 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
     by_dense(src->dtype, [&](auto tc) {
       constexpr int T = decltype(tc)::value;
       if (fast) {
-        quant_rows_kernel<T><<<device_sms() * 4, 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);  // 4 CTAs of <= 64 registers per SM: one wave
+        // one wave: 3 CTAs of 256 threads per SM
+        if (o.ue) quant_rows_kernel<T, true><<<device_sms() * 3, 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
+        else quant_rows_kernel<T, false><<<device_sms() * 3, 256, 0, stream>>>(s, lds, rows, bpr, o, d->amax);
       } else {
         const int orows = col ? cols : rows, ocols = col ? rows : cols;
         const long long units = (long long)((orows + 15) / 16) * ((ocols + 15) / 16);
