@@ -159,23 +159,30 @@ def _b_operand(x, x_scales, x_global, x_flags, x_smax, k):
 
 
 def linear(x, x_scales, x_global, x_flags, x_smax, w, w_scales, w_global, w_flags, w_smax, k, bias=None, out_dtype=None, out=None, alpha=1.0,
-           beta=0.0, amax_out=None, w_img=None):
-    """``alpha * x @ W^T + bias + beta * out``: ``nvfp4a_gemm``, or ``nvfp4a_gemv_tc`` when the weight's image is given and T <= 8."""
+           beta=0.0, amax_out=None, w_img=None, w_rows=None, swiglu=False):
+    """``alpha * x @ W^T + bias + beta * out``: ``nvfp4a_gemm``, or ``nvfp4a_gemv_tc`` when the weight's image is given and T <= 8.
+    ``swiglu``: W holds gate and up rows interleaved per 16-row slice (8 gate rows, then their 8 up rows); the result is
+    ``silu(gate) * up``, [T, N / 2], through the ``_ex`` entry points."""
     if beta != 0.0 and out is None:
         raise ValueError("beta != 0 accumulates into out, so out must be given")
     if out is not None and out_dtype is not None and out_dtype != out.dtype:
         raise ValueError(f"out_dtype {out_dtype} does not match out.dtype {out.dtype}")
-    _cuda(w, "weight")
+    _cuda(w if w is not None else w_img, "weight")
     if k % 64:
         raise ValueError(f"in_features (K = {k}) must be a multiple of 64")
-    N, T = w.shape[0], x.shape[0]
+    N, T = (w.shape[0] if w is not None else w_rows), x.shape[0]
+    dev = w.device if w is not None else w_img.device
     tB, ldb, keepB = _b_operand(x, x_scales, x_global, x_flags, x_smax, k)
     od = out.dtype if out is not None else (out_dtype or (x.dtype if x.dtype in _DENSE else torch.bfloat16))
+    NO = N // 2 if swiglu else N
     if out is None:
-        out = torch.empty((T, N), dtype=od, device=w.device)
-    elif out.dim() != 2 or tuple(out.shape) != (T, N) or out.stride(1) != 1:
-        raise ValueError(f"out must be a [T, N] = [{T}, {N}] tensor with contiguous rows")
-    amax = torch.zeros(1, dtype=torch.float32, device=w.device) if amax_out is not None else None
+        out = torch.empty((T, NO), dtype=od, device=dev)
+    elif out.dim() != 2 or tuple(out.shape) != (T, NO) or out.stride(1) != 1:
+        raise ValueError(f"out must be a [T, N] = [{T}, {NO}] tensor with contiguous rows")
+    amax = torch.zeros(1, dtype=torch.float32, device=dev) if amax_out is not None else None
+    ex = L.Epilogue()
+    ex.swiglu = 1
+    pe = ctypes.byref(ex)
     tD = L.Tensor(_ptr(out), _dense_code(od), None, 0, None, _ptr(amax), 0, 0)
     tbias = None
     if bias is not None:
@@ -187,12 +194,12 @@ def linear(x, x_scales, x_global, x_flags, x_smax, w, w_scales, w_global, w_flag
     pc, ldc = (ctypes.byref(tD), out.stride(0)) if beta != 0.0 else (None, 0)  # beta accumulates into out: C is D
     if w_img is not None and T <= 8:
         tA = L.Tensor(_ptr(w_img), L.NVFP4, None, 0, _ptr(w_global), None, w_flags, w_smax)
-        st = L.lib.nvfp4a_gemv_tc(N, T, k, alpha, ctypes.byref(tA), ctypes.byref(tB), ldb, beta, pc, ldc, ctypes.byref(tD), out.stride(0), pb,
-                                  _stream())
+        args = (N, T, k, alpha, ctypes.byref(tA), ctypes.byref(tB), ldb, beta, pc, ldc, ctypes.byref(tD), out.stride(0), pb)
+        st = L.lib.nvfp4a_gemv_tc_ex(*args, pe, _stream()) if swiglu else L.lib.nvfp4a_gemv_tc(*args, _stream())
     else:
         tA, lda, keepA = _fp4_operand(w, w_scales, w_global, w_flags, w_smax, k)
-        st = L.lib.nvfp4a_gemm(N, T, k, alpha, ctypes.byref(tA), lda, ctypes.byref(tB), ldb, beta, pc, ldc, ctypes.byref(tD), out.stride(0), pb,
-                               _stream())
+        args = (N, T, k, alpha, ctypes.byref(tA), lda, ctypes.byref(tB), ldb, beta, pc, ldc, ctypes.byref(tD), out.stride(0), pb)
+        st = L.lib.nvfp4a_gemm_ex(*args, pe, _stream()) if swiglu else L.lib.nvfp4a_gemm(*args, _stream())
     L.check(st)
     if amax_out is not None:
         torch.maximum(amax_out, amax, out=amax_out)
@@ -228,13 +235,13 @@ def _workspace(device):
 
 
 def linear_tc(x_img, x_dtype, x_global, x_flags, x_smax, T, w_img, w_global, w_flags, w_smax, N, K, bias=None, out_dtype=torch.bfloat16, out=None,
-              alpha=1.0, beta=0.0, amax_out=None):
-    """``nvfp4a_gemm_tc`` on images; x_dtype 0 NVFP4, 1 int8, 2 bfloat16."""
+              alpha=1.0, beta=0.0, amax_out=None, swiglu=False):
+    """``nvfp4a_gemm_tc`` on images; x_dtype 0 NVFP4, 1 int8, 2 bfloat16.  ``swiglu`` as in ``linear`` (``nvfp4a_gemm_tc_ex``)."""
     if beta != 0.0 and out is None:
         raise ValueError("beta != 0 accumulates into out, so out must be given")
     od = out.dtype if out is not None else out_dtype
     if out is None:
-        out = torch.empty((T, N), dtype=od, device=w_img.device)
+        out = torch.empty((T, N // 2 if swiglu else N), dtype=od, device=w_img.device)
     amax = torch.zeros(1, dtype=torch.float32, device=w_img.device) if amax_out is not None else None
     tA = L.Tensor(_ptr(w_img), L.NVFP4, None, 0, _ptr(w_global), None, w_flags, w_smax)
     bt = (L.NVFP4, L.INT8, L.BF16)[x_dtype]
@@ -245,8 +252,14 @@ def linear_tc(x_img, x_dtype, x_global, x_flags, x_smax, T, w_img, w_global, w_f
         bias = bias.contiguous()
         tbias = L.Tensor(_ptr(bias), _dense_code(bias.dtype), None, 0, None, None, 0, 0)
     pc, ldc = (ctypes.byref(tD), out.stride(0)) if beta != 0.0 else (None, 0)
-    L.check(L.lib.nvfp4a_gemm_tc(N, T, K, alpha, ctypes.byref(tA), ctypes.byref(tB), beta, pc, ldc, ctypes.byref(tD), out.stride(0),
-                                 ctypes.byref(tbias) if tbias is not None else None, _ptr(_workspace(w_img.device)), _stream()))
+    args = (N, T, K, alpha, ctypes.byref(tA), ctypes.byref(tB), beta, pc, ldc, ctypes.byref(tD), out.stride(0),
+            ctypes.byref(tbias) if tbias is not None else None)
+    if swiglu:
+        ex = L.Epilogue()
+        ex.swiglu = 1
+        L.check(L.lib.nvfp4a_gemm_tc_ex(*args, ctypes.byref(ex), _ptr(_workspace(w_img.device)), _stream()))
+    else:
+        L.check(L.lib.nvfp4a_gemm_tc(*args, _ptr(_workspace(w_img.device)), _stream()))
     if amax_out is not None:
         torch.maximum(amax_out, amax, out=amax_out)
     return out

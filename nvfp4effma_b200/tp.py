@@ -1,0 +1,142 @@
+"""Tensor-parallel NVFP4 linear layers: a weight's output rows are split over the GPUs of one node, every rank computes
+its rows of ``y = x @ W.T`` from the full (replicated) ``x``, and an NCCL all-gather over NVLink reassembles ``y``.
+
+The reference has no multi-GPU code; this module shards the units its API already treats as independent -- output rows
+(include/nvfp4effma.h:78-92 there: every D[i, j] depends on row i of A only).  Rows are cut on multiples of 128, so that a
+shard's swizzled block scales are a contiguous range of the tensor's (128-row tiles) and the 16-row gate / up slices of a
+SwiGLU weight stay whole.  A tensor is quantized BEFORE it is sharded: the per-tensor global is shared by all shards and a
+rank's outputs equal the corresponding outputs of the one-GPU call bit for bit.
+
+One process per GPU (``torch.distributed``).  The layout functions (``shard_bounds``, ``shard_rows``, ``gather_features``)
+work on tensors of any device and with any backend, which is how the host logic is tested on CPU ranks over gloo; the
+layers themselves run the CUDA library only.
+"""
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import _ops
+from .tensor import NVFP4Tensor
+
+ROW_ALIGN = 128
+
+
+def shard_bounds(rows: int, world: int, rank: int, align: int = ROW_ALIGN) -> Tuple[int, int]:
+    """Rows ``[start, stop)`` of rank ``rank``: equal shares that are multiples of ``align``."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} is outside a group of {world}")
+    if rows % (world * align):
+        raise ValueError(f"{rows} rows do not split into {world} equal shards of a multiple of {align} rows")
+    per = rows // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(w: NVFP4Tensor, world: int, rank: int) -> NVFP4Tensor:
+    """The rows of rank ``rank`` of a 2-D ``NVFP4Tensor`` as views of its buffers (no copy): nibbles, block scales (linear or
+    swizzled), per-row globals.  The per-tensor global is shared."""
+    if w.dim() != 2:
+        raise ValueError("only 2-D weights are sharded")
+    a, b = shard_bounds(w.shape[0], world, rank)
+    g = w.global_scale
+    if g is not None and g.numel() > 1:
+        g = g[a:b]
+    kw = dict(scale_max=w.scale_max, swizzled=w.swizzled, ue5m3=w.ue5m3, cols=w.cols, block=w.block)
+    scales = w.scales[a:b]  # swizzled: 128-row tiles are contiguous row ranges of the [rows, cols / 16] buffer
+    return NVFP4Tensor(w.data[a:b], scales, amax=g, **kw) if w.global_is_amax else NVFP4Tensor(w.data[a:b], scales, g, **kw)
+
+
+def gather_features(y_shard: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather of ``y_shard`` [T, n_local] along the feature dimension -> [T, world * n_local].
+
+    One ``all_gather_into_tensor`` yields the rank-major [world, T, n_local]; for T == 1 that already is the result, for
+    T > 1 one strided copy turns it into the token-major layout the next layer reads."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return y_shard
+    T, nl = y_shard.shape
+    y_shard = y_shard.contiguous()
+    stage = torch.empty((world * T, nl), dtype=y_shard.dtype, device=y_shard.device)  # rank-major: rank r holds rows [r * T, (r + 1) * T)
+    dist.all_gather_into_tensor(stage, y_shard, group=group)
+    if T == 1:
+        return stage.view(1, world * nl)
+    stage = stage.view(world, T, nl)
+    if out is None:
+        out = torch.empty((T, world * nl), dtype=y_shard.dtype, device=y_shard.device)
+    out.view(T, world, nl).copy_(stage.permute(1, 0, 2))
+    return out
+
+
+class TPLinear:
+    """One rank's part of ``y = x @ W.T + bias`` (optionally ``silu(gate) * up`` of interleaved gate / up rows).
+
+    Holds the image of its rows of ``W`` (built once), the shared global and its part of the bias.  ``forward`` takes the
+    replicated ``x`` [T, K] (bfloat16) and returns the full ``y``; ``forward_local`` returns this rank's columns only."""
+
+    def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False):
+        self.group = group
+        solo = replicate or not dist.is_initialized()  # replicate: the whole weight on this rank, no collective
+        self.world = 1 if solo else dist.get_world_size(group)
+        self.rank = 0 if solo else dist.get_rank(group)
+        if swiglu and weight.shape[0] % 16:
+            raise ValueError("a SwiGLU weight has a multiple of 16 rows")
+        self.out_features, self.in_features = weight.shape[0] // (2 if swiglu else 1), weight.shape[1]
+        self.swiglu = swiglu
+        shard = shard_rows(weight, self.world, self.rank)
+        d, s, g, f, smax, k = shard._flat()
+        self.rows = d.shape[0]
+        self.global_scale, self.flags, self.scale_max = g, f, smax
+        self.image = _ops.tc_image(0, d, s.view(torch.uint8), f, k)
+        a, b = shard_bounds(weight.shape[0], self.world, self.rank)
+        self.bias = bias[a:b].contiguous() if bias is not None else None
+
+    def forward_local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
+            raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
+        T = x.shape[0]
+        if T <= 8:
+            return _ops.linear(x, None, None, 0, 0, None, None, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias,
+                               torch.bfloat16, out, w_img=self.image, w_rows=self.rows, swiglu=self.swiglu)
+        xi = _ops.tc_image(1, x, None, 0, self.in_features)
+        return _ops.linear_tc(xi, 2, None, 0, 0, T, self.image, self.global_scale, self.flags, self.scale_max, self.rows, self.in_features,
+                              self.bias, torch.bfloat16, out, swiglu=self.swiglu)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.forward_local(x)
+        return y if self.world == 1 else gather_features(y, self.group)
+
+    __call__ = forward
+
+
+class TPDecoderLinears:
+    """The linear layers of a Llama-style decoder stack under tensor parallelism: per layer QKV (hidden -> qkv), O (hidden ->
+    hidden), gate / up with SwiGLU (hidden -> 2 x intermediate, interleaved per 16 rows) and down (intermediate -> hidden).
+    Attention, norms and residuals are not part of this path: O reads the first ``hidden`` features of the QKV output."""
+
+    def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
+                 device="cuda", std: float = 0.02, replicate: bool = False):
+        self.hidden, self.layers = hidden, []
+        from . import quantize
+        for layer in range(layers):
+            mods = []
+            for j, (rows, cols, glu) in enumerate(((qkv, hidden, False), (hidden, hidden, False), (2 * intermediate, hidden, True),
+                                                   (hidden, intermediate, False))):
+                gen = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 4 + j)  # the same weights on every rank
+                w = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
+                amax = w.abs().amax().float().reshape(1)
+                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate))
+                del w
+            self.layers.append(mods)
+
+    def weight_bytes_local(self) -> int:
+        return sum(m.image.numel() for layer in self.layers for m in layer)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        for qkv, o, gate_up, down in self.layers:
+            a = qkv(h)[:, :self.hidden]
+            h = down(gate_up(o(a)))
+        return h
+
+    __call__ = forward

@@ -1,0 +1,84 @@
+"""Tensor-parallel layers on the GPU: one rank against the plain linear call, and (with two or more GPUs) two NCCL ranks
+against the unsharded layers, bit for bit."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def rand(shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to("cuda").to(dtype)
+
+
+@pytest.mark.parametrize("T", [1, 4, 8, 40])
+def test_one_rank_layer_equals_linear(T):
+    import nvfp4effma_b200 as nf
+    from nvfp4effma_b200.tp import TPLinear
+    w = nf.quantize(rand((256, 320), seed=1), torch.tensor([0.002], device="cuda"))
+    bias = rand((256,), torch.bfloat16, seed=2)
+    x = rand((T, 320), torch.bfloat16, seed=3)
+    y = TPLinear(w, bias)(x)
+    ref = nf.linear(x, nf.TCWeight(w, "exact"), bias)
+    assert y.shape == (T, 256) and torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("T", [1, 8, 33])
+def test_swiglu_layer(T):
+    import nvfp4effma_b200 as nf
+    from nvfp4effma_b200.tp import TPLinear
+    w = nf.quantize(rand((512, 256), seed=4, scale=0.05), torch.tensor([0.0002], device="cuda"))
+    x = rand((T, 256), torch.bfloat16, seed=5)
+    y = TPLinear(w, swiglu=True)(x)
+    z = nf.linear(x, w, act="exact", out_dtype=torch.float32).reshape(T, 32, 2, 8)  # slices of 8 gate rows, 8 up rows
+    want = (torch.nn.functional.silu(z[:, :, 0]) * z[:, :, 1]).reshape(T, 256)
+    assert y.shape == (T, 256)
+    assert torch.allclose(y.float(), want, rtol=2 ** -7, atol=1e-6)
+
+
+def test_decoder_stack_runs_decode_and_prefill():
+    from nvfp4effma_b200.tp import TPDecoderLinears
+    stack = TPDecoderLinears(layers=2, hidden=256, intermediate=512, qkv=384, std=0.06)
+    for T in (1, 8, 64):
+        h = stack(rand((T, 256), torch.bfloat16, seed=6))
+        assert h.shape == (T, 256) and bool(torch.isfinite(h.float()).all()) and float(h.float().abs().max()) > 0
+
+
+RANK_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["NVB_ROOT"])
+rank = int(os.environ["RANK"]); torch.cuda.set_device(rank)
+dist.init_process_group("nccl", rank=rank, world_size=int(os.environ["WORLD_SIZE"]), device_id=torch.device("cuda", rank))
+from nvfp4effma_b200.tp import TPDecoderLinears
+kw = dict(layers=2, hidden=256, intermediate=512, qkv=512, std=0.06)
+tp, solo = TPDecoderLinears(**kw), TPDecoderLinears(replicate=True, **kw)
+ok = True
+for T in (1, 5, 48):
+    g = torch.Generator(device="cpu").manual_seed(T)
+    x = torch.randn((T, 256), generator=g).cuda().bfloat16()
+    ok = ok and torch.equal(tp(x), solo(x))
+torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
+print("RANK_OK" if ok else "RANK_MISMATCH", flush=True)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_equal_one_rank_bit_for_bit(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "rank.py"
+    script.write_text(RANK_SCRIPT)
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NVB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("RANK_OK" in o for o in outs), outs
