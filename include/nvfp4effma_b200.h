@@ -17,7 +17,8 @@ nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long
 
 /* Kernel route of the GEMM entry points (no counterpart in the reference, which picks kernels from per-architecture
  * tables): 0 = automatic (GEMV for n <= 8, tcgen05 GEMMs where the operand formats have a tensor-core form, CUDA cores
- * otherwise), 1 = always the CUDA-core kernel, whose results are bit-identical to the reference's tiled kernels.
+ * otherwise), 1 = always the CUDA-core kernel, whose results are bit-identical to the reference's tiled kernels, 2 = automatic
+ * but with the mma.sync GEMV in place of the FP4 tensor-core GEMV (n <= 2).
  * Process-wide, not thread-safe; meant for tests and debugging.  Returns the previous value. */
 int nvfp4a_b200_set_route(int route);
 
@@ -32,6 +33,15 @@ nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
  * epilogue overlaps the next tile) or 256 (one accumulator, less shared-memory traffic per flop).  Tuning / test aid, no
  * counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_tile_n(int bn);
+
+/* The kernel the calling thread's last GEMM / GEMV call launched: 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core GEMV, 4 W4A4
+ * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM; 0 before any call.  Test aid, no counterpart in the reference. */
+int nvfp4a_b200_last_route(void);
+
+/* Pins the number of k ranges (CTAs per cluster) of the FP4 tensor-core GEMV: 0 = by problem size, else 1, 2, 4 or 8; a
+ * value the problem cannot use (shared memory for the activation digit planes, k / 256) makes that GEMV step aside for the
+ * mma.sync one.  A pinned value also lifts the size threshold below which the automatic choice prefers the mma.sync GEMV.  Tuning / test aid, no counterpart in the reference.  Returns 0, or -1 for another value. */
+int nvfp4a_b200_set_gemv_splits(int splits);
 
 #ifdef __cplusplus
 }

@@ -73,6 +73,8 @@ _PROTOS = {
     "nvfp4a_b200_set_route": (_i, [_i]),
     "nvfp4a_b200_kernel_status": (_i, [C.POINTER(C.c_uint), _i]),
     "nvfp4a_b200_set_tile_n": (_i, [_i]),
+    "nvfp4a_b200_set_gemv_splits": (_i, [_i]),
+    "nvfp4a_b200_last_route": (_i, []),
 }
 EXPORTS = tuple(_PROTOS)
 

@@ -20,8 +20,8 @@ static bool blocked_t(const nvfp4a_tensor *t) { return t->dtype == NVFP4A_NVFP4 
 static bool aligned(const void *p, unsigned a) { return ((uintptr_t)p & (a - 1)) == 0; }
 static bool dense_dt(nvfp4a_dtype t) { return t >= NVFP4A_BF16 && t <= NVFP4A_FP32; }
 
-// Route override (nvfp4a_b200_set_route): 0 = automatic, 1 = always the exact CUDA-core kernel.  The environment variable
-// NVFP4A_B200_ROUTE=generic sets the initial value.
+// Route override (nvfp4a_b200_set_route): 0 = automatic, 1 = always the exact CUDA-core kernel, 2 = automatic without the
+// FP4 tensor-core GEMV.  The environment variable NVFP4A_B200_ROUTE=generic sets the initial value to 1.
 static int g_route = -1;
 static int forced_route() {
   if (g_route < 0) {
@@ -87,14 +87,19 @@ static nvfp4a_status check_epilogue_operands(const char *fn, int m, float beta, 
   return NVFP4A_OK;
 }
 
+// kernel the last GEMM call of this thread launched (nvfp4a_b200_last_route): 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core
+// GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM
+static thread_local int g_last_route = 0;
+
 static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t stream) {
   cudaError_t err;
   const bool gemv = g.k == 0 || g.n <= kGemvMaxN;
-  if (forced_route()) err = launch_gemm_generic(g, stream);
-  else if (gemv && gemv_supports(g)) err = launch_gemv(g, stream);
-  else if (!gemv && gemm_w4a4_supports(g)) err = launch_gemm_w4a4(g, stream);
-  else if (!gemv && gemm_w4a16_supports(g)) err = launch_gemm_w4a16(g, stream);
-  else err = launch_gemm_generic(g, stream);
+  if (forced_route() == 1) { g_last_route = 1; err = launch_gemm_generic(g, stream); }
+  else if (gemv && g.k > 0 && forced_route() != 2 && gemv_fp4_supports(g)) { g_last_route = 3; err = launch_gemv_fp4(g, stream); }
+  else if (gemv && gemv_supports(g)) { g_last_route = 2; err = launch_gemv(g, stream); }
+  else if (!gemv && gemm_w4a4_supports(g)) { g_last_route = 4; err = launch_gemm_w4a4(g, stream); }
+  else if (!gemv && gemm_w4a16_supports(g)) { g_last_route = 5; err = launch_gemm_w4a16(g, stream); }
+  else { g_last_route = 1; err = launch_gemm_generic(g, stream); }
   return cuda_fail(err, fn);
 }
 
@@ -266,8 +271,16 @@ using namespace nvb;
 
 extern "C" int nvfp4a_b200_set_route(int route) {
   const int old = forced_route();
-  g_route = route ? 1 : 0;
+  g_route = route == 2 ? 2 : (route ? 1 : 0);
   return old;
+}
+
+extern "C" int nvfp4a_b200_last_route(void) { return g_last_route; }
+
+extern "C" int nvfp4a_b200_set_gemv_splits(int splits) {
+  if (splits < 0 || splits > 8 || (splits & (splits - 1))) return -1;
+  set_gemv_fp4_splits(splits);
+  return 0;
 }
 
 extern "C" nvfp4a_status nvfp4a_gemm(int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb, float beta,

@@ -96,7 +96,7 @@ class NVFP4Tensor:
 
     @classmethod
     def from_float(cls, x: torch.Tensor, global_scale: Optional[torch.Tensor] = None, **recipe) -> "NVFP4Tensor":
-        from . import quantize
+        from .api import quantize
         return quantize(x, global_scale, **recipe)
 
     @classmethod
@@ -127,7 +127,7 @@ class NVFP4Tensor:
         return row
 
     def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-        from . import dequantize
+        from .api import dequantize
         return dequantize(self, dtype)
 
     def _like(self, data, scales, swizzled, cols, block):
@@ -207,7 +207,7 @@ class Int8Tensor:
 
     @classmethod
     def from_float(cls, x: torch.Tensor) -> "Int8Tensor":
-        from . import quantize_int8
+        from .api import quantize_int8
         return quantize_int8(x)
 
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -277,7 +277,7 @@ class NVFP4Linear(torch.nn.Module):
         return NVFP4Tensor(self.weight, self.weight_scale, self.weight_scale_2)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        from . import linear
+        from .api import linear
         bias = self.bias if self.bias is None or self.bias.dtype == x.dtype else self.bias.to(x.dtype)
         return linear(x, self.nvfp4_weight(), bias, act=self.act)
 

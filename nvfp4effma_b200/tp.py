@@ -118,7 +118,7 @@ class TPDecoderLinears:
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
                  device="cuda", std: float = 0.02, replicate: bool = False):
         self.hidden, self.layers = hidden, []
-        from . import quantize
+        from .api import quantize
         for layer in range(layers):
             mods = []
             for j, (rows, cols, glu) in enumerate(((qkv, hidden, False), (hidden, hidden, False), (2 * intermediate, hidden, True),

@@ -1,0 +1,99 @@
+"""The FP4 tensor-core GEMV (n <= 2 BF16 activation vectors, weights fed to tcgen05 as stored, activations as FP4 digit
+planes) against the CPU oracle: plain epilogue within the FP32-accumulation bound, extended epilogue bit for bit given the
+kernel's own accumulators -- the checks of test_gemm_gpu / test_epilogue_gpu, with the kernel pinned by
+nvfp4a_b200_set_gemv_splits and its use confirmed by nvfp4a_b200_last_route."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from nvfp4effma_b200 import _lib as L
+from test_epilogue_gpu import run_case
+from test_gemm_gpu import AM, OUTS, PR, SW, Case, build_case, check_bound, kernel_status, oracle_case, run_gemm, run_tc
+from util import DevFp4, dev, host, stream, tensor
+
+pytestmark = pytest.mark.gpu
+FP4_GEMV = 3
+
+
+@pytest.fixture
+def pin():
+    def set_splits(s):
+        assert L.lib.nvfp4a_b200_set_gemv_splits(s) == 0
+    yield set_splits
+    L.lib.nvfp4a_b200_set_gemv_splits(0)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_image_operand_all_splits(pin, splits):
+    pin(splits)
+    sizes = [(77, 1, 2048), (300, 2, 2048), (256, 1, 4096), (515, 2, 2048), (1100, 1, 2304), (4096, 2, 2048)]
+    for i, (m, n, k) in enumerate(sizes):
+        for fa in (0, AM | PR):
+            c = Case(m, n, k, L.BF16, OUTS[i % 3], -1 if i % 4 == 1 else OUTS[i % 3], L.BF16 if i % 2 else -1, 1.25 if i % 2 else 1.0,
+                     1.0 if i % 4 == 1 else 0.0, fa=fa)
+            h = build_case(c, 900 + i)
+            exp = oracle_case(c, h, want_ref=True)
+            got, amax = run_tc(c, h, gemv=True)
+            assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV, c
+            check_bound(c, h, got, amax, exp)
+    assert kernel_status() == 0
+
+
+def test_plain_operand_with_swizzled_scales(pin):
+    pin(2)
+    for i, (m, n, k) in enumerate([(200, 1, 512), (513, 2, 1024), (2048, 1, 4096)]):
+        c = Case(m, n, k, L.BF16, OUTS[i % 3], OUTS[i % 3], L.FP32, 0.5, 0.0, fa=SW | (AM if i else 0))
+        h = build_case(c, 950 + i)
+        exp = oracle_case(c, h, want_ref=True)
+        got, amax = run_gemm(c, h)
+        assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV, c
+        check_bound(c, h, got, amax, exp)
+    # linear scales are left to the mma.sync GEMV
+    c = Case(200, 1, 512, L.BF16, L.BF16, L.BF16, -1, 1.0, 0.0)
+    run_gemm(c, build_case(c, 960))
+    assert L.lib.nvfp4a_b200_last_route() == 2
+    assert kernel_status() == 0
+
+
+def test_automatic_route_by_size():
+    c = Case(300, 1, 2048, L.BF16, L.BF16, L.BF16, -1, 1.0, 0.0, fa=SW)
+    run_gemm(c, build_case(c, 961))
+    assert L.lib.nvfp4a_b200_last_route() == 2          # small: the mma.sync GEMV
+    c = Case(8192, 1, 8192, L.BF16, L.BF16, L.BF16, -1, 1.0, 0.0, fa=SW)
+    h = build_case(c, 962)
+    exp = oracle_case(c, h, want_ref=True)
+    got, amax = run_gemm(c, h)
+    assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV   # 38 MB of weights
+    check_bound(c, h, got, amax, exp)
+
+
+@pytest.mark.parametrize("spread", [0, 12, 23])
+def test_activations_with_a_wide_dynamic_range(pin, spread):
+    """|x| spread over 2^-spread .. 1 (and exact zeros): up to 2^-24 of the largest element the digit planes hold every bit."""
+    pin(2)
+    m, n, k = 384, 2, 2048
+    c = Case(m, n, k, L.BF16, L.FP32, L.FP32, -1, 1.0, 0.0, fa=SW)
+    h = build_case(c, 970 + spread)
+    rng = np.random.default_rng(spread)
+    x = rng.standard_normal(h["ldb"] * n).astype(np.float32) * np.exp2(-rng.integers(0, spread + 1, h["ldb"] * n)).astype(np.float32)
+    x[rng.random(x.size) < 0.1] = 0.0
+    h["B"] = O.Dense(L.BF16, O.from_f32(x, L.BF16), h["ldb"])
+    exp = oracle_case(c, h, want_ref=True)
+    got, amax = run_gemm(c, h)
+    assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
+    check_bound(c, h, got, amax, exp)
+
+
+def test_extended_epilogue(pin):
+    pin(2)
+    v = 0
+    for (m, n, k) in [(64, 1, 512), (1024, 1, 1024), (528, 2, 2304), (4096, 2, 1024)]:
+        for mask in range(1, 6):
+            glu = bool(mask & 2)
+            run_case(m, n, k, L.BF16, L.FP32 if v % 2 else L.BF16, mask, (not glu) and v % 3 == 1, (not glu) and v % 4 == 2, True)
+            assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
+            v += 1
+    assert kernel_status() == 0
