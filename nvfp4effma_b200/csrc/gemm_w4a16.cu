@@ -1,5 +1,412 @@
+// NVFP4 weights x BF16 activations (W4A16) GEMM on the 5th-generation tensor cores: tcgen05.mma kind::f16 (BF16 in, FP32
+// accumulators in tensor memory) on weights expanded to exact BF16 in shared memory.
+//
+// An NVFP4 value times its block scale has at most 2 + 4 significant bits, so e2m1 * scale is exact in BF16; the tensor
+// cores then form exact products with the BF16 activations and accumulate in FP32 -- the reference's "exact" W4A16
+// definition (include/nvfp4effma.h:82-92 there) up to the order of the FP32 additions, like its own tensor-core path.
+//
+// Tile: 128 weight rows (MMA M) x BN tokens (MMA N) x 64 values of k per stage; a stage in shared memory is
+// [A 128 rows x 128 B | B BN rows x 128 B], both K-major with the 128-byte swizzle.
+//   warp 0      TMA producer of the activation tiles (2-D tensor map over B, no multicast)
+//   warp 1      MMA issuer (4 x K16 per stage), owner of the tensor memory: 2 accumulators of BN columns
+//   warps 2-5   epilogue, one 32-lane quadrant each: plain or extended (RMSNorm column scale, SwiGLU, second output + sums
+//               of squares), D through a shared-memory staging tile and TMA stores when its layout allows
+//   warps 6-13  weight expansion: each thread owns half a row of the stage (32 nibbles + 2 scale bytes, fetched from
+//               global memory two stages ahead), decodes them with shifts and masks to BF16 pairs (value * 2^-126, the
+//               subnormal trick), multiplies by the block scale in BF16 (exact) and stores 64 bytes into the swizzled
+//               A tile.  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for E4M3, 16 for
+//               UE5M3 scales) and the accumulator is multiplied by 2^Z in the epilogue.
+// Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
 #include "operands.cuh"
+#include "sm100.cuh"
+
 namespace nvb {
-bool gemm_w4a16_supports(const GemmArgs &) { return false; }
-cudaError_t launch_gemm_w4a16(const GemmArgs &, cudaStream_t) { return cudaErrorNotSupported; }
+
+using namespace sm100;
+
+namespace {
+
+struct W4A16Args {
+  int m, n, k;
+  Fp4Operand A;
+  Epilogue e;
+  EpilogueEx x;
+  unsigned *status;
+  int d_tma;     // the main output goes through the staging tile and TMA stores
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kABytes = 128 * 128, kBBytes = BN * 128, kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingBytes = 8192;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + 1024 /* scale table */ + BN * 4 /* column scales */ + 256;
+};
+
+constexpr int kThreads = 448, kConvWarps = 8;
+constexpr unsigned kStWaitFullA = 0x301, kStWaitFullB = 0x302, kStWaitEmpty = 0x303, kStWaitTmemFull = 0x304, kStWaitTmemEmpty = 0x305,
+                   kStWaitConv = 0x306;
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// nibbles p and p + 4 of w -> BF16 pair (low half: nibble p), each value * 2^-126: magnitude bits to [6, 9), sign to 15
+template <int P>
+__device__ __forceinline__ uint32_t decode_pair(uint32_t w) {
+  const uint32_t mag = (P < 2 ? w << (6 - 4 * P) : w >> (4 * P - 6)) & 0x01C001C0u;
+  const uint32_t sgn = (w << (12 - 4 * P)) & 0x80008000u;
+  return mag | sgn;
+}
+
+// what a conversion thread fetches for one stage: 32 nibbles and the two scale bytes of its half row
+struct RawHalfRow {
+  uint4 w;
+  uint32_t sc;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d, const W4A16Args g) {
+  using C = Cfg<BN>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t *staging = smem + kStages * C::kStageBytes;
+  uint32_t *lut = (uint32_t *)(staging + C::kStagingBytes);      // scale code -> BF16 pair (sa * 2^(126 - Z), twice)
+  float *colscale = (float *)(lut + 256);                           // RMSNorm column scales of the current token tile
+  uint64_t *bars = (uint64_t *)(colscale + BN);
+  uint64_t *full_a = bars, *full_b = bars + kStages, *empty = bars + 2 * kStages, *tmem_full = bars + 3 * kStages, *tmem_empty = tmem_full + 2;
+  uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gm = g.m, gn = g.n, gk = g.k;
+  const int tiles_m = (gm + 127) / 128, tiles_n = (gn + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int nk = gk / 64;
+  const bool ue = g.A.ue != 0;
+  unsigned *const status_word = g.status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kConvWarps); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_b);
+  }
+  if (threadIdx.x < 256) {
+    const float s = scale_to_f32((uint32_t)threadIdx.x, ue) * (ue ? 0x1p110f : 0x1p118f);  // exact: 4 significant bits
+    const uint32_t h = __float_as_uint(s) >> 16;
+    lut[threadIdx.x] = h | (h << 16);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+    if (*abort_flag) return false;
+    if (mbar_wait(bar, parity)) return true;
+    *abort_flag = 1;
+    atomicCAS(status_word, 0u, code);
+    return false;
+  };
+
+  if (warp == 0) {
+    // ---------------- producer: activation tiles ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int tn = t / tiles_m;
+        for (int ks = 0; ks < nk; ++ks, ++it) {
+          const int s = it % kStages;
+          if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty)) goto done;
+          mbar_arrive_expect_tx(&full_b[s], C::kBBytes);
+          tma_load_2d(smem + (size_t)s * C::kStageBytes + C::kABytes, &tmap_b, ks * 128, tn * BN, &full_b[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(128, BN, 1);
+      uint32_t it = 0, tile_i = 0;
+      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+        const int acc = tile_i & 1;
+        if (!wait(&tmem_empty[acc], ((tile_i >> 1) & 1) ^ 1, kStWaitTmemEmpty)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int ks = 0; ks < nk; ++ks, ++it) {
+          const int s = it % kStages;
+          if (!wait(&full_a[s], (it / kStages) & 1, kStWaitFullA)) goto done;
+          if (!wait(&full_b[s], (it / kStages) & 1, kStWaitFullB)) goto done;
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + (size_t)s * C::kStageBytes);
+          const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sA + C::kABytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_f16(d_tmem, da + 2 * j, db + 2 * j, idesc, (ks | j) != 0);  // K = 16 per instruction: 32 bytes along the row
+          tc_commit(&empty[s]);
+        }
+        tc_commit(&tmem_full[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue ----------------
+    const int quad = warp & 3;
+    const float *const ga = g.e.ga;
+    const int ga_stride = g.e.ga_stride;
+    const float gf = g.e.gf, alpha = g.e.alpha, beta = g.e.beta;
+    const void *const cptr = g.e.c, *const biasptr = g.e.bias;
+    const int ldc = g.e.ldc, c_dtype = g.e.c_dtype, bias_dtype = g.e.bias_dtype;
+    uint8_t *const dptr = (uint8_t *)g.e.d;
+    const int ldd = g.e.ldd, d_dtype = g.e.d_dtype;
+    float *const amax_out = g.e.amax;
+    const int mask = g.x.mask;
+    const float *const norm_parts = g.x.norm_parts;
+    const int norm_nparts = g.x.norm_nparts, norm_ld = g.x.norm_ld;
+    const float norm_inv_n = g.x.norm_inv_n, norm_eps = g.x.norm_eps;
+    uint8_t *const d2ptr = (uint8_t *)g.x.d2;
+    const int d2_dtype = g.x.d2_dtype, ldd2 = g.x.ldd2, w2_dtype = g.x.w2_dtype, ld_sq = g.x.ld_sq;
+    const void *const w2ptr = g.x.w2;
+    float *const sqptr = g.x.sq;
+    const bool d_tma = g.d_tma;
+    const int esz = dense_bytes(d_dtype);
+    const int cw = esz == 2 ? 32 : 16;
+    const bool leader = warp == 2 && lane == 0;
+    const float zf = ue ? 65536.f : 256.f;
+    float amax = 0.f;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+      const int tm = t % tiles_m, tn = t / tiles_m, acc = tile_i & 1;
+      const int i = tm * 128 + quad * 32 + lane;
+      const bool row_ok = i < gm;
+      const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
+      const float bias = (row_ok && biasptr) ? load_dense(bias_dtype, biasptr, i) : 0.f;
+      const float w2 = (row_ok && (mask & kExOut2)) ? load_dense(w2_dtype, w2ptr, i) : 0.f;
+      const float s_plain = __fmul_rn(rowp, gf);   // ((alpha gA) * 1) * gf: B is dense, its column part is 1
+      if (mask & kExNorm) {  // column scales of this token tile (the previous tile's are no longer in use: see the barrier below)
+        named_barrier(1, 128);
+        for (int jj = quad; jj < BN; jj += 4) {
+          const int j = tn * BN + jj;
+          float s = 0.f;
+          if (j < gn) {
+            const float *p = norm_parts + (size_t)j * norm_ld;
+            for (int q = lane; q < norm_nparts; q += 32) s = __fadd_rn(s, __ldcg(p + q));
+          }
+#pragma unroll
+          for (int o = 16; o; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, o));
+          if (lane == 0) colscale[jj] = __frsqrt_rn(__fadd_rn(__fmul_rn(s, norm_inv_n), norm_eps));
+        }
+      }
+      if (!wait(&tmem_full[acc], (tile_i >> 1) & 1, kStWaitTmemFull)) *abort_flag = 1;
+      named_barrier(1, 128);   // the four epilogue warps go on together or not at all
+      if (*abort_flag) goto done;
+      tc_fence_after();
+      const int nchunks = min(BN / 32, (gn - tn * BN + 31) / 32);
+      for (int c = 0; c < nchunks; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (c == nchunks - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+        const int j0 = tn * BN + c * 32;
+        const int nvalid = min(32, gn - j0);
+        // values before the output rounding, kept in r[] as FP32 bits
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const float a = __fmul_rn(__uint_as_float(r[jj]), zf);
+          const float s = (mask & kExNorm) ? __fmul_rn(__fmul_rn(rowp, colscale[c * 32 + jj]), gf) : s_plain;
+          float v = __fmul_rn(a, s);
+          if (biasptr) v = __fadd_rn(v, bias);
+          if (beta != 0.f && row_ok && jj < nvalid) v = __fmaf_rn(beta, load_dense(c_dtype, cptr, (size_t)(j0 + jj) * ldc + i), v);
+          r[jj] = __float_as_uint(v);
+        }
+        if (mask & kExOut2) {  // second output v * w2[i] and the slice's sum of squares (rows 16 q .. 16 q + 15 in ascending order)
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const float v = __uint_as_float(r[jj]);
+            if (row_ok && jj < nvalid) store_dense(d2_dtype, d2ptr, (size_t)(j0 + jj) * ldd2 + i, __fmul_rn(v, w2));
+            const float vv = __fmul_rn(v, v);
+            float sq = 0.f;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) sq = __fadd_rn(sq, __shfl_sync(0xFFFFFFFFu, vv, (lane & 16) + q));
+            if (row_ok && !(lane & 15) && jj < nvalid) sqptr[(size_t)(j0 + jj) * ld_sq + (i >> 4)] = sq;
+          }
+        }
+        if (mask & kExSwiglu) {  // rows 16 q + r (gate) and 16 q + 8 + r (up) -> output row 8 q + r; plain stores
+          const int io = (i >> 4) * 8 + (i & 7);
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const float v = __uint_as_float(r[jj]);
+            const float up = __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+            if (row_ok && !(lane & 8) && jj < nvalid) {
+              const float h = silu_mul(v, up);
+              amax = fmaxf(amax, fabsf(h));
+              store_dense(d_dtype, dptr, (size_t)(j0 + jj) * ldd + io, h);
+            }
+          }
+          continue;
+        }
+        if (amax_out && row_ok) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            if (jj < nvalid) amax = fmaxf(amax, fabsf(__uint_as_float(r[jj])));
+        }
+        if (d_dtype == NVFP4A_BF16) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = f32_to_bf16_bits(__uint_as_float(r[jj]));
+        } else if (d_dtype == NVFP4A_FP16) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(r[jj])));
+        }
+        if (!d_tma) {
+          if (row_ok) {
+            if (esz == 2) {
+              uint16_t *d16 = (uint16_t *)dptr + (size_t)j0 * ldd + i;
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (jj < nvalid) d16[(size_t)jj * ldd] = (uint16_t)r[jj];
+            } else {
+              uint32_t *d32 = (uint32_t *)dptr + (size_t)j0 * ldd + i;
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (jj < nvalid) d32[(size_t)jj * ldd] = r[jj];
+            }
+          }
+          continue;
+        }
+        for (int half = 0; half < 32 / cw; ++half) {
+          if (leader) bulk_wait_read_all();
+          named_barrier(1, 128);
+          const int rr = quad * 32 + lane;
+          if (esz == 2) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) ((uint16_t *)staging)[jj * 128 + rr] = (uint16_t)r[jj];
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) ((uint32_t *)staging)[jj * 128 + rr] = half ? r[16 + jj] : r[jj];
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (leader) {
+            tma_store_2d(&tmap_d, staging, tm * 128, j0 + half * cw);
+            bulk_commit();
+          }
+        }
+      }
+    }
+    if (leader) bulk_wait_all();
+    if (amax_out) warp_amax_commit(amax_out, amax);
+  } else {
+    // ---------------- weight expansion: NVFP4 -> BF16 into the swizzled A tile ----------------
+    const int cwarp = warp - 6;
+    const int row = cwarp * 16 + (lane >> 1), half = lane & 1;   // lanes 2 r, 2 r + 1: the two halves of one row (one 32-byte sector)
+    const Fp4Operand A = g.A;
+    const ScalePos sp{A.sld};
+    auto fetch = [&](uint32_t f_it) -> RawHalfRow {
+      RawHalfRow v;
+      const uint32_t tl = f_it / (uint32_t)nk, ks = f_it - tl * (uint32_t)nk;
+      const int t = blockIdx.x + (int)tl * gridDim.x;
+      if (t >= ntiles) { v.w = make_uint4(0, 0, 0, 0); v.sc = 0; return v; }
+      const int r = min((t % tiles_m) * 128 + row, gm - 1);
+      const int kb = (int)ks * 4 + half * 2;
+      if (A.image) {
+        const uint8_t *tile = A.data + ((size_t)(r >> 7) * A.ktiles + (ks >> 2)) * kImgTileBytes;
+        const int rr = r & 127, kq = (int)(ks & 3) * 4 + half * 2;
+        v.w = __ldg((const uint4 *)(tile + rr * 128 + (ks & 3) * 32 + half * 16));
+        v.sc = __ldg((const uint16_t *)(tile + kImgDataBytes + (kq >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (kq & 3)));
+      } else {
+        v.w = __ldg((const uint4 *)(A.data + (size_t)r * (A.ld >> 1) + (size_t)ks * 32 + half * 16));
+        v.sc = __ldg((const uint16_t *)(A.sc + sp.at(r, kb)));
+      }
+      return v;
+    };
+    uint32_t it = 0;
+    RawHalfRow cur = fetch(0), nxt = fetch(1);
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        const RawHalfRow nn = fetch(it + 2);
+        const int s = it % kStages;
+        if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitConv)) goto done;
+        uint8_t *sA = smem + (size_t)s * C::kStageBytes + row * 128;
+        const uint32_t wv[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
+        const uint32_t s0 = lut[cur.sc & 0xFF], s1 = lut[(cur.sc >> 8) & 0xFF];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // word q: k = 32 half + 8 q .. + 7, block q / 2 of this half row
+          const uint32_t sc = q < 2 ? s0 : s1;
+          const uint32_t d0 = bf16x2_mul(decode_pair<0>(wv[q]), sc), d1 = bf16x2_mul(decode_pair<1>(wv[q]), sc);
+          const uint32_t d2 = bf16x2_mul(decode_pair<2>(wv[q]), sc), d3 = bf16x2_mul(decode_pair<3>(wv[q]), sc);
+          // (n0 n4)(n1 n5)(n2 n6)(n3 n7) -> (n0 n1)(n2 n3)(n4 n5)(n6 n7)
+          const uint4 o = make_uint4(prmt(d0, d1, 0x5410), prmt(d2, d3, 0x5410), prmt(d0, d1, 0x7632), prmt(d2, d3, 0x7632));
+          const int chunk = half * 4 + q;
+          *(uint4 *)(sA + ((chunk ^ (row & 7)) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_a[s]);
+        cur = nxt; nxt = nn;
+      }
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int BN>
+cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const W4A16Args &a, cudaStream_t s) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev & 63] = true;
+  }
+  const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
+  const int grid = tiles < device_sms() ? tiles : device_sms();
+  gemm_w4a16_kernel<BN><<<grid, kThreads, C::kSmemBytes, s>>>(tb, td, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_w4a16_supports(const GemmArgs &g) {
+  if (g.B.dtype != NVFP4A_BF16 || g.k < 64 || ((uintptr_t)g.B.data & 15) || g.B.ld % 8) return false;
+  if (!g.A.image && (((uintptr_t)g.A.data & 15) || g.A.ld % 32 || ((uintptr_t)g.A.sc & 1))) return false;
+  return true;
+}
+
+cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s) {
+  W4A16Args a;
+  memset(&a, 0, sizeof a);
+  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.A = g.A;
+  a.e = g.e; a.x = g.x;
+  a.status = kernel_status_device_ptr();
+  const int bn = g.n > 128 ? 256 : 128;
+  CUtensorMap tb, td;
+  if (!make_tmap_bytes(&tb, g.B.data, (uint64_t)g.k * 2, (uint64_t)g.n, (uint64_t)g.B.ld * 2, bn)) return cudaErrorInvalidValue;
+  memset(&td, 0, sizeof td);
+  const int esz = dense_bytes(g.e.d_dtype);
+  a.d_tma = !(g.x.mask & kExSwiglu) && ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
+            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
+  return bn == 256 ? launch_cfg<256>(tb, td, a, s) : launch_cfg<128>(tb, td, a, s);
+}
+
+}  // namespace nvb
