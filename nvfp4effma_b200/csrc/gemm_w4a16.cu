@@ -11,8 +11,8 @@
 //   warp 1      MMA issuer (4 x K16 per stage), owner of the tensor memory: 2 accumulators of BN columns
 //   warps 2-5   epilogue, one 32-lane quadrant each: plain or extended (RMSNorm column scale, SwiGLU, second output + sums
 //               of squares), D through a shared-memory staging tile and TMA stores when its layout allows
-//   warps 6-13  weight expansion: each thread owns half a row of the stage (32 nibbles + 2 scale bytes, fetched from
-//               global memory two stages ahead), decodes them with shifts and masks to BF16 pairs (value * 2^-126, the
+//   warps 6-13  weight expansion, two groups of four warps on alternate stages: each thread owns a row of its stage (64
+//               nibbles + 4 scale bytes, fetched from global memory ahead of use), decodes them with shifts and masks to BF16 pairs (value * 2^-126, the
 //               subnormal trick), multiplies by the block scale in BF16 (exact) and stores 64 bytes into the swizzled
 //               A tile.  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for E4M3, 16 for
 //               UE5M3 scales) and the accumulator is multiplied by 2^Z in the epilogue.
@@ -32,7 +32,7 @@ struct W4A16Args {
   Epilogue e;
   EpilogueEx x;
   unsigned *status;
-  int d_tma;     // the main output goes through the staging tile and TMA stores
+  int d_tma;     // the output goes through the staging tile and TMA stores (SwiGLU: 64 output rows per tile)
 };
 
 template <int BN>
@@ -65,9 +65,9 @@ __device__ __forceinline__ uint32_t decode_pair(uint32_t w) {
   return mag | sgn;
 }
 
-// what a conversion thread fetches for one stage: 32 nibbles and the two scale bytes of its half row
-struct RawHalfRow {
-  uint4 w;
+// what a conversion thread fetches for one stage: the 64 nibbles and 4 scale bytes of its row
+struct RawRow {
+  uint4 w0, w1;
   uint32_t sc;
 };
 
@@ -94,7 +94,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
   unsigned *const status_word = g.status;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kConvWarps); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kConvWarps / 2); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -193,16 +193,44 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
       const float s_plain = __fmul_rn(rowp, gf);   // ((alpha gA) * 1) * gf: B is dense, its column part is 1
       if (mask & kExNorm) {  // column scales of this token tile (the previous tile's are no longer in use: see the barrier below)
         named_barrier(1, 128);
-        for (int jj = quad; jj < BN; jj += 4) {
-          const int j = tn * BN + jj;
-          float s = 0.f;
-          if (j < gn) {
-            const float *p = norm_parts + (size_t)j * norm_ld;
-            for (int q = lane; q < norm_nparts; q += 32) s = __fadd_rn(s, __ldcg(p + q));
+        // The defining order (reference include/nvfp4effma.h:224-226 there): lane l adds parts l, l + 32, ... in ascending
+        // order, then an xor butterfly 16..1.  A warp takes 8 tokens at a time so that their loads fly together.
+        for (int j8 = quad * 8; j8 < BN; j8 += 32) {
+          float sum[8];
+          if (norm_nparts <= 256) {
+            float v[8][8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int j = min(tn * BN + j8 + u, gn - 1);
+              const float *p = norm_parts + (size_t)j * norm_ld + lane;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) v[u][q] = (32 * q + lane < norm_nparts) ? __ldcg(p + 32 * q) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float a = 0.f;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (32 * q + lane < norm_nparts) a = __fadd_rn(a, v[u][q]);
+              sum[u] = a;
+            }
+          } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int j = min(tn * BN + j8 + u, gn - 1);
+              const float *p = norm_parts + (size_t)j * norm_ld;
+              float a = 0.f;
+              for (int q = lane; q < norm_nparts; q += 32) a = __fadd_rn(a, __ldcg(p + q));
+              sum[u] = a;
+            }
           }
 #pragma unroll
-          for (int o = 16; o; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xFFFFFFFFu, s, o));
-          if (lane == 0) colscale[jj] = __frsqrt_rn(__fadd_rn(__fmul_rn(s, norm_inv_n), norm_eps));
+          for (int u = 0; u < 8; ++u) {
+            float a = sum[u];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            if (lane == 0) colscale[j8 + u] = __frsqrt_rn(__fadd_rn(__fmul_rn(a, norm_inv_n), norm_eps));
+          }
         }
       }
       if (!wait(&tmem_full[acc], (tile_i >> 1) & 1, kStWaitTmemFull)) *abort_flag = 1;
@@ -243,16 +271,49 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
             if (row_ok && !(lane & 15) && jj < nvalid) sqptr[(size_t)(j0 + jj) * ld_sq + (i >> 4)] = sq;
           }
         }
-        if (mask & kExSwiglu) {  // rows 16 q + r (gate) and 16 q + 8 + r (up) -> output row 8 q + r; plain stores
+        if (mask & kExSwiglu) {  // rows 16 q + r (gate) and 16 q + 8 + r (up) -> output row 8 q + r: 64 output rows per tile
+          // The gate lane and its up lane (lane ^ 8) share the work: the gate lane forms the even columns of their output
+          // row, the up lane the odd ones; one shuffle per column pair carries what each needs from the other.
           const int io = (i >> 4) * 8 + (i & 7);
+          const bool gate = !(lane & 8);
+          const int odd = gate ? 0 : 1;
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const float v = __uint_as_float(r[jj]);
-            const float up = __shfl_xor_sync(0xFFFFFFFFu, v, 8);
-            if (row_ok && !(lane & 8) && jj < nvalid) {
-              const float h = silu_mul(v, up);
-              amax = fmaxf(amax, fabsf(h));
-              store_dense(d_dtype, dptr, (size_t)(j0 + jj) * ldd + io, h);
+          for (int q = 0; q < 16; ++q) {
+            const float v0 = __uint_as_float(r[2 * q]), v1 = __uint_as_float(r[2 * q + 1]);
+            const float got = __shfl_xor_sync(0xFFFFFFFFu, gate ? v1 : v0, 8);
+            const float h = gate ? silu_mul(v0, got) : silu_mul(got, v1);
+            if (row_ok && 2 * q + odd < nvalid) amax = fmaxf(amax, fabsf(h));
+            if (d_dtype == NVFP4A_BF16) r[q] = f32_to_bf16_bits(h);
+            else if (d_dtype == NVFP4A_FP16) r[q] = (uint32_t)__half_as_ushort(__float2half_rn(h));
+            else r[q] = __float_as_uint(h);
+          }
+          if (!d_tma) {
+            if (row_ok) {
+#pragma unroll
+              for (int q = 0; q < 16; ++q)
+                if (2 * q + odd < nvalid) {
+                  if (esz == 2) ((uint16_t *)dptr)[(size_t)(j0 + 2 * q + odd) * ldd + io] = (uint16_t)r[q];
+                  else ((uint32_t *)dptr)[(size_t)(j0 + 2 * q + odd) * ldd + io] = r[q];
+                }
+            }
+            continue;
+          }
+          const int lr = quad * 16 + (lane >> 4) * 8 + (lane & 7);  // output row inside the tile's 64
+          for (int half = 0; half < 32 / cw; ++half) {
+            if (leader) bulk_wait_read_all();
+            named_barrier(1, 128);
+            if (esz == 2) {
+#pragma unroll
+              for (int q = 0; q < 16; ++q) ((uint16_t *)staging)[(2 * q + odd) * 64 + lr] = (uint16_t)r[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) ((uint32_t *)staging)[(2 * q + odd) * 64 + lr] = half ? r[8 + q] : r[q];
+            }
+            fence_proxy_async_smem();
+            named_barrier(1, 128);
+            if (leader) {
+              tma_store_2d(&tmap_d, staging, tm * 64, j0 + half * cw);
+              bulk_commit();
             }
           }
           continue;
@@ -309,52 +370,68 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
     if (amax_out) warp_amax_commit(amax_out, amax);
   } else {
     // ---------------- weight expansion: NVFP4 -> BF16 into the swizzled A tile ----------------
-    const int cwarp = warp - 6;
-    const int row = cwarp * 16 + (lane >> 1), half = lane & 1;   // lanes 2 r, 2 r + 1: the two halves of one row (one 32-byte sector)
+    // Two groups of four warps take alternate stages; inside a group thread r owns row r of the stage: 64 nibbles (32
+    // contiguous bytes) and their 4 scale bytes, fetched one of its own stages (two pipeline stages) ahead.
+    const int cwarp = warp - 6, group = cwarp >> 2;
+    const int row = (cwarp & 3) * 32 + lane;
     const Fp4Operand A = g.A;
     const ScalePos sp{A.sld};
-    auto fetch = [&](uint32_t f_it) -> RawHalfRow {
-      RawHalfRow v;
-      const uint32_t tl = f_it / (uint32_t)nk, ks = f_it - tl * (uint32_t)nk;
-      const int t = blockIdx.x + (int)tl * gridDim.x;
-      if (t >= ntiles) { v.w = make_uint4(0, 0, 0, 0); v.sc = 0; return v; }
+    // source pointers of (tile t, k step 0) for this thread's row; a k step advances nibbles by 32 bytes and scales by 4
+    auto tile_ptrs = [&](int t, const uint8_t *&wp, const uint8_t *&scp) {
       const int r = min((t % tiles_m) * 128 + row, gm - 1);
-      const int kb = (int)ks * 4 + half * 2;
       if (A.image) {
-        const uint8_t *tile = A.data + ((size_t)(r >> 7) * A.ktiles + (ks >> 2)) * kImgTileBytes;
-        const int rr = r & 127, kq = (int)(ks & 3) * 4 + half * 2;
-        v.w = __ldg((const uint4 *)(tile + rr * 128 + (ks & 3) * 32 + half * 16));
-        v.sc = __ldg((const uint16_t *)(tile + kImgDataBytes + (kq >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (kq & 3)));
+        const uint8_t *tile = A.data + (size_t)(r >> 7) * A.ktiles * kImgTileBytes;
+        const int rr = r & 127;
+        wp = tile + rr * 128;
+        scp = tile + kImgDataBytes + (rr & 31) * 16 + (rr >> 5) * 4;
       } else {
-        v.w = __ldg((const uint4 *)(A.data + (size_t)r * (A.ld >> 1) + (size_t)ks * 32 + half * 16));
-        v.sc = __ldg((const uint16_t *)(A.sc + sp.at(r, kb)));
+        wp = A.data + (size_t)r * (A.ld >> 1);
+        scp = A.sc + sp.row(r);
       }
-      return v;
     };
+    const bool img = A.image, swz = A.sld < 0;
+    auto fetch = [&](const uint8_t *wp, const uint8_t *scp, int ks, RawRow &v) {
+      size_t woff, soff;
+      if (img) { woff = (size_t)(ks >> 2) * kImgTileBytes + (ks & 3) * 32; soff = (size_t)(ks >> 2) * kImgTileBytes + (ks & 3) * 512; }
+      else { woff = (size_t)ks * 32; soff = swz ? (size_t)ks * 512 : (size_t)ks * 4; }
+      v.w0 = __ldg((const uint4 *)(wp + woff));
+      v.w1 = __ldg((const uint4 *)(wp + woff + 16));
+      v.sc = __ldg((const uint32_t *)(scp + soff));
+    };
+    // prefetch cursor: this group's next stage (tile pf_t, k step pf_ks)
+    int pf_t = blockIdx.x, pf_ks = group;
+    const uint8_t *pf_w = nullptr, *pf_s = nullptr;
+    auto advance = [&]() {  // to the group's following stage
+      pf_ks += 2;
+      while (pf_ks >= nk && pf_t < ntiles) { pf_ks -= nk; pf_t += gridDim.x; if (pf_t < ntiles) tile_ptrs(pf_t, pf_w, pf_s); }
+    };
+    RawRow cur, nxt;
+    cur.w0 = cur.w1 = nxt.w0 = nxt.w1 = make_uint4(0, 0, 0, 0); cur.sc = nxt.sc = 0;
+    if (pf_t < ntiles) tile_ptrs(pf_t, pf_w, pf_s);
+    while (pf_ks >= nk && pf_t < ntiles) { pf_ks -= nk; pf_t += gridDim.x; if (pf_t < ntiles) tile_ptrs(pf_t, pf_w, pf_s); }
+    if (pf_t < ntiles) { fetch(pf_w, pf_s, pf_ks, cur); advance(); }
     uint32_t it = 0;
-    RawHalfRow cur = fetch(0), nxt = fetch(1);
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
       for (int ks = 0; ks < nk; ++ks, ++it) {
-        const RawHalfRow nn = fetch(it + 2);
+        if ((int)(it & 1) != group) continue;
+        if (pf_t < ntiles) { fetch(pf_w, pf_s, pf_ks, nxt); advance(); }
         const int s = it % kStages;
         if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitConv)) goto done;
         uint8_t *sA = smem + (size_t)s * C::kStageBytes + row * 128;
-        const uint32_t wv[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
-        const uint32_t s0 = lut[cur.sc & 0xFF], s1 = lut[(cur.sc >> 8) & 0xFF];
+        const uint32_t wv[8] = {cur.w0.x, cur.w0.y, cur.w0.z, cur.w0.w, cur.w1.x, cur.w1.y, cur.w1.z, cur.w1.w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {  // word q: k = 32 half + 8 q .. + 7, block q / 2 of this half row
-          const uint32_t sc = q < 2 ? s0 : s1;
+        for (int q = 0; q < 8; ++q) {  // word q: k = 8 q .. 8 q + 7 of the stage, block q / 2
+          const uint32_t sc = lut[(cur.sc >> (8 * (q >> 1))) & 0xFF];
           const uint32_t d0 = bf16x2_mul(decode_pair<0>(wv[q]), sc), d1 = bf16x2_mul(decode_pair<1>(wv[q]), sc);
           const uint32_t d2 = bf16x2_mul(decode_pair<2>(wv[q]), sc), d3 = bf16x2_mul(decode_pair<3>(wv[q]), sc);
           // (n0 n4)(n1 n5)(n2 n6)(n3 n7) -> (n0 n1)(n2 n3)(n4 n5)(n6 n7)
           const uint4 o = make_uint4(prmt(d0, d1, 0x5410), prmt(d2, d3, 0x5410), prmt(d0, d1, 0x7632), prmt(d2, d3, 0x7632));
-          const int chunk = half * 4 + q;
-          *(uint4 *)(sA + ((chunk ^ (row & 7)) << 4)) = o;
+          *(uint4 *)(sA + ((q ^ (row & 7)) << 4)) = o;
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_a[s]);
-        cur = nxt; nxt = nn;
+        cur = nxt;
       }
     }
   }
@@ -404,8 +481,10 @@ cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s) {
   if (!make_tmap_bytes(&tb, g.B.data, (uint64_t)g.k * 2, (uint64_t)g.n, (uint64_t)g.B.ld * 2, bn)) return cudaErrorInvalidValue;
   memset(&td, 0, sizeof td);
   const int esz = dense_bytes(g.e.d_dtype);
-  a.d_tma = !(g.x.mask & kExSwiglu) && ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
-            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
+  const bool glu = (g.x.mask & kExSwiglu) != 0;
+  const int drows = glu ? g.m / 2 : g.m;   // SwiGLU: the output has m / 2 rows, 64 per tile
+  a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)drows * esz) % 16 == 0 &&
+            make_tmap_dense(&td, g.e.d, esz, (uint64_t)drows, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, glu ? 64 : 128, esz == 2 ? 32 : 16);
   return bn == 256 ? launch_cfg<256>(tb, td, a, s) : launch_cfg<128>(tb, td, a, s);
 }
 
