@@ -131,6 +131,7 @@ struct EpilogueEx {
   const float *norm_parts; int norm_nparts, norm_ld; float norm_inv_n, norm_eps;
   void *d2; int d2_dtype, ldd2; const void *w2; int w2_dtype;
   float *sq; int ld_sq;
+  const float *colscales;  // kExNorm: the column scales s_j, already computed (one float per token), or NULL
 };
 constexpr int kExNorm = 1, kExSwiglu = 2, kExOut2 = 4;
 

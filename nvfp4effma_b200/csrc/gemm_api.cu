@@ -91,6 +91,10 @@ static nvfp4a_status check_epilogue_operands(const char *fn, int m, float beta, 
 // GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM
 static thread_local int g_last_route = 0;
 
+// The workspace of nvfp4a_gemm_tc_ex holds the RMSNorm column scales of up to kWorkspaceTokens tokens while a call runs (a
+// small kernel fills it before the GEMM, a memset restores the zeros after it); the other tensor-core calls leave it alone.
+constexpr int kWorkspaceTokens = 16384;
+
 static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t stream) {
   cudaError_t err;
   const bool gemv = g.k == 0 || g.n <= kGemvMaxN;
@@ -213,7 +217,15 @@ static nvfp4a_status gemm_tc_run(const char *fn, int m, int n, int k, float alph
   } else g.B = make_b(B, k, 0, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
-  return dispatch(fn, g, stream);
+  // RMSNorm column scales once per call instead of once per tile of weight rows (the tcgen05 W4A16 GEMM reads them)
+  const bool stage_scales = (ex.mask & kExNorm) && n > kGemvMaxN && n <= kWorkspaceTokens && forced_route() != 1 && gemm_w4a16_supports(g);
+  if (stage_scales) {
+    if (nvfp4a_status st = cuda_fail(launch_norm_scales(ex, n, (float *)workspace, stream), fn)) return st;
+    g.x.colscales = (const float *)workspace;
+  }
+  const nvfp4a_status st = dispatch(fn, g, stream);
+  if (stage_scales && st == NVFP4A_OK) return cuda_fail(cudaMemsetAsync(workspace, 0, (size_t)n * sizeof(float), stream), fn);
+  return st;
 }
 
 static nvfp4a_status gemv_tc_run(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
@@ -326,7 +338,7 @@ extern "C" size_t nvfp4a_tc_image_bytes(int operand, nvfp4a_dtype dtype, int row
   return (size_t)rows * k * 2;
 }
 
-extern "C" size_t nvfp4a_tc_workspace_bytes(void) { return 1024; }  // the tcgen05 kernels keep no cross-CTA state; kept non-zero for callers
+extern "C" size_t nvfp4a_tc_workspace_bytes(void) { return (size_t)kWorkspaceTokens * sizeof(float); }
 
 extern "C" nvfp4a_status nvfp4a_tc_image(int operand, const nvfp4a_tensor *src, int ld, int rows, int k, void *image, cudaStream_t stream) {
   clear_error();

@@ -172,6 +172,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
     const float *const norm_parts = g.x.norm_parts;
     const int norm_nparts = g.x.norm_nparts, norm_ld = g.x.norm_ld;
     const float norm_inv_n = g.x.norm_inv_n, norm_eps = g.x.norm_eps;
+    const float *const colscales = g.x.colscales;
     uint8_t *const d2ptr = (uint8_t *)g.x.d2;
     const int d2_dtype = g.x.d2_dtype, ldd2 = g.x.ldd2, w2_dtype = g.x.w2_dtype, ld_sq = g.x.ld_sq;
     const void *const w2ptr = g.x.w2;
@@ -193,9 +194,12 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
       const float s_plain = __fmul_rn(rowp, gf);   // ((alpha gA) * 1) * gf: B is dense, its column part is 1
       if (mask & kExNorm) {  // column scales of this token tile (the previous tile's are no longer in use: see the barrier below)
         named_barrier(1, 128);
+        if (colscales) {  // computed before the launch, one float per token
+          for (int jj = quad * 32 + lane; jj < BN; jj += 128) colscale[jj] = __ldcg(colscales + min(tn * BN + jj, gn - 1));
+        }
         // The defining order (reference include/nvfp4effma.h:224-226 there): lane l adds parts l, l + 32, ... in ascending
         // order, then an xor butterfly 16..1.  A warp takes 8 tokens at a time so that their loads fly together.
-        for (int j8 = quad * 8; j8 < BN; j8 += 32) {
+        for (int j8 = quad * 8; j8 < BN && !colscales; j8 += 32) {
           float sum[8];
           if (norm_nparts <= 256) {
             float v[8][8];

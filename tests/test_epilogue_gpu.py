@@ -106,6 +106,7 @@ def run_case(m, n, k, bt, dt, mask, use_bias, use_c, tc):
         gsq = host(sq).reshape(n, lsq)
         assert np.array_equal(gsq[:, : m // 16].view(np.uint32), r["sq"].reshape(n, lsq)[:, : m // 16].view(np.uint32)), tag + " (sq)"
         assert np.all(gsq[:, m // 16:] == -1.0)
+    assert not bool(ws.any()), tag + " (the workspace is left zeroed)"
 
 
 @pytest.mark.parametrize("tc", [False, True])
