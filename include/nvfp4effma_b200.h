@@ -43,6 +43,20 @@ int nvfp4a_b200_last_route(void);
  * mma.sync one.  A pinned value also lifts the size threshold below which the automatic choice prefers the mma.sync GEMV.  Tuning / test aid, no counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_gemv_splits(int splits);
 
+/* nvfp4a_gemm_ex that allocates nothing and still computes the RMSNorm column scales once per call: they are staged in a
+ * 64 KiB device array inside the library image instead of a workspace.  No counterpart in the reference (its
+ * nvfp4a_gemm_ex needs no scratch; its tensor-core entries take a caller workspace).  Same arguments and the same results,
+ * bit for bit, as nvfp4a_gemm_ex.  For callers that cannot hand over or allocate scratch at the call: inside stream
+ * capture, or where a framework allocator holds all device memory.
+ *   - n is limited to nvfp4a_b200_static_scratch_tokens() (16384); a larger n returns NVFP4A_INVALID_VALUE.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress): make it before capturing a stream.
+ *   - Nothing needs zeroing: every call writes the entries it reads.
+ *   - One array per device: calls that overlap in time on a device (two streams, two threads) race on it; serialise them. */
+nvfp4a_status nvfp4a_b200_gemm_ex_static(int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb,
+                                         float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd,
+                                         const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex, cudaStream_t stream);
+int nvfp4a_b200_static_scratch_tokens(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,8 @@ _PROTOS = {
     "nvfp4a_b200_set_tile_n": (_i, [_i]),
     "nvfp4a_b200_set_gemv_splits": (_i, [_i]),
     "nvfp4a_b200_last_route": (_i, []),
+    "nvfp4a_b200_gemm_ex_static": (_i, _GEMM + [_E, _s]),
+    "nvfp4a_b200_static_scratch_tokens": (_i, []),
 }
 EXPORTS = tuple(_PROTOS)
 

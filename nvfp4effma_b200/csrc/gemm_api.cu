@@ -277,6 +277,21 @@ static nvfp4a_status check_weight_image(const char *fn, int kind, const void *im
   return NVFP4A_OK;
 }
 
+// nvfp4a_gemm_ex with the RMSNorm column scales of all n tokens computed first into `colscales` (n floats the caller of this
+// function owns for the duration of the call); used by nvfp4a_b200_gemm_ex_static.  The scales kernel runs after the
+// descriptor has been checked and before the operand checks of gemm_run; it writes nothing but `colscales`.
+nvfp4a_status gemm_ex_with_scales(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb,
+                                  float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias,
+                                  const nvfp4a_epilogue *ex, float *colscales, cudaStream_t stream) {
+  EpilogueEx x;
+  if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, beta, ldd, &x)) return st;
+  if ((x.mask & kExNorm) && colscales && n > kGemvMaxN && B && B->dtype == NVFP4A_BF16 && forced_route() != 1) {
+    if (nvfp4a_status st = cuda_fail(launch_norm_scales(x, n, colscales, stream), fn)) return st;
+    x.colscales = colscales;
+  }
+  return gemm_run(fn, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, x, stream);
+}
+
 }  // namespace nvb
 
 using namespace nvb;
