@@ -57,7 +57,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -148,6 +148,49 @@ def time_steps(fn, steps, warmup, stream, dist, world):
     return ms
 
 
+def time_graph(fn, calls, replays, warmup, dist, world):
+    """Kernels of a few microseconds: `calls` launches of fn(i) captured into one CUDA graph (the host's ctypes overhead per
+    call would otherwise exceed the kernel), replayed `replays` times after `warmup` direct calls; CUDA events around each
+    replay; returns (median ms per call, max over ranks; launches issued on this rank)."""
+    import torch
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ts = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / calls)
+    ts.sort()
+    ms = ts[len(ts) // 2]
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    return ms, warmup + calls * (replays + 2)
+
+
+def hbm_entry(name, bytes_per_call, ms, world, peaks, traffic, key, workload, l2, **more):
+    gbs = bytes_per_call / (ms * 1e-3) / 1e9
+    d = {"metric": name, "value": gbs * world, "unit": "GB/s", "us_per_call": ms * 1e3,
+         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                      "traffic": traffic.get(key)},
+         "config": {"workload": workload, "l2": l2}}
+    d.update(more)
+    return d
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -161,13 +204,14 @@ def run_ours(args, rank, world, local_rank):
     stream = torch.cuda.current_stream()
     peaks = load_peaks()
     traffic = load_traffic()
+    launches = 0
 
     # ---- GEMM W4A4 4096^3: rotating sets (inputs 18.9 MB + D 33.6 MB each; 3 sets > 126 MB of L2) ----
     nsets = 3
     sets = []
     for s in range(nsets):
-        A = W.quantize_decode_factor(W.randn_bf16(M, K, 1.0, 200 + 2 * s + 1000 * rank, dev))
-        B = W.quantize_decode_factor(W.randn_bf16(N, K, 1.0, 201 + 2 * s + 1000 * rank, dev))
+        A = W.quantize_decode_factor(W.randn_bf16(M, K, 1.0, 200 + 2 * s + 1000 * rank, dev), swizzled=True)
+        B = W.quantize_decode_factor(W.randn_bf16(N, K, 1.0, 201 + 2 * s + 1000 * rank, dev), swizzled=True)
         D = torch.empty(N * M, dtype=torch.bfloat16, device=dev)
         sets.append((A, B, D, A.tensor(), B.tensor()))
     torch.cuda.synchronize()
@@ -176,14 +220,14 @@ def run_ours(args, rank, world, local_rank):
         A, B, D, tA, tB = sets[i % nsets]
         W.gemm(M, N, K, tA, tB, D)
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank)   # runs until every timed region of this process is over
     if rank == 0:
         sampler.start()
+        t_wait = time.perf_counter()
+        while not sampler.rows and time.perf_counter() - t_wait < 3.0:   # nvidia-smi needs a moment before its first sample
+            time.sleep(0.05)
     ms = time_steps(gemm_step, args.steps, args.warmup, stream, dist, world)
-    clocks = sampler.stop() if rank == 0 else None
-    status = W.kernel_status()
-    if status:
-        raise RuntimeError(f"a tensor-core kernel gave up a wait (status 0x{status:x})")
+    launches += args.steps + args.warmup
     ms_step = ms / args.steps
     tflops = 2.0 * M * N * K * world / (ms_step * 1e-3) / 1e12
     peak_fp4 = 4.0 * peaks["bf16_tflops"]
@@ -211,49 +255,71 @@ def run_ours(args, rank, world, local_rank):
 
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = time_steps(e2e_step, e2e_steps, 3, stream, dist, world) / e2e_steps
+    launches += e2e_steps + 3
     e2e = {"value": 2.0 * M * N * K * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": ms_e2e}
+    del sets, hA, hB, hD
 
     extra = {}
-    launches = args.steps
-    if rank == 0 or True:
-        # ---- GEMV 8192^2 batch 1 (W4A16): 8 distinct weights = 302 MB > L2 ----
-        nw = 8
-        ws = [W.quantize_decode_factor(W.randn_bf16(GEMV_M, GEMV_K, 0.02, 300 + s + 1000 * rank, dev)) for s in range(nw)]
-        x = W.randn_bf16(1, GEMV_K, 1.0, 400 + rank, dev)
-        y = torch.empty(GEMV_M, dtype=torch.bfloat16, device=dev)
-        tws, tx, ty = [w.tensor() for w in ws], W.tensor(x, L.BF16), W.tensor(y, L.BF16)
+    # ---- GEMV 8192^2 batch 1 (W4A16): 8 distinct weights = 302 MB > L2; the image entry is what TCWeight decodes through ----
+    nw = 8
+    ws = [W.quantize_decode_factor(W.randn_bf16(GEMV_M, GEMV_K, 0.02, 300 + s + 1000 * rank, dev)) for s in range(nw)]
+    imgs = [W.weight_image(w) for w in ws]
+    x = W.randn_bf16(1, GEMV_K, 1.0, 400 + rank, dev)
+    y = torch.empty(GEMV_M, dtype=torch.bfloat16, device=dev)
+    tws, tx, ty = [w.tensor() for w in ws], W.tensor(x, L.BF16), W.tensor(y, L.BF16)
 
-        def gemv_step(i):
-            L.check(L.lib.nvfp4a_gemm(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(tws[i % nw]), GEMV_K, ctypes.byref(tx), GEMV_K, 0.0, None, 0,
-                                      ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
+    def gemv_image(i):
+        L.check(L.lib.nvfp4a_gemv_tc(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(imgs[i % nw][1]), ctypes.byref(tx), GEMV_K, 0.0, None, 0,
+                                     ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
 
-        gsteps = max(args.steps, 40)
-        ms_gemv = time_steps(gemv_step, gsteps, 8, stream, dist, world) / gsteps
-        gbytes = GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16
-        gbs = gbytes / (ms_gemv * 1e-3) / 1e9
-        extra["gemv_8192_b1"] = {"metric": "gemv_w4a16_8192x8192_b1_gbs", "value": gbs * world, "unit": "GB/s", "us_per_call": ms_gemv * 1e3,
-                                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                              "frac": gbs / peaks["hbm_gbs"], "traffic": traffic.get("gemv_8192_dram_bytes")},
-                                 "config": {"workload": "gemv_w4a16_m8192_k8192_n1", "l2": "8 rotating weights (302 MB) > L2"}}
-        del ws, tws
-        # ---- quantization 8192^2 BF16 -> NVFP4, swizzled scales, amax computed: 3 inputs = 403 MB > L2 ----
-        nx = 3
-        xs = [W.outlier_input(QUANT_R, QUANT_C, 500 + s + 1000 * rank, dev) for s in range(nx)]
-        out = W.QuantizedMatrix(QUANT_R, QUANT_C, True, dev)
+    def gemv_plain(i):
+        L.check(L.lib.nvfp4a_gemm(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(tws[i % nw]), GEMV_K, ctypes.byref(tx), GEMV_K, 0.0, None, 0,
+                                  ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
 
-        def quant_step(i):
-            W.quantize_amax_swizzled(xs[i % nx], out)
+    gbytes = GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16
+    ms_gi, n1 = time_graph(gemv_image, 48, 7, 8, dist, world)
+    route_image = L.lib.nvfp4a_b200_last_route()
+    ms_gp, n2 = time_graph(gemv_plain, 48, 7, 8, dist, world)
+    route_plain = L.lib.nvfp4a_b200_last_route()
+    launches += n1 + n2
+    routes = {2: "mma.sync GEMV", 3: "FP4 tensor-core GEMV (tcgen05)"}
+    extra["gemv_8192_b1"] = hbm_entry("gemv_w4a16_8192x8192_b1_gbs", gbytes, ms_gi, world, peaks, traffic, "gemv_8192_dram_bytes",
+                                      "gemv_w4a16_m8192_k8192_n1", "8 rotating weights (302 MB) > L2", entry="nvfp4a_gemv_tc (weight image)",
+                                      kernel=routes.get(route_image), timing="CUDA graph of 48 calls, median of 7 replays",
+                                      plain_operand={"entry": "nvfp4a_gemm (linear scales)", "us_per_call": ms_gp * 1e3,
+                                                     "gbs": gbytes / (ms_gp * 1e-3) / 1e9, "kernel": routes.get(route_plain)})
+    del ws, tws, imgs
+    # ---- quantization 8192^2 BF16 -> NVFP4, swizzled scales: 3 inputs = 403 MB > L2 ----
+    nx = 3
+    xs = [W.outlier_input(QUANT_R, QUANT_C, 500 + s + 1000 * rank, dev) for s in range(nx)]
+    out = W.QuantizedMatrix(QUANT_R, QUANT_C, True, dev)
+    qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
+    ms_q, n1 = time_graph(lambda i: W.quantize_amax_swizzled(xs[i % nx], out), 24, 7, 5, dist, world)
+    ms_qg, n2 = time_graph(lambda i: W.quantize_given_amax(xs[i % nx], out), 24, 7, 5, dist, world)
+    launches += 3 * n1 + n2   # amax computed: memset + amax kernel + encode kernel per call
+    extra["quant_8192"] = hbm_entry("quantize_bf16_nvfp4_8192x8192_gbs", qbytes, ms_q, world, peaks, traffic, "quant_8192_dram_bytes",
+                                    "quantize_ex_8192x8192_bf16_swizzled_amax_computed", "3 rotating inputs (403 MB) > L2",
+                                    timing="CUDA graph of 24 calls, median of 7 replays",
+                                    note="amax computed by the call: the input is read twice, the second read is not credited",
+                                    amax_given={"us_per_call": ms_qg * 1e3, "gbs": qbytes / (ms_qg * 1e-3) / 1e9,
+                                                "frac": qbytes / (ms_qg * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                                "note": "global given (delayed scaling): one read, one write"})
+    del xs, out
 
-        qsteps = max(args.steps, 20)
-        ms_q = time_steps(quant_step, qsteps, 5, stream, dist, world) / qsteps
-        qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
-        qgbs = qbytes / (ms_q * 1e-3) / 1e9
-        extra["quant_8192"] = {"metric": "quantize_bf16_nvfp4_8192x8192_gbs", "value": qgbs * world, "unit": "GB/s", "us_per_call": ms_q * 1e3,
-                               "roofline": {"bound": "hbm", "achieved": qgbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                            "frac": qgbs / peaks["hbm_gbs"], "traffic": traffic.get("quant_8192_dram_bytes")},
-                               "config": {"workload": "quantize_ex_8192x8192_bf16_swizzled_amax", "l2": "3 rotating inputs (403 MB) > L2"}}
-        del xs
+    # ---- fused transformer-MLP GEMMs (W4A16, extended epilogue) at 2048 tokens ----
+    if not args.no_mlp:
+        extra["mlp_w4a16"] = bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks)
+        launches += extra["mlp_w4a16"].pop("_launches")
+    # ---- tensor-parallel decoder linear stack ----
+    if not args.no_tp:
+        extra["tp_llama8b_linears"] = bench_tp(args, dev, rank, world, dist, stream, peaks)
+        launches += extra["tp_llama8b_linears"].pop("_launches")
+
+    clocks = sampler.stop() if rank == 0 else None
+    status = W.kernel_status()
+    if status:
+        raise RuntimeError(f"a tensor-core kernel gave up a wait (status 0x{status:x})")
 
     # ---- CPU baseline beside it (rank 0, N = 1 only): bounded sample of the same GEMM through the oracle ----
     cpu = None
@@ -274,12 +340,120 @@ def run_ours(args, rank, world, local_rank):
         line = {"metric": "w4a4_gemm_4096_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "fp4 (e2m1, ue4m3 block scales) -> fp32 accumulate -> bf16", "data": "synthetic",
-                "config": {"workload": "w4a4_gemm_m4096_n4096_k4096", "entry": "nvfp4a_gemm", "scales": "linear E4M3 1x16, FP32 decode-factor globals",
+                "config": {"workload": "w4a4_gemm_m4096_n4096_k4096", "entry": "nvfp4a_gemm",
+                           "scales": "E4M3 1x16 in the cuBLASLt GEMM-swizzled layout, FP32 decode-factor globals",
                            "l2": f"{nsets} rotating operand/output sets (157 MB) > L2", "per_rank": "independent GEMMs, no collective"},
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "extra": extra}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks):
+    """gate / up (RMSNorm column scale + SwiGLU + bias + amax) and down (second output + sums of squares) of a Llama-3-8B MLP
+    through nvfp4a_gemm_tc_ex: NVFP4 weights, 2048 BF16 tokens."""
+    import torch
+    T, H, I = 2048, 4096, 14336
+    gu = W.quantize_decode_factor(W.randn_bf16(2 * I, H, 0.02, 600 + rank, dev))
+    dn = W.quantize_decode_factor(W.randn_bf16(H, I, 0.02, 601 + rank, dev))
+    gu_img, t_gu = W.weight_image(gu)
+    dn_img, t_dn = W.weight_image(dn)
+    x = W.randn_bf16(T, H, 1.0, 602 + rank, dev)
+    parts = torch.rand(T, 256, device=dev) * 0.03 + 0.002
+    bias_gu, bias_dn = W.randn_bf16(1, 2 * I, 0.01, 603, dev), W.randn_bf16(1, H, 0.01, 604, dev)
+    w2 = (torch.rand(H, device=dev) + 0.5).float()
+    h = torch.empty(T * I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(T * H, dtype=torch.bfloat16, device=dev)
+    d2 = torch.empty(T * H, dtype=torch.bfloat16, device=dev)
+    sq = torch.empty(T * (H // 16), dtype=torch.float32, device=dev)
+    amax = torch.zeros(2, dtype=torch.float32, device=dev)
+    ws = torch.zeros(L.lib.nvfp4a_tc_workspace_bytes(), dtype=torch.uint8, device=dev)
+    ex_gu, ex_dn = L.Epilogue(), L.Epilogue()
+    ex_gu.norm_parts, ex_gu.norm_nparts, ex_gu.norm_ld, ex_gu.norm_inv_n, ex_gu.norm_eps = parts.data_ptr(), 256, 256, 1.0 / H, 1e-6
+    ex_gu.swiglu = 1
+    ex_dn.d2, ex_dn.d2_dtype, ex_dn.ldd2, ex_dn.w2, ex_dn.w2_dtype, ex_dn.sq, ex_dn.ld_sq = d2.data_ptr(), L.BF16, H, w2.data_ptr(), L.FP32, sq.data_ptr(), H // 16
+
+    def image_b(t, rows, k):
+        img = torch.empty(L.lib.nvfp4a_tc_image_bytes(L.TC_B, L.BF16, rows, k), dtype=torch.uint8, device=dev)
+        tt = W.tensor(t, L.BF16)
+        L.check(L.lib.nvfp4a_tc_image(L.TC_B, ctypes.byref(tt), k, rows, k, W.ptr(img), W.stream_ptr()))
+        return img
+
+    xi, hi = image_b(x, T, H), None
+    t_h, t_y = W.tensor(h, L.BF16, amax=amax[0:1]), W.tensor(y, L.BF16, amax=amax[1:2])
+    t_bg, t_bd = W.tensor(bias_gu, L.BF16), W.tensor(bias_dn, L.BF16)
+    t_xi = W.tensor(xi, L.BF16)
+
+    def gate_up(i):
+        L.check(L.lib.nvfp4a_gemm_tc_ex(2 * I, T, H, 1.0, ctypes.byref(t_gu), ctypes.byref(t_xi), 0.0, None, 0, ctypes.byref(t_h), I, ctypes.byref(t_bg),
+                                        ctypes.byref(ex_gu), W.ptr(ws), W.stream_ptr()))
+
+    gate_up(0)
+    hi = image_b(h.view(T, I), T, I)
+    t_hi = W.tensor(hi, L.BF16)
+
+    def down(i):
+        L.check(L.lib.nvfp4a_gemm_tc_ex(H, T, I, 1.0, ctypes.byref(t_dn), ctypes.byref(t_hi), 0.0, None, 0, ctypes.byref(t_y), H, ctypes.byref(t_bd),
+                                        ctypes.byref(ex_dn), W.ptr(ws), W.stream_ptr()))
+
+    steps = max(3, min(args.steps, 10))
+    ms_gu = time_steps(gate_up, steps, 3, stream, dist, world) / steps
+    ms_dn = time_steps(down, steps, 3, stream, dist, world) / steps
+    f_gu, f_dn = 2.0 * 2 * I * T * H, 2.0 * H * T * I
+    tf = lambda f, ms: f / (ms * 1e-3) / 1e12
+    return {"metric": "mlp_w4a16_tflops", "unit": "TFLOP/s", "value": tf(f_gu + f_dn, ms_gu + ms_dn) * world, "tokens": T,
+            "gate_up": {"m": 2 * I, "k": H, "epilogue": "RMSNorm column scale + bias + SwiGLU + amax", "ms": ms_gu, "tflops": tf(f_gu, ms_gu)},
+            "down": {"m": H, "k": I, "epilogue": "bias + second output * w2 + sums of squares + amax", "ms": ms_dn, "tflops": tf(f_dn, ms_dn)},
+            "roofline": {"bound": "tensor", "achieved": tf(f_gu + f_dn, ms_gu + ms_dn), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf(f_gu + f_dn, ms_gu + ms_dn) / peaks["bf16_tflops"], "traffic": None},
+            "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1}
+
+
+def bench_tp(args, dev, rank, world, dist, stream, peaks):
+    """Llama-3-8B-shaped linear stack, weights sharded by output rows over the ranks, NCCL all-gather per layer: decode
+    (1 and 8 tokens, the whole step in one CUDA graph when the collectives capture) and prefill (4096 tokens)."""
+    import torch
+    from nvfp4effma_b200.tp import TPDecoderLinears
+    layers = args.tp_layers
+    stack = TPDecoderLinears(layers=layers, group=None, seed=4, device=dev)
+    weights = 218103808 * layers   # values: QKV 6144 x 4096, O 4096 x 4096, gate / up 28672 x 4096, down 4096 x 14336
+    out = {"layers": layers, "world": world, "weight_bytes_per_rank": stack.weight_bytes_local(), "_launches": 0}
+    for T in (1, 8):
+        g = torch.Generator(device=dev).manual_seed(40 + T)
+        h = torch.randn((T, 4096), generator=g, device=dev).bfloat16()
+        for _ in range(2):
+            stack(h)
+        torch.cuda.synchronize()
+        graph = None
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                stack(h)
+            gr.replay()
+            torch.cuda.synchronize()
+            graph = gr
+        except Exception:
+            graph = None
+        step = (lambda i: graph.replay()) if graph is not None else (lambda i: stack(h))
+        steps = 20
+        ms = time_steps(step, steps, 3, stream, dist, world) / steps
+        gbs = weights * 0.5625 / (ms * 1e-3) / 1e9
+        out[f"decode_{T}"] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "weight_gbs_all_ranks": gbs, "frac_of_hbm_all_ranks": gbs / (peaks["hbm_gbs"] * world),
+                              "cuda_graph": graph is not None}
+        out["_launches"] += 4 * layers * (steps + 6)
+        del graph
+    if not args.no_tp_prefill:
+        T = 4096
+        g = torch.Generator(device=dev).manual_seed(44)
+        h = torch.randn((T, 4096), generator=g, device=dev).bfloat16()
+        stack(h)
+        steps = 3
+        ms = time_steps(lambda i: stack(h), steps, 1, stream, dist, world) / steps
+        tfl = 2.0 * weights * T / (ms * 1e-3) / 1e12
+        out["prefill_4096"] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "tflops_all_ranks": tfl,
+                               "frac_of_bf16_peak_all_ranks": tfl / (peaks["bf16_tflops"] * world)}
+        out["_launches"] += 8 * layers * (steps + 2)
+    return out
 
 
 def main():
@@ -289,6 +463,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline beside the GPU number")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the fused-MLP (W4A16, extended epilogue) extra")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel linear stack extra")
+    ap.add_argument("--no-tp-prefill", action="store_true", help="tensor-parallel extra: decode only")
+    ap.add_argument("--tp-layers", type=int, default=32)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

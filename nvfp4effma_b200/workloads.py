@@ -87,6 +87,25 @@ def gemm(m, n, k, A, B, D, alpha=1.0, stream=None):
                               stream_ptr(stream)))
 
 
+def weight_image(q):
+    """The tensor-core image of a quantized weight (what ``TCWeight`` holds): returns (image tensor, nvfp4a_tensor on it)."""
+    nb = L.lib.nvfp4a_tc_image_bytes(L.TC_A16, L.NVFP4, q.rows, q.cols)
+    img = torch.empty(nb, dtype=torch.uint8, device=q.data.device)
+    t = q.tensor()
+    L.check(L.lib.nvfp4a_tc_image(L.TC_A16, ctypes.byref(t), q.cols, q.rows, q.cols, ptr(img), stream_ptr()))
+    return img, tensor(img, L.NVFP4, glob=q.glob)
+
+
+def quantize_given_amax(x, out, stream=None):
+    """Quantization with the amax global already in ``out.glob`` (a delayed-scaling step): one read, one write."""
+    rows, cols = x.shape
+    src = tensor(x, L.BF16)
+    dst = tensor(out.data, L.NVFP4, out.scales, 0, out.glob, None, L.SCALES_SWIZZLED | L.GLOBAL_AMAX, 0)
+    cfg = L.QuantConfig(1, L.FOS_OFF, 0)
+    L.check(L.lib.nvfp4a_quantize_ex(ctypes.byref(src), cols, rows, cols, ctypes.byref(dst), cols, None, 0, ctypes.byref(cfg),
+                                     stream_ptr(stream)))
+
+
 def kernel_status(reset=True):
     st = ctypes.c_uint(0)
     L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), int(reset)))
