@@ -205,6 +205,7 @@ def run_ours(args, rank, world, local_rank):
     peaks = load_peaks()
     traffic = load_traffic()
     launches = 0
+    only = args.only
 
     # ---- GEMM W4A4 4096^3: rotating sets (inputs 18.9 MB + D 33.6 MB each; 3 sets > 126 MB of L2) ----
     nsets = 3
@@ -253,8 +254,8 @@ def run_ours(args, rank, world, local_rank):
         W.gemm(M, N, K, tA, tB, D)
         hD.copy_(D, non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 10))
-    ms_e2e = time_steps(e2e_step, e2e_steps, 3, stream, dist, world) / e2e_steps
+    e2e_steps = max(3, min(args.steps, 10)) if only in ("all", "gemm") else 1
+    ms_e2e = time_steps(e2e_step, e2e_steps, 3 if only in ("all", "gemm") else 0, stream, dist, world) / e2e_steps
     launches += e2e_steps + 3
     e2e = {"value": 2.0 * M * N * K * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": ms_e2e}
@@ -262,57 +263,59 @@ def run_ours(args, rank, world, local_rank):
 
     extra = {}
     # ---- GEMV 8192^2 batch 1 (W4A16): 8 distinct weights = 302 MB > L2; the image entry is what TCWeight decodes through ----
-    nw = 8
-    ws = [W.quantize_decode_factor(W.randn_bf16(GEMV_M, GEMV_K, 0.02, 300 + s + 1000 * rank, dev)) for s in range(nw)]
-    imgs = [W.weight_image(w) for w in ws]
-    x = W.randn_bf16(1, GEMV_K, 1.0, 400 + rank, dev)
-    y = torch.empty(GEMV_M, dtype=torch.bfloat16, device=dev)
-    tws, tx, ty = [w.tensor() for w in ws], W.tensor(x, L.BF16), W.tensor(y, L.BF16)
+    if only in ("all", "gemv"):
+        nw = 8
+        ws = [W.quantize_decode_factor(W.randn_bf16(GEMV_M, GEMV_K, 0.02, 300 + s + 1000 * rank, dev)) for s in range(nw)]
+        imgs = [W.weight_image(w) for w in ws]
+        x = W.randn_bf16(1, GEMV_K, 1.0, 400 + rank, dev)
+        y = torch.empty(GEMV_M, dtype=torch.bfloat16, device=dev)
+        tws, tx, ty = [w.tensor() for w in ws], W.tensor(x, L.BF16), W.tensor(y, L.BF16)
 
-    def gemv_image(i):
-        L.check(L.lib.nvfp4a_gemv_tc(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(imgs[i % nw][1]), ctypes.byref(tx), GEMV_K, 0.0, None, 0,
-                                     ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
+        def gemv_image(i):
+            L.check(L.lib.nvfp4a_gemv_tc(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(imgs[i % nw][1]), ctypes.byref(tx), GEMV_K, 0.0, None, 0,
+                                         ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
 
-    def gemv_plain(i):
-        L.check(L.lib.nvfp4a_gemm(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(tws[i % nw]), GEMV_K, ctypes.byref(tx), GEMV_K, 0.0, None, 0,
-                                  ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
+        def gemv_plain(i):
+            L.check(L.lib.nvfp4a_gemm(GEMV_M, 1, GEMV_K, 1.0, ctypes.byref(tws[i % nw]), GEMV_K, ctypes.byref(tx), GEMV_K, 0.0, None, 0,
+                                      ctypes.byref(ty), GEMV_M, None, W.stream_ptr()))
 
-    gbytes = GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16
-    ms_gi, n1 = time_graph(gemv_image, 48, 7, 8, dist, world)
-    route_image = L.lib.nvfp4a_b200_last_route()
-    ms_gp, n2 = time_graph(gemv_plain, 48, 7, 8, dist, world)
-    route_plain = L.lib.nvfp4a_b200_last_route()
-    launches += n1 + n2
-    routes = {2: "mma.sync GEMV", 3: "FP4 tensor-core GEMV (tcgen05)"}
-    extra["gemv_8192_b1"] = hbm_entry("gemv_w4a16_8192x8192_b1_gbs", gbytes, ms_gi, world, peaks, traffic, "gemv_8192_dram_bytes",
-                                      "gemv_w4a16_m8192_k8192_n1", "8 rotating weights (302 MB) > L2", entry="nvfp4a_gemv_tc (weight image)",
-                                      kernel=routes.get(route_image), timing="CUDA graph of 48 calls, median of 7 replays",
-                                      plain_operand={"entry": "nvfp4a_gemm (linear scales)", "us_per_call": ms_gp * 1e3,
-                                                     "gbs": gbytes / (ms_gp * 1e-3) / 1e9, "kernel": routes.get(route_plain)})
-    del ws, tws, imgs
+        gbytes = GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16
+        ms_gi, n1 = time_graph(gemv_image, 48, 7, 8, dist, world)
+        route_image = L.lib.nvfp4a_b200_last_route()
+        ms_gp, n2 = time_graph(gemv_plain, 48, 7, 8, dist, world)
+        route_plain = L.lib.nvfp4a_b200_last_route()
+        launches += n1 + n2
+        routes = {2: "mma.sync GEMV", 3: "FP4 tensor-core GEMV (tcgen05)"}
+        extra["gemv_8192_b1"] = hbm_entry("gemv_w4a16_8192x8192_b1_gbs", gbytes, ms_gi, world, peaks, traffic, "gemv_8192_dram_bytes",
+                                          "gemv_w4a16_m8192_k8192_n1", "8 rotating weights (302 MB) > L2", entry="nvfp4a_gemv_tc (weight image)",
+                                          kernel=routes.get(route_image), timing="CUDA graph of 48 calls, median of 7 replays",
+                                          plain_operand={"entry": "nvfp4a_gemm (linear scales)", "us_per_call": ms_gp * 1e3,
+                                                         "gbs": gbytes / (ms_gp * 1e-3) / 1e9, "kernel": routes.get(route_plain)})
+        del ws, tws, imgs
     # ---- quantization 8192^2 BF16 -> NVFP4, swizzled scales: 3 inputs = 403 MB > L2 ----
-    nx = 3
-    xs = [W.outlier_input(QUANT_R, QUANT_C, 500 + s + 1000 * rank, dev) for s in range(nx)]
-    out = W.QuantizedMatrix(QUANT_R, QUANT_C, True, dev)
-    qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
-    ms_q, n1 = time_graph(lambda i: W.quantize_amax_swizzled(xs[i % nx], out), 24, 7, 5, dist, world)
-    ms_qg, n2 = time_graph(lambda i: W.quantize_given_amax(xs[i % nx], out), 24, 7, 5, dist, world)
-    launches += 3 * n1 + n2   # amax computed: memset + amax kernel + encode kernel per call
-    extra["quant_8192"] = hbm_entry("quantize_bf16_nvfp4_8192x8192_gbs", qbytes, ms_q, world, peaks, traffic, "quant_8192_dram_bytes",
-                                    "quantize_ex_8192x8192_bf16_swizzled_amax_computed", "3 rotating inputs (403 MB) > L2",
-                                    timing="CUDA graph of 24 calls, median of 7 replays",
-                                    note="amax computed by the call: the input is read twice, the second read is not credited",
-                                    amax_given={"us_per_call": ms_qg * 1e3, "gbs": qbytes / (ms_qg * 1e-3) / 1e9,
-                                                "frac": qbytes / (ms_qg * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                                "note": "global given (delayed scaling): one read, one write"})
-    del xs, out
+    if only in ("all", "quant"):
+        nx = 3
+        xs = [W.outlier_input(QUANT_R, QUANT_C, 500 + s + 1000 * rank, dev) for s in range(nx)]
+        out = W.QuantizedMatrix(QUANT_R, QUANT_C, True, dev)
+        qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
+        ms_q, n1 = time_graph(lambda i: W.quantize_amax_swizzled(xs[i % nx], out), 24, 7, 5, dist, world)
+        ms_qg, n2 = time_graph(lambda i: W.quantize_given_amax(xs[i % nx], out), 24, 7, 5, dist, world)
+        launches += 3 * n1 + n2   # amax computed: memset + amax kernel + encode kernel per call
+        extra["quant_8192"] = hbm_entry("quantize_bf16_nvfp4_8192x8192_gbs", qbytes, ms_q, world, peaks, traffic, "quant_8192_dram_bytes",
+                                        "quantize_ex_8192x8192_bf16_swizzled_amax_computed", "3 rotating inputs (403 MB) > L2",
+                                        timing="CUDA graph of 24 calls, median of 7 replays",
+                                        note="amax computed by the call: the input is read twice, the second read is not credited",
+                                        amax_given={"us_per_call": ms_qg * 1e3, "gbs": qbytes / (ms_qg * 1e-3) / 1e9,
+                                                    "frac": qbytes / (ms_qg * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                                    "note": "global given (delayed scaling): one read, one write"})
+        del xs, out
 
     # ---- fused transformer-MLP GEMMs (W4A16, extended epilogue) at 2048 tokens ----
-    if not args.no_mlp:
+    if not args.no_mlp and only in ("all", "mlp"):
         extra["mlp_w4a16"] = bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks)
         launches += extra["mlp_w4a16"].pop("_launches")
     # ---- tensor-parallel decoder linear stack ----
-    if not args.no_tp:
+    if not args.no_tp and only in ("all", "tp"):
         extra["tp_llama8b_linears"] = bench_tp(args, dev, rank, world, dist, stream, peaks)
         launches += extra["tp_llama8b_linears"].pop("_launches")
 
@@ -323,7 +326,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- CPU baseline beside it (rank 0, N = 1 only): bounded sample of the same GEMM through the oracle ----
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and only == "all":
         threads = os.cpu_count() or 1
         cols = 32
         cpu_gemm_sample(4, threads)
@@ -467,6 +470,8 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel linear stack extra")
     ap.add_argument("--no-tp-prefill", action="store_true", help="tensor-parallel extra: decode only")
     ap.add_argument("--tp-layers", type=int, default=32)
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "gemv", "quant", "mlp", "tp"],
+                    help="run one workload only (for profiling captures); the JSON line then lacks the others")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
