@@ -420,8 +420,11 @@ def bench_tp(args, dev, rank, world, dist, stream, peaks):
     layers = args.tp_layers
     stack = TPDecoderLinears(layers=layers, group=None, seed=4, device=dev)
     weights = 218103808 * layers   # values: QKV 6144 x 4096, O 4096 x 4096, gate / up 28672 x 4096, down 4096 x 14336
-    out = {"layers": layers, "world": world, "weight_bytes_per_rank": stack.weight_bytes_local(), "_launches": 0}
-    for T in (1, 8):
+    out = {"layers": layers, "world": world, "weight_bytes_per_rank": stack.weight_bytes_local(), "_launches": 0,
+           "collective": {"peer": "own all-gather over peer-mapped buffers (nvfp4a_b200_tp_gather)", "nccl": "all_gather_into_tensor",
+                          "none": "single rank"}[stack.collective]}
+
+    def decode(T, tag):
         g = torch.Generator(device=dev).manual_seed(40 + T)
         h = torch.randn((T, 4096), generator=g, device=dev).bfloat16()
         for _ in range(2):
@@ -441,10 +444,16 @@ def bench_tp(args, dev, rank, world, dist, stream, peaks):
         steps = 20
         ms = time_steps(step, steps, 3, stream, dist, world) / steps
         gbs = weights * 0.5625 / (ms * 1e-3) / 1e9
-        out[f"decode_{T}"] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "weight_gbs_all_ranks": gbs, "frac_of_hbm_all_ranks": gbs / (peaks["hbm_gbs"] * world),
-                              "cuda_graph": graph is not None}
+        out[tag] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "weight_gbs_all_ranks": gbs, "frac_of_hbm_all_ranks": gbs / (peaks["hbm_gbs"] * world),
+                    "cuda_graph": graph is not None}
         out["_launches"] += 4 * layers * (steps + 6)
-        del graph
+
+    decode(1, "decode_1")
+    decode(8, "decode_8")
+    if world > 1 and stack.collective == "peer":   # the same step with NCCL all-gathers, for comparison
+        stack.set_collective("nccl")
+        decode(1, "decode_1_nccl")
+        stack.set_collective("peer")
     if not args.no_tp_prefill:
         T = 4096
         g = torch.Generator(device=dev).manual_seed(44)

@@ -25,7 +25,7 @@ int nvfp4a_b200_set_route(int route);
 /* Health word of the tensor-core kernels (no counterpart in the reference, whose device-side waits are unbounded:
  * src/tensors/mma.cuh:108-114, src/tensors/gemm_tc.cuh:555 there).  Every wait inside this library's kernels gives up
  * after about a second; the kernel then records which wait it was (0x101 operands not delivered, 0x102 stage never
- * released, 0x103 accumulator never completed, 0x104 accumulator never drained, 0x105 scale gather) and returns.
+ * released, 0x103 accumulator never completed, 0x104 accumulator never drained, 0x105 scale gather; 0x2xx the FP4 GEMV, 0x3xx the W4A16 GEMM, 0x401 a peer missing at the tensor-parallel barrier) and returns.
  * This call SYNCHRONISES the device, copies the word to *status (0 = healthy) and clears it when reset != 0. */
 nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
 
@@ -42,6 +42,16 @@ int nvfp4a_b200_last_route(void);
  * value the problem cannot use (shared memory for the activation digit planes, k / 256) makes that GEMV step aside for the
  * mma.sync one.  A pinned value also lifts the size threshold below which the automatic choice prefers the mma.sync GEMV.  Tuning / test aid, no counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_gemv_splits(int splits);
+
+/* All-gather of a tensor-parallel layer's output over peer memory (no counterpart in the reference, which is single-GPU).
+ * buffers[p] / flags[p], p < world <= 8: the activation buffer [rows][row_pitch_bytes] and a flag array of 9 64-bit words
+ * (zero before the first use) as mapped on this GPU for every rank of the node (peer mappings of symmetric allocations;
+ * entry `rank` is local).  The rank's own columns [col_offset_bytes, + shard_bytes) of every row, already written locally,
+ * are stored into every peer's buffer (plain 16-byte stores over NVLink, no multicast), then the ranks meet in a barrier:
+ * after the call's kernels the complete matrix is in `buffers[rank]` on every rank.  Every rank must make the same
+ * sequence of calls.  The barrier's wait is bounded; nvfp4a_b200_kernel_status reports 0x401 if a peer never arrived. */
+nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
+                                    long long col_offset_bytes, long long shard_bytes, cudaStream_t stream);
 
 /* nvfp4a_gemm_ex that allocates nothing and still computes the RMSNorm column scales once per call: they are staged in a
  * 64 KiB device array inside the library image instead of a workspace.  No counterpart in the reference (its

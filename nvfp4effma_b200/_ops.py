@@ -263,3 +263,11 @@ def linear_tc(x_img, x_dtype, x_global, x_flags, x_smax, T, w_img, w_global, w_f
     if amax_out is not None:
         torch.maximum(amax_out, amax, out=amax_out)
     return out
+
+
+def tp_gather(buffer_ptrs, flag_ptrs, rank, rows, row_pitch_bytes, col_offset_bytes, shard_bytes):
+    """``nvfp4a_b200_tp_gather``: push this rank's columns of a peer-mapped activation buffer to every peer, then barrier."""
+    world = len(buffer_ptrs)
+    bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
+    flags = (ctypes.c_void_p * world)(*flag_ptrs)
+    L.check(L.lib.nvfp4a_b200_tp_gather(bufs, flags, world, rank, rows, row_pitch_bytes, col_offset_bytes, shard_bytes, _stream()))

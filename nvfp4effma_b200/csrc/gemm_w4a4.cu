@@ -34,7 +34,6 @@ struct W4A4Args {
   Epilogue e;
   unsigned *status;
   int d_tma;                   // D is stored by TMA from a shared-memory staging tile (needs 16-byte aligned D and column stride)
-  int dbg;                     // debugging: 1 skip tcgen05.cp, 2 skip mma, 4 skip stores, 8 skip epilogue tmem loads
 };
 
 template <int BN, int ACC, int STAGES>
@@ -51,8 +50,6 @@ struct W4A4Cfg {
 };
 
 constexpr int kThreads = 320;
-__device__ unsigned long long g_dbg_times[16];  // debugging (dbg & 32): cycles per role phase, summed over CTAs
-#define DBG_T(slot, expr) do { if (dbg & 32) { const long long t0_ = clock64(); expr; atomicAdd(&g_dbg_times[slot], (unsigned long long)(clock64() - t0_)); } else { expr; } } while (0)
 constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
                    kStatusWaitGather = 0x105;
 
@@ -70,7 +67,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t *staging = smem + STAGES * Cfg::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gm = g.m, gn = g.n, gk = g.k, dbg = g.dbg, ktiles = g.ktiles;
+  const int gm = g.m, gn = g.n, gk = g.k, ktiles = g.ktiles;
   const bool a_image = g.a_image, b_image = g.b_image, sa_gather = g.sa_gather, sb_gather = g.sb_gather, d_tma = g.d_tma;
   const uint8_t *const sa_base = g.sa, *const sb_base = g.sb;
   const int sa_ld = g.sa_ld, sb_ld = g.sb_ld;
@@ -113,7 +110,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % STAGES;
           bool okw;
-          DBG_T(0, okw = wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty));
+          okw = wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty);
           if (!okw) goto done;
           uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
           uint8_t *sA = st, *sB = st + Cfg::kABytes, *sSfa = sB + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
@@ -154,13 +151,13 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
         const int acc = tile_i % ACC;
         bool okw;
-        DBG_T(1, okw = wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty));
+        okw = wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty);
         if (!okw) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % STAGES;
-          DBG_T(2, okw = wait(&full[s], (it / STAGES) & 1, kStatusWaitFull));
+          okw = wait(&full[s], (it / STAGES) & 1, kStatusWaitFull);
           if (!okw) goto done;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
@@ -169,27 +166,13 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
           const int ng = min(4, (gk - ks * 256) / 64);
           const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
-          if (dbg & 256) {  // experiment: all scale copies of the stage first, then its MMAs
-            for (int j = 0; j < ng && !(dbg & 1); ++j) {
-              tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
+          // per 64 values of k: the scale tiles of that group, then its MMA (32 bytes further along each 128-byte row)
+          for (int j = 0; j < ng; ++j) {
+            tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
 #pragma unroll
-              for (int h = 0; h < BN / 128; ++h)
-                tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
-            }
-            for (int j = 0; j < ng && !(dbg & 2); ++j)
-              mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
-          } else {
-            // per 64 values of k: the scale tiles of that group, then its MMA (32 bytes further along each 128-byte row)
-            for (int j = 0; j < ng; ++j) {
-              if (!(dbg & 1)) {
-                tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
-#pragma unroll
-                for (int h = 0; h < BN / 128; ++h)
-                  tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
-              }
-              if (!(dbg & 2))
-                mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
-            }
+            for (int h = 0; h < BN / 128; ++h)
+              tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+            mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
           }
           tc_commit(&empty[s]);
         }
@@ -224,9 +207,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const float s_lane = __fmul_rn(__fmul_rn(rowp, colp0), gf);
       // the four epilogue warps decide together whether to go on: none may be left alone at a named barrier
       bool okw;
-      DBG_T(3, okw = wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull));
+      okw = wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull);
       if (!okw) *abort_flag = 1;
-      const long long tep0 = clock64();
       named_barrier(1, 128);
       if (*abort_flag) goto done;
       tc_fence_after();
@@ -240,7 +222,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         }
-        if (dbg & 4) continue;
         const int j0 = tn * BN + c * 32;
         const int nvalid = min(32, gn - j0);
         // values before rounding, kept in r[] as FP32 bits
@@ -312,7 +293,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
-      if ((dbg & 32) && warp == 2 && lane == 0) atomicAdd(&g_dbg_times[4], (unsigned long long)(clock64() - tep0));
     }
     if (leader) bulk_wait_all();
     if (amax_out) warp_amax_commit(amax_out, amax);
@@ -431,8 +411,6 @@ static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, cons
   return cudaGetLastError();
 }
 
-static int g_w4a4_dbg = 0;
-void set_w4a4_dbg(int d) { g_w4a4_dbg = d; }
 static int g_w4a4_bn = 0;  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
 void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
 
@@ -443,7 +421,6 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   a.e = g.e;
   a.status = kernel_status_device_ptr();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
-  a.dbg = g_w4a4_dbg;
   const int bn = g_w4a4_bn ? g_w4a4_bn : (g.n > 128 ? 256 : 128);
   CUtensorMap ta, tb;
   const Fp4Operand &A = g.A, &B = g.B.q;
@@ -467,7 +444,7 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   CUtensorMap td;
   memset(&td, 0, sizeof td);
   const int esz = dense_bytes(g.e.d_dtype);
-  a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 && !(g_w4a4_dbg & 16) &&
+  a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
             make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
   if (bn == 256) return launch_cfg<256, 1, 4>(ta, tb, td, a, s);
   return launch_cfg<128, 2, 6>(ta, tb, td, a, s);
@@ -484,13 +461,6 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
   cudaError_t e = cudaMemcpy(status, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && reset) e = cudaMemset(p, 0, sizeof(unsigned int));
   return cuda_fail(e, "nvfp4a_b200_kernel_status");
-}
-
-extern "C" void nvfp4a_b200_debug(int d) { nvb::set_w4a4_dbg(d); }
-extern "C" void nvfp4a_b200_debug_times(unsigned long long *out16, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, nvb::g_dbg_times, sizeof(unsigned long long) * 16);
-  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(nvb::g_dbg_times, z, sizeof z); }
 }
 
 extern "C" int nvfp4a_b200_set_tile_n(int bn) {

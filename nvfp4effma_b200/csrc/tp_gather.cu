@@ -1,0 +1,119 @@
+// All-gather of a tensor-parallel layer's output over peer memory: every rank has written its own columns of the activation
+// matrix [T][M] (row pitch M elements) into its local copy of a buffer that exists at the same place on every GPU of the
+// node (peer-mapped); this kernel copies those columns into every peer's copy with plain 16-byte stores over NVLink and
+// then runs a barrier among the ranks on flags in the same kind of memory, so that after it the whole matrix is present
+// everywhere -- one launch instead of an NCCL all-gather plus a reassembly copy.  There are no multicast loads or stores.
+//
+// Barrier: rank r bumps its epoch (a counter in its own memory, so that a replayed CUDA graph keeps counting), fences,
+// writes the epoch into slot r of every peer's flag array and waits until all slots of its own array have reached the
+// epoch.  The wait is bounded (about a second of SM clock); on expiry the kernel records code 0x401 in the kernel status
+// word and returns.  Copies larger than one CTA handles well are split into a copy launch and a one-CTA barrier launch.
+// Ranks live on different GPUs: kernels that wait on one another must never share a GPU.
+#include "operands.cuh"
+#include "sm100.cuh"
+
+namespace nvb {
+
+constexpr int kMaxRanks = 8;
+struct TpGatherArgs {
+  uint8_t *buf[kMaxRanks];                 // the activation buffer on every rank (buf[rank] is local)
+  unsigned long long *flags[kMaxRanks];    // flag array (kMaxRanks slots + the epoch counter at slot kMaxRanks) on every rank
+  int world, rank;
+  int rows;                                // T
+  long long row_pitch_bytes, col_offset_bytes, shard_bytes;  // this rank's columns: [col_offset, col_offset + shard_bytes) of every row
+  unsigned *status;
+  int copy, barrier;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(1024) tp_gather_kernel(const TpGatherArgs a) {
+  if (a.copy) {
+    const long long vec_per_row = a.shard_bytes >> 4;   // 16-byte vectors (the shard is a multiple of 128 elements)
+    const long long total = vec_per_row * a.rows;
+    const uint8_t *src = a.buf[a.rank];
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+      const long long r = v / vec_per_row, c = v - r * vec_per_row;
+      const long long off = r * a.row_pitch_bytes + a.col_offset_bytes + (c << 4);
+      const uint4 x = *(const uint4 *)(src + off);
+      for (int p = 0; p < a.world; ++p)
+        if (p != a.rank) *(uint4 *)(a.buf[p] + off) = x;
+    }
+    __threadfence_system();
+  }
+  if (!a.barrier) return;
+  __syncthreads();
+  __shared__ unsigned long long epoch_s;
+  unsigned long long *mine = a.flags[a.rank];
+  if (threadIdx.x == 0) {
+    epoch_s = mine[kMaxRanks] + 1;
+    mine[kMaxRanks] = epoch_s;
+  }
+  __syncthreads();
+  const unsigned long long epoch = epoch_s;
+  if ((int)threadIdx.x < a.world) {
+    const int p = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(a.flags[p] + a.rank, epoch);      // slot `rank` on peer p (p == rank: my own slot)
+    const long long start = clock64();
+    while (ld_acquire_sys(mine + p) < epoch) {
+      if (clock64() - start > 2000000000ll) {       // about a second: a peer never arrived
+        atomicCAS(a.status, 0u, 0x401u);
+        break;
+      }
+    }
+  }
+}
+
+}  // namespace nvb
+
+using namespace nvb;
+
+// buffers / flags: `world` device pointers each (peer mappings of one symmetric allocation; entry `rank` is local).
+// The shard is columns [col_offset_bytes, col_offset_bytes + shard_bytes) of each of `rows` rows of row_pitch_bytes; all
+// three are multiples of 16.  The flag array holds 9 unsigned 64-bit words, zero before the first use and owned by this
+// function afterwards.
+extern "C" nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
+                                               long long col_offset_bytes, long long shard_bytes, cudaStream_t stream) {
+  const char *fn = "nvfp4a_b200_tp_gather";
+  clear_error();
+  if (!buffers || !flags || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(NVFP4A_INVALID_VALUE, "%s: needs buffers, flags and 0 <= rank < world <= %d", fn, kMaxRanks);
+  if (rows < 0 || row_pitch_bytes < 0 || ((row_pitch_bytes | col_offset_bytes | shard_bytes) & 15) || col_offset_bytes < 0 || shard_bytes < 0 ||
+      col_offset_bytes + shard_bytes > row_pitch_bytes)
+    return fail(NVFP4A_INVALID_VALUE, "%s: pitch, offset and shard bytes must be non-negative multiples of 16 with the shard inside a row", fn);
+  if (nvfp4a_status st = check_device()) return st;
+  TpGatherArgs a;
+  memset(&a, 0, sizeof a);
+  for (int p = 0; p < world; ++p) {
+    if (!buffers[p] || !flags[p] || ((uintptr_t)buffers[p] & 15) || ((uintptr_t)flags[p] & 7))
+      return fail(NVFP4A_INVALID_VALUE, "%s: buffer / flag pointer of rank %d is NULL or misaligned", fn, p);
+    a.buf[p] = (uint8_t *)buffers[p];
+    a.flags[p] = (unsigned long long *)flags[p];
+  }
+  a.world = world; a.rank = rank; a.rows = rows;
+  a.row_pitch_bytes = row_pitch_bytes; a.col_offset_bytes = col_offset_bytes; a.shard_bytes = shard_bytes;
+  a.status = kernel_status_device_ptr();
+  const long long bytes = (long long)rows * shard_bytes * (world - 1);
+  if (world == 1) return NVFP4A_OK;
+  if (bytes <= (1 << 20)) {   // one CTA copies and joins the barrier
+    a.copy = 1; a.barrier = 1;
+    tp_gather_kernel<<<1, 1024, 0, stream>>>(a);
+  } else {
+    a.copy = 1; a.barrier = 0;
+    const long long vecs = (long long)rows * (shard_bytes >> 4);
+    long long grid = (vecs + 1023) / 1024;
+    const int cap = device_sms() * 2;
+    tp_gather_kernel<<<(int)(grid < cap ? grid : cap), 1024, 0, stream>>>(a);
+    a.copy = 0; a.barrier = 1;
+    tp_gather_kernel<<<1, 32, 0, stream>>>(a);
+  }
+  return cuda_fail(cudaGetLastError(), fn);
+}

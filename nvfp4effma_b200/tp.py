@@ -69,14 +69,46 @@ def gather_features(y_shard: torch.Tensor, group=None, out: Optional[torch.Tenso
     return out
 
 
+class PeerGather:
+    """Activation buffers that exist at the same place on every GPU of the node (torch symmetric memory: peer-mapped device
+    memory) and the library's own all-gather over them: a rank writes its columns of ``y`` into its local buffer, one launch
+    stores them into every peer's buffer over NVLink and joins a barrier (``nvfp4a_b200_tp_gather``).  Two buffers alternate
+    between consecutive layers: a rank that runs ahead writes the buffer its peers have finished reading (they passed the
+    previous barrier)."""
+
+    def __init__(self, group, max_elems: int, device):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        try:
+            symm.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.bufs = [symm.empty(max_elems, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.flags = symm.empty(16, dtype=torch.int64, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        self.buf_ptrs = [list(symm.rendezvous(b, group).buffer_ptrs) for b in self.bufs]
+        self.flag_ptrs = list(symm.rendezvous(self.flags, group).buffer_ptrs)
+        dist.barrier(group)   # every rank's flags are zero before anyone signals
+
+    def view(self, slot: int, T: int, M: int) -> torch.Tensor:
+        return self.bufs[slot][:T * M].view(T, M)
+
+    def push(self, slot: int, T: int, M: int, col0: int, cols: int):
+        _ops.tp_gather(self.buf_ptrs[slot], self.flag_ptrs, self.rank, T, M * 2, col0 * 2, cols * 2)
+
+
 class TPLinear:
     """One rank's part of ``y = x @ W.T + bias`` (optionally ``silu(gate) * up`` of interleaved gate / up rows).
 
     Holds the image of its rows of ``W`` (built once), the shared global and its part of the bias.  ``forward`` takes the
     replicated ``x`` [T, K] (bfloat16) and returns the full ``y``; ``forward_local`` returns this rank's columns only."""
 
-    def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False):
+    def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False,
+                 gather: Optional["PeerGather"] = None):
         self.group = group
+        self.gather = gather
         solo = replicate or not dist.is_initialized()  # replicate: the whole weight on this rank, no collective
         self.world = 1 if solo else dist.get_world_size(group)
         self.rank = 0 if solo else dist.get_rank(group)
@@ -103,9 +135,16 @@ class TPLinear:
         return _ops.linear_tc(xi, 2, None, 0, 0, T, self.image, self.global_scale, self.flags, self.scale_max, self.rows, self.in_features,
                               self.bias, torch.bfloat16, out, swiglu=self.swiglu)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.forward_local(x)
-        return y if self.world == 1 else gather_features(y, self.group)
+    def forward(self, x: torch.Tensor, slot: int = 0) -> torch.Tensor:
+        if self.world == 1:
+            return self.forward_local(x)
+        if self.gather is None:
+            return gather_features(self.forward_local(x), self.group)
+        T, nl, M = x.shape[0], self.rows // (2 if self.swiglu else 1), self.out_features
+        y = self.gather.view(slot, T, M)
+        self.forward_local(x, out=y[:, self.rank * nl:(self.rank + 1) * nl])
+        self.gather.push(slot, T, M, self.rank * nl, nl)
+        return y
 
     __call__ = forward
 
@@ -116,8 +155,14 @@ class TPDecoderLinears:
     Attention, norms and residuals are not part of this path: O reads the first ``hidden`` features of the QKV output."""
 
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
-                 device="cuda", std: float = 0.02, replicate: bool = False):
+                 device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096):
+        """``collective``: "peer" = the library's all-gather over peer-mapped buffers, "nccl" = ``all_gather_into_tensor``."""
         self.hidden, self.layers = hidden, []
+        multi = dist.is_initialized() and dist.get_world_size(group) > 1 and not replicate
+        self.collective = collective if multi else "none"
+        gather = PeerGather(group, max_tokens * max(hidden, intermediate, qkv), device) if multi and collective == "peer" else None
+        self.max_tokens = max_tokens
+        self._gather = gather
         from .api import quantize
         for layer in range(layers):
             mods = []
@@ -126,17 +171,28 @@ class TPDecoderLinears:
                 gen = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 4 + j)  # the same weights on every rank
                 w = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
                 amax = w.abs().amax().float().reshape(1)
-                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate))
+                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate, gather=gather))
                 del w
             self.layers.append(mods)
+
+    def set_collective(self, collective: str):
+        """Switch between the peer-memory all-gather ("peer", if the stack was built with it) and NCCL ("nccl")."""
+        if self.collective == "none":
+            return
+        for layer in self.layers:
+            for m in layer:
+                m.gather = self._gather if collective == "peer" else None
+        self.collective = collective
 
     def weight_bytes_local(self) -> int:
         return sum(m.image.numel() for layer in self.layers for m in layer)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        for qkv, o, gate_up, down in self.layers:
-            a = qkv(h)[:, :self.hidden]
-            h = down(gate_up(o(a)))
+        if self.collective == "peer" and h.shape[0] > self.max_tokens:
+            raise ValueError(f"{h.shape[0]} tokens exceed the peer buffers ({self.max_tokens})")
+        for qkv, o, gate_up, down in self.layers:   # consecutive layers alternate between the two peer buffers
+            a = qkv(h, 0)[:, :self.hidden]
+            h = down(gate_up(o(a, 1), 0), 1)
         return h
 
     __call__ = forward

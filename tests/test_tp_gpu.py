@@ -57,12 +57,16 @@ rank = int(os.environ["RANK"]); torch.cuda.set_device(rank)
 dist.init_process_group("nccl", rank=rank, world_size=int(os.environ["WORLD_SIZE"]), device_id=torch.device("cuda", rank))
 from nvfp4effma_b200.tp import TPDecoderLinears
 kw = dict(layers=2, hidden=256, intermediate=512, qkv=512, std=0.06)
-tp, solo = TPDecoderLinears(**kw), TPDecoderLinears(replicate=True, **kw)
-ok = True
-for T in (1, 5, 48):
-    g = torch.Generator(device="cpu").manual_seed(T)
-    x = torch.randn((T, 256), generator=g).cuda().bfloat16()
-    ok = ok and torch.equal(tp(x), solo(x))
+peer, nccl, solo = TPDecoderLinears(collective="peer", max_tokens=64, **kw), TPDecoderLinears(collective="nccl", **kw), TPDecoderLinears(replicate=True, **kw)
+ok = peer.collective == "peer" and nccl.collective == "nccl"
+for rep in range(2):
+    for T in (1, 5, 48):
+        g = torch.Generator(device="cpu").manual_seed(T)
+        x = torch.randn((T, 256), generator=g).cuda().bfloat16()
+        want = solo(x)
+        ok = ok and torch.equal(peer(x).clone(), want) and torch.equal(nccl(x), want)
+from nvfp4effma_b200 import workloads
+ok = ok and workloads.kernel_status() == 0
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
 print("RANK_OK" if ok else "RANK_MISMATCH", flush=True)
 """
