@@ -41,17 +41,18 @@ struct W4A4Cfg {
   static constexpr int kABytes = 128 * 128, kBBytes = BN * 128, kSfaBytes = 2048, kSfbBytes = BN * 16;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kSfCols = 16 + BN / 8;      // per scale buffer: A 4 groups x 4 columns, B 4 groups x BN / 32 columns
-  static constexpr int kSfBuffers = 2;
+  static constexpr int kSfBuffers = STAGES;        // one per pipeline stage
   static constexpr int kAccCols = ACC * BN;
   static constexpr int kTmemCols = 512;
   static constexpr int kStagingBytes = 8192;       // epilogue staging: 128 rows x 32 (16-bit) or 16 (32-bit) columns
   static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kStagingBytes;
+  static_assert((3 * STAGES + 2 * ACC) * 8 + 8 <= 256, "barrier block");
   static_assert(kAccCols + kSfBuffers * kSfCols <= kTmemCols, "tensor memory budget");
 };
 
 constexpr int kThreads = 320;
 constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
-                   kStatusWaitGather = 0x105;
+                   kStatusWaitGather = 0x105, kStatusWaitSf = 0x106;
 
 template <int BN, int ACC, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -61,8 +62,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + STAGES * Cfg::kStageBytes);
-  uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + ACC;
-  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 2 * ACC);
+  uint64_t *full = bars, *empty = bars + STAGES, *sf_ready = bars + 2 * STAGES, *tmem_full = bars + 3 * STAGES, *tmem_empty = tmem_full + ACC;
+  uint32_t *tmem_slot = (uint32_t *)(tmem_empty + ACC);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
   uint8_t *staging = smem + STAGES * Cfg::kStageBytes + 256;
 
@@ -76,7 +77,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool any_gather = sa_gather || sb_gather;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 4); }
     for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -157,21 +158,25 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % STAGES;
-          okw = wait(&full[s], (it / STAGES) & 1, kStatusWaitFull);
+          // tiled scales: four warps have put the stage's scale columns into tensor memory (which implies the operands landed);
+          // gathered scales: this thread copies them from shared memory itself
+          okw = any_gather ? wait(&full[s], (it / STAGES) & 1, kStatusWaitFull) : wait(&sf_ready[s], (it / STAGES) & 1, kStatusWaitSf);
           if (!okw) goto done;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
           const uint32_t sA = st, sB = st + Cfg::kABytes, sSfa = sB + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;
-          const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + (it % Cfg::kSfBuffers) * Cfg::kSfCols;
+          const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + s * Cfg::kSfCols;
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
           const int ng = min(4, (gk - ks * 256) / 64);
           const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
-          // per 64 values of k: the scale tiles of that group, then its MMA (32 bytes further along each 128-byte row)
+          // per 64 values of k: (the scale tiles of that group, then) its MMA, 32 bytes further along each 128-byte row
           for (int j = 0; j < ng; ++j) {
-            tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
+            if (any_gather) {
+              tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
 #pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+              for (int h = 0; h < BN / 128; ++h)
+                tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
+            }
             mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
           }
           tc_commit(&empty[s]);
@@ -296,7 +301,44 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     if (leader) bulk_wait_all();
     if (amax_out) warp_amax_commit(amax_out, amax);
-  } else if (any_gather) {
+  } else if (!any_gather) {
+    // ---------------- scale warps: the stage's 512-byte scale tiles, shared memory -> registers -> tensor memory ----------------
+    // A tile's 16 bytes at offset 16 l are what lane l of every quadrant holds in four scale columns (the layout
+    // tcgen05.cp.32x128b.warpx4 would produce); each of the four warps writes its own quadrant, off the MMA issuer's queue.
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        const int s = it % STAGES;
+        if (!wait(&full[s], (it / STAGES) & 1, kStatusWaitGather)) goto done;
+        const uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
+        const uint8_t *sSfa = st + Cfg::kABytes + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
+        const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + s * Cfg::kSfCols + lane_base;
+        const int ng = min(4, (gk - ks * 256) / 64);
+        uint32_t r[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = j < ng ? *(const uint4 *)(sSfa + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
+          r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+        }
+        tmem_st16(sf_tmem, r);
+#pragma unroll
+        for (int part = 0; part < BN / 128; ++part) {   // B: group j occupies BN / 32 columns: [half 0: 4 | half 1: 4]
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {                 // register quad q of this part = columns 4 q .. 4 q + 3 of the 16
+            const int col = part * 16 + 4 * q, j = col / (BN / 32), h = (col % (BN / 32)) / 4;
+            const uint4 v = j < ng ? *(const uint4 *)(sSfb + h * 2048 + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
+            r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+          }
+          tmem_st16(sf_tmem + 16 + part * 16, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_ready[s]);
+      }
+    }
+  } else {
     // ---------------- scale gather: linear / unaligned block scales -> 512-byte tiles in shared memory ----------------
     // Warp w of the four takes the pipeline iterations it % 4 == w, so four stages' loads are in flight together.
     const int w = warp - 6;
