@@ -9,9 +9,10 @@ extern "C" {
 
 /* Self-test of the hardware FP32 -> E2M1 / E4M3 conversions the quantizer uses (no counterpart in the reference, whose
  * encoders are software; the reference proves its own exhaustively in tests/test_nvfp4effma.cu:487-495).  Adds to
- * mismatches[0..2] (device, 3 x unsigned long long, zeroed by the caller) the number of FP32 bit patterns in
+ * mismatches[0..3] (device, 4 x unsigned long long, zeroed by the caller) the number of FP32 bit patterns in
  * [first, first + count) on which the hardware conversion differs from the software encoder: [0] E2M1 in the low
- * nibble, [1] E2M1 in the high nibble, [2] E4M3.  NaN inputs are skipped. */
+ * nibble, [1] E2M1 in the high nibble, [2] E4M3 (NaN inputs are skipped for these three), [3] the packed FP32 -> BF16 rounding
+ * of the GEMM epilogues against the software rounding (NaN -> 0x7FC0 included). */
 nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long long count, unsigned long long *mismatches,
                                          cudaStream_t stream);
 

@@ -81,6 +81,27 @@ __host__ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
   return (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;
 }
 
+// 32 FP32 values (bit patterns in r[]) -> BF16 bit patterns in the low halves of r[], round to nearest even, NaN -> 0x7FC0:
+// the same results as f32_to_bf16_bits, by the hardware's packed conversion (16 instructions with short dependency chains
+// instead of 32 chains of integer arithmetic; the epilogues of the tensor-core GEMMs run on one warp per scheduler, where
+// chain latency is what costs).  The conversion turns every NaN into 0x7FFF, which no other input produces.
+__device__ __forceinline__ void round32_to_bf16(uint32_t (&r)[32]) {
+  uint32_t nan = 0;
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(r[2 * q + 1])), "f"(__uint_as_float(r[2 * q])));
+    nan |= (d & 0x7FFF7FFFu) + 0x00010001u;   // a half that was 0x7FFF carries into its top bit
+    r[2 * q] = d & 0xFFFFu;
+    r[2 * q + 1] = d >> 16;
+  }
+  if (nan & 0x80008000u) {
+#pragma unroll
+    for (int jj = 0; jj < 32; ++jj)
+      if ((r[jj] & 0x7FFFu) == 0x7FFFu) r[jj] = 0x7FC0u;
+  }
+}
+
 // ---- block scale addressing ----------------------------------------------------------------------------------------
 // ld > 0: linear, ld scales per row.  ld < 0: swizzled 128 x 4 tiles, -ld = padded scale columns.
 struct ScalePos {

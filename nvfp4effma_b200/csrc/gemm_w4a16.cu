@@ -328,8 +328,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
             if (jj < nvalid) amax = fmaxf(amax, fabsf(__uint_as_float(r[jj])));
         }
         if (d_dtype == NVFP4A_BF16) {
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) r[jj] = f32_to_bf16_bits(__uint_as_float(r[jj]));
+          round32_to_bf16(r);
         } else if (d_dtype == NVFP4A_FP16) {
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) r[jj] = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(r[jj])));

@@ -218,15 +218,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (*abort_flag) goto done;
       tc_fence_after();
       const int nchunks = min(BN / 32, (gn - tn * BN + 31) / 32);
-      for (int c = 0; c < nchunks; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        if (c == nchunks - 1) {  // accumulator drained into registers: the MMA warp may start the next tile on it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-        }
+      // The accumulator leaves tensor memory 32 columns at a time; the load of the next 32 is in flight while these are
+      // scaled, rounded and staged (two register sets alternate).
+      auto drain = [&](uint32_t (&r)[32], int c) {
         const int j0 = tn * BN + c * 32;
         const int nvalid = min(32, gn - j0);
         // values before rounding, kept in r[] as FP32 bits
@@ -257,8 +251,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         // rounding to the output type (in place, low bits of r[])
         if (d_dtype == NVFP4A_BF16) {
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) r[jj] = f32_to_bf16_bits(__uint_as_float(r[jj]));
+          round32_to_bf16(r);
         } else if (d_dtype == NVFP4A_FP16) {
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) r[jj] = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(r[jj])));
@@ -277,7 +270,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (jj < nvalid) d32[(size_t)jj * ldd] = r[jj];
             }
           }
-          continue;
+          return;
         }
         for (int half = 0; half < 32 / cw; ++half) {
           if (leader) bulk_wait_read_all();   // the previous store has finished reading the staging tile
@@ -296,6 +289,26 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tma_store_2d(&tmap_d, staging, tm * 128, j0 + half * cw);
             bulk_commit();
           }
+        }
+      };
+      const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      auto release_acc = [&]() {  // every column is in registers: the MMA warp may start the next tile on this accumulator
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      };
+      uint32_t ra[32], rb[32];
+      tmem_ld32(acc_addr, ra);
+      for (int c = 0; c < nchunks; c += 2) {
+        tmem_ld_wait();
+        if (c + 1 < nchunks) tmem_ld32(acc_addr + (c + 1) * 32, rb);
+        else release_acc();
+        drain(ra, c);
+        if (c + 1 < nchunks) {
+          tmem_ld_wait();
+          if (c + 2 < nchunks) tmem_ld32(acc_addr + (c + 2) * 32, ra);
+          else release_acc();
+          drain(rb, c + 1);
         }
       }
     }

@@ -695,12 +695,25 @@ extern "C" nvfp4a_status nvfp4a_transpose(const nvfp4a_tensor *src, int lds, con
 // ---- self-test of the hardware conversions -------------------------------------------------------------------------------------
 // Counts, over FP32 bit patterns [first, first + count), the inputs on which cvt.rn.satfinite.{e2m1x2,e4m3x2}.f32 and the
 // software encoders disagree (NaN inputs excluded: outside the quantizer's contract).  out[0]: E2M1 as the low nibble,
-// out[1]: E2M1 as the high nibble, out[2]: E4M3.
+// out[1]: E2M1 as the high nibble, out[2]: E4M3, out[3]: the packed BF16 rounding of the GEMM epilogues (NaN included).
 __global__ void codec_selftest_kernel(unsigned long long first, unsigned long long count, unsigned long long *out) {
-  unsigned long long bad0 = 0, bad1 = 0, bad2 = 0;
+  unsigned long long bad0 = 0, bad1 = 0, bad2 = 0, bad3 = 0;
   for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
        i += (unsigned long long)gridDim.x * blockDim.x) {
     const uint32_t u = (uint32_t)(first + i);
+    {
+      uint32_t r[32];
+#pragma unroll
+      for (int q = 0; q < 32; ++q) r[q] = (q & 1) ? u : (u ^ (uint32_t)q * 0x01010101u);
+      uint32_t want[32];
+#pragma unroll
+      for (int q = 0; q < 32; ++q) want[q] = nvb::f32_to_bf16_bits(__uint_as_float(r[q]));
+      nvb::round32_to_bf16(r);
+      bool bad = false;
+#pragma unroll
+      for (int q = 0; q < 32; ++q) bad |= r[q] != want[q];
+      bad3 += bad;
+    }
     if ((u & 0x7FFFFFFFu) > 0x7F800000u) continue;
     const float x = __uint_as_float(u);
     float v[8] = {x, 1.0f, -3.0f, x, 0.f, 0.f, 0.f, 0.f};
@@ -712,6 +725,7 @@ __global__ void codec_selftest_kernel(unsigned long long first, unsigned long lo
   if (bad0) atomicAdd(out, bad0);
   if (bad1) atomicAdd(out + 1, bad1);
   if (bad2) atomicAdd(out + 2, bad2);
+  if (bad3) atomicAdd(out + 3, bad3);
 }
 extern "C" nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long long count, unsigned long long *mismatches,
                                                     cudaStream_t stream) {
