@@ -45,7 +45,7 @@ int nvfp4a_b200_last_route(void);
 int nvfp4a_b200_set_gemv_splits(int splits);
 
 /* All-gather of a tensor-parallel layer's output over peer memory (no counterpart in the reference, which is single-GPU).
- * buffers[p] / flags[p], p < world <= 8: the activation buffer [rows][row_pitch_bytes] and a flag array of 9 64-bit words
+ * buffers[p] / flags[p], p < world <= 8: the activation buffer [rows][row_pitch_bytes] and a flag array of 16 64-bit words
  * (zero before the first use) as mapped on this GPU for every rank of the node (peer mappings of symmetric allocations;
  * entry `rank` is local).  The rank's own columns [col_offset_bytes, + shard_bytes) of every row, already written locally,
  * are stored into every peer's buffer (plain 16-byte stores over NVLink, no multicast), then the ranks meet in a barrier:
@@ -53,6 +53,15 @@ int nvfp4a_b200_set_gemv_splits(int splits);
  * sequence of calls.  The barrier's wait is bounded; nvfp4a_b200_kernel_status reports 0x401 if a peer never arrived. */
 nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
                                     long long col_offset_bytes, long long shard_bytes, cudaStream_t stream);
+
+/* nvfp4a_gemv_tc / nvfp4a_gemv_tc_ex (beta = 0) of one rank of a tensor-parallel group with the all-gather fused into the
+ * kernel (no counterpart in the reference): D->data points into buffers[rank]; every output is also stored at the same place
+ * of each peer's buffer (plain peer stores), and the kernel's last CTA joins the ranks' barrier of nvfp4a_b200_tp_gather
+ * (same buffers / flags, same rules).  When the problem runs on another kernel than the mma.sync GEMV, the push is a
+ * second launch; the result is the same.  ex may be NULL; a second output (d2) is not supported here. */
+nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
+                                     const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
+                                     void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream);
 
 /* nvfp4a_gemm_ex that allocates nothing and still computes the RMSNorm column scales once per call: they are staged in a
  * 64 KiB device array inside the library image instead of a workspace.  No counterpart in the reference (its

@@ -271,3 +271,22 @@ def tp_gather(buffer_ptrs, flag_ptrs, rank, rows, row_pitch_bytes, col_offset_by
     bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
     flags = (ctypes.c_void_p * world)(*flag_ptrs)
     L.check(L.lib.nvfp4a_b200_tp_gather(bufs, flags, world, rank, rows, row_pitch_bytes, col_offset_bytes, shard_bytes, _stream()))
+
+
+def gemv_tp(x, w_img, w_rows, w_global, w_flags, w_smax, k, bias, out, swiglu, buffer_ptrs, flag_ptrs, rank):
+    """``nvfp4a_b200_gemv_tc_tp``: up to 8 rows of bfloat16 ``x`` against a weight image; ``out`` (a view into this rank's
+    peer-mapped buffer) is also written into every peer's buffer and the ranks meet in a barrier."""
+    T = x.shape[0]
+    x = _rows_2d(x, 64, "x")
+    world = len(buffer_ptrs)
+    bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
+    flags = (ctypes.c_void_p * world)(*flag_ptrs)
+    tA = L.Tensor(_ptr(w_img), L.NVFP4, None, 0, _ptr(w_global), None, w_flags, w_smax)
+    tB = L.Tensor(_ptr(x), L.BF16, None, 0, None, None, 0, 0)
+    tD = L.Tensor(_ptr(out), _dense_code(out.dtype), None, 0, None, None, 0, 0)
+    tbias = L.Tensor(_ptr(bias), _dense_code(bias.dtype), None, 0, None, None, 0, 0) if bias is not None else None
+    ex = L.Epilogue()
+    ex.swiglu = int(bool(swiglu))
+    L.check(L.lib.nvfp4a_b200_gemv_tc_tp(w_rows, T, k, 1.0, ctypes.byref(tA), ctypes.byref(tB), x.stride(0), ctypes.byref(tD), out.stride(0),
+                                         ctypes.byref(tbias) if tbias is not None else None, ctypes.byref(ex), bufs, flags, world, rank, _stream()))
+    return out

@@ -95,6 +95,9 @@ static thread_local int g_last_route = 0;
 // small kernel fills it before the GEMM, a memset restores the zeros after it); the other tensor-core calls leave it alone.
 constexpr int kWorkspaceTokens = 16384;
 
+extern "C" nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
+                                               long long col_offset_bytes, long long shard_bytes, cudaStream_t stream);
+
 static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t stream) {
   cudaError_t err;
   const bool gemv = g.k == 0 || g.n <= kGemvMaxN;
@@ -104,6 +107,15 @@ static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t st
   else if (!gemv && gemm_w4a4_supports(g)) { g_last_route = 4; err = launch_gemm_w4a4(g, stream); }
   else if (!gemv && gemm_w4a16_supports(g)) { g_last_route = 5; err = launch_gemm_w4a16(g, stream); }
   else { g_last_route = 1; err = launch_gemm_generic(g, stream); }
+  if (err == cudaSuccess && g.tp.world > 1 && g_last_route != 2) {
+    // only the mma.sync GEMV pushes its results to the peers itself; after any other kernel a copy launch does it
+    void *bufs[kMaxRanks], *flags[kMaxRanks];
+    for (int p = 0; p < g.tp.world; ++p) { bufs[p] = g.tp.local_base + g.tp.delta[p]; flags[p] = g.tp.flags[p]; }
+    const int esz = dense_bytes(g.e.d_dtype);
+    const long long drows = (g.x.mask & kExSwiglu) ? g.m / 2 : g.m;
+    return nvfp4a_b200_tp_gather(bufs, flags, g.tp.world, g.tp.rank, g.n, (long long)g.e.ldd * esz, (long long)((uint8_t *)g.e.d - g.tp.local_base),
+                                 drows * esz, stream);
+  }
   return cuda_fail(err, fn);
 }
 
@@ -230,7 +242,7 @@ static nvfp4a_status gemm_tc_run(const char *fn, int m, int n, int k, float alph
 
 static nvfp4a_status gemv_tc_run(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
                                  float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias,
-                                 const EpilogueEx &ex, cudaStream_t stream) {
+                                 const EpilogueEx &ex, cudaStream_t stream, const TpPush *tp = nullptr) {
   if (!A || !B || !D || !A->data || !B->data || !D->data) return fail(NVFP4A_INVALID_VALUE, "%s: A, B or D (or its data pointer) is NULL", fn);
   if (m < 0 || k < 0 || n < 1 || n > 8) return fail(NVFP4A_INVALID_VALUE, "%s: m = %d, n = %d, k = %d (needs 1 <= n <= 8)", fn, m, n, k);
   if (A->dtype != NVFP4A_NVFP4) return fail(NVFP4A_NOT_SUPPORTED, "%s: A must be NVFP4 (dtype %d)", fn, (int)A->dtype);
@@ -266,6 +278,7 @@ static nvfp4a_status gemv_tc_run(const char *fn, int m, int n, int k, float alph
   g.B = make_b(B, ldb, ldsb, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
+  if (tp) g.tp = *tp;
   return dispatch(fn, g, stream);
 }
 
@@ -457,4 +470,30 @@ extern "C" nvfp4a_status nvfp4a_gemv_tc_ex(int m, int n, int k, float alpha, con
   EpilogueEx x;
   if (nvfp4a_status st = make_epilogue_ex("nvfp4a_gemv_tc_ex", ex, m, beta, ldd, &x)) return st;
   return gemv_tc_run("nvfp4a_gemv_tc_ex", m, n, k, alpha, A, B, ldb, beta, C, ldc, D, ldd, bias, x, stream);
+}
+
+// nvfp4a_gemv_tc(_ex) of one rank of a tensor-parallel group with the all-gather fused in: D (inside buffers[rank]) is also
+// stored at the same place of every peer's buffer and the ranks meet in a barrier before the stream goes on.
+extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
+                                                const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
+                                                void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream) {
+  const char *fn = "nvfp4a_b200_gemv_tc_tp";
+  clear_error();
+  if (!buffers || !flags || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(NVFP4A_INVALID_VALUE, "%s: needs buffers, flags and 0 <= rank < world <= %d", fn, kMaxRanks);
+  TpPush tp;
+  memset(&tp, 0, sizeof tp);
+  tp.world = world; tp.rank = rank;
+  tp.local_base = (unsigned char *)buffers[rank];
+  for (int p = 0; p < world; ++p) {
+    if (!buffers[p] || !flags[p] || ((uintptr_t)buffers[p] & 15) || ((uintptr_t)flags[p] & 7))
+      return fail(NVFP4A_INVALID_VALUE, "%s: buffer / flag pointer of rank %d is NULL or misaligned", fn, p);
+    tp.delta[p] = (long long)((unsigned char *)buffers[p] - tp.local_base);
+    tp.flags[p] = (unsigned long long *)flags[p];
+  }
+  if (D && D->data && (unsigned char *)D->data < tp.local_base) return fail(NVFP4A_INVALID_VALUE, "%s: D must lie inside buffers[rank]", fn);
+  EpilogueEx x;
+  if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
+  if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemv_tc_ex and nvfp4a_b200_tp_gather", fn);
+  return gemv_tc_run(fn, m, n, k, alpha, A, B, ldb, 0.f, nullptr, 0, D, ldd, bias, x, stream, world > 1 ? &tp : nullptr);
 }

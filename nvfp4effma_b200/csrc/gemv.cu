@@ -18,6 +18,7 @@
 // 2^-118 in magnitude.
 #include <cuda_bf16.h>
 #include "operands.cuh"
+#include "sm100.cuh"
 
 namespace nvb {
 
@@ -29,6 +30,7 @@ struct GemvArgs {
   const uint16_t *x; int ldx;   // BF16 activations [n][ldx]
   Epilogue e;
   EpilogueEx ex;
+  TpPush tp;
 };
 
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
@@ -190,6 +192,36 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
     }
   }
   if (e.amax && tid < 128) warp_amax_commit(e.amax, amax);
+  if (g.tp.world > 1) {
+    // All-gather fused into this kernel: the CTA that finishes last copies the rank's outputs (n rows of the activation
+    // buffer, just written and still in L2) into every peer's buffer with 16-byte stores and joins the ranks' barrier.
+    __shared__ int last_cta;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      unsigned *ctas = (unsigned *)(g.tp.flags[g.tp.rank] + kFlagCtas);
+      const unsigned ticket = atomicAdd(ctas, 1u);
+      last_cta = ticket == gridDim.x - 1;
+      if (last_cta) *ctas = 0;
+    }
+    __syncthreads();
+    if (last_cta) {
+      __threadfence();
+      const int esz = dense_bytes(e.d_dtype);
+      const int drows = (g.ex.mask & kExSwiglu) ? gm / 2 : gm;
+      const int vec_per_row = drows * esz / 16;
+      for (int v = tid; v < vec_per_row * gn; v += blockDim.x) {
+        const int j = v / vec_per_row, c = v - j * vec_per_row;
+        uint8_t *src = (uint8_t *)e.d + ((size_t)j * e.ldd * esz + (size_t)c * 16);
+        const uint4 x = __ldcg((const uint4 *)src);
+        for (int p = 0; p < g.tp.world; ++p)
+          if (p != g.tp.rank) *(uint4 *)(src + g.tp.delta[p]) = x;
+      }
+      __threadfence_system();
+      __syncthreads();
+      tp_barrier_cta(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status);
+    }
+  }
 }
 
 bool gemv_supports(const GemmArgs &g) {
@@ -202,7 +234,8 @@ cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
   a.m = g.m; a.n = g.n; a.k = g.k;
   a.A = g.A;
   a.x = (const uint16_t *)g.B.data; a.ldx = g.B.ld;
-  a.e = g.e; a.ex = g.x;
+  a.e = g.e; a.ex = g.x; a.tp = g.tp;
+  a.tp.status = kernel_status_device_ptr();
   const int grid = (g.m + 15) / 16;
   if (a.A.image) gemv_kernel<2><<<grid, kGemvWarps * 32, 0, s>>>(a);
   else if (a.A.sld < 0) gemv_kernel<1><<<grid, kGemvWarps * 32, 0, s>>>(a);

@@ -1,6 +1,7 @@
 // Device views of GEMM operands and the internal launch interface between the host API (gemm_api.cu) and the kernels.
 #pragma once
 #include "common.cuh"
+#include "tp_barrier.cuh"
 
 namespace nvb {
 
@@ -57,6 +58,7 @@ struct GemmArgs {
   BOperand B;
   Epilogue e;
   EpilogueEx x;
+  TpPush tp;   // tensor-parallel GEMV: D also goes to the peers, then the ranks' barrier (world <= 1: off)
 };
 
 // kernels (each returns the launch error)

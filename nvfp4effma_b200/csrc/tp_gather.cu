@@ -11,28 +11,19 @@
 // Ranks live on different GPUs: kernels that wait on one another must never share a GPU.
 #include "operands.cuh"
 #include "sm100.cuh"
+#include "tp_barrier.cuh"
 
 namespace nvb {
 
-constexpr int kMaxRanks = 8;
 struct TpGatherArgs {
   uint8_t *buf[kMaxRanks];                 // the activation buffer on every rank (buf[rank] is local)
-  unsigned long long *flags[kMaxRanks];    // flag array (kMaxRanks slots + the epoch counter at slot kMaxRanks) on every rank
+  unsigned long long *flags[kMaxRanks];    // flag array on every rank
   int world, rank;
   int rows;                                // T
   long long row_pitch_bytes, col_offset_bytes, shard_bytes;  // this rank's columns: [col_offset, col_offset + shard_bytes) of every row
   unsigned *status;
   int copy, barrier;
 };
-
-__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __global__ void __launch_bounds__(1024) tp_gather_kernel(const TpGatherArgs a) {
   if (a.copy) {
@@ -50,26 +41,7 @@ __global__ void __launch_bounds__(1024) tp_gather_kernel(const TpGatherArgs a) {
   }
   if (!a.barrier) return;
   __syncthreads();
-  __shared__ unsigned long long epoch_s;
-  unsigned long long *mine = a.flags[a.rank];
-  if (threadIdx.x == 0) {
-    epoch_s = mine[kMaxRanks] + 1;
-    mine[kMaxRanks] = epoch_s;
-  }
-  __syncthreads();
-  const unsigned long long epoch = epoch_s;
-  if ((int)threadIdx.x < a.world) {
-    const int p = threadIdx.x;
-    __threadfence_system();
-    st_release_sys(a.flags[p] + a.rank, epoch);      // slot `rank` on peer p (p == rank: my own slot)
-    const long long start = clock64();
-    while (ld_acquire_sys(mine + p) < epoch) {
-      if (clock64() - start > 2000000000ll) {       // about a second: a peer never arrived
-        atomicCAS(a.status, 0u, 0x401u);
-        break;
-      }
-    }
-  }
+  tp_barrier_cta(a.flags, a.world, a.rank, a.status);
 }
 
 }  // namespace nvb
@@ -78,7 +50,7 @@ using namespace nvb;
 
 // buffers / flags: `world` device pointers each (peer mappings of one symmetric allocation; entry `rank` is local).
 // The shard is columns [col_offset_bytes, col_offset_bytes + shard_bytes) of each of `rows` rows of row_pitch_bytes; all
-// three are multiples of 16.  The flag array holds 9 unsigned 64-bit words, zero before the first use and owned by this
+// three are multiples of 16.  The flag array holds 16 unsigned 64-bit words, zero before the first use and owned by this
 // function afterwards.
 extern "C" nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
                                                long long col_offset_bytes, long long shard_bytes, cudaStream_t stream) {

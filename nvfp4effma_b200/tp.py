@@ -79,10 +79,6 @@ class PeerGather:
     def __init__(self, group, max_elems: int, device):
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
-        try:
-            symm.enable_symm_mem_for_group(group.group_name)
-        except Exception:
-            pass
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.bufs = [symm.empty(max_elems, dtype=torch.bfloat16, device=device) for _ in range(2)]
         self.flags = symm.empty(16, dtype=torch.int64, device=device)
@@ -106,9 +102,12 @@ class TPLinear:
     replicated ``x`` [T, K] (bfloat16) and returns the full ``y``; ``forward_local`` returns this rank's columns only."""
 
     def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False,
-                 gather: Optional["PeerGather"] = None):
+                 gather: Optional["PeerGather"] = None, fused_decode: bool = False):
+        """``fused_decode``: up to 8 tokens, the GEMV kernel itself copies the rank's outputs to the peers and joins the
+        barrier (``nvfp4a_b200_gemv_tc_tp``) instead of a second launch; measured slower at 2 GPUs, so off by default."""
         self.group = group
         self.gather = gather
+        self.fused_decode = fused_decode
         solo = replicate or not dist.is_initialized()  # replicate: the whole weight on this rank, no collective
         self.world = 1 if solo else dist.get_world_size(group)
         self.rank = 0 if solo else dist.get_rank(group)
@@ -142,8 +141,15 @@ class TPLinear:
             return gather_features(self.forward_local(x), self.group)
         T, nl, M = x.shape[0], self.rows // (2 if self.swiglu else 1), self.out_features
         y = self.gather.view(slot, T, M)
-        self.forward_local(x, out=y[:, self.rank * nl:(self.rank + 1) * nl])
-        self.gather.push(slot, T, M, self.rank * nl, nl)
+        mine = y[:, self.rank * nl:(self.rank + 1) * nl]
+        if T <= 8 and self.fused_decode:   # the GEMV's last CTA stores to every rank and joins the barrier itself
+            if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
+                raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
+            _ops.gemv_tp(x, self.image, self.rows, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias, mine, self.swiglu,
+                         self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
+        else:
+            self.forward_local(x, out=mine)
+            self.gather.push(slot, T, M, self.rank * nl, nl)
         return y
 
     __call__ = forward
@@ -155,7 +161,8 @@ class TPDecoderLinears:
     Attention, norms and residuals are not part of this path: O reads the first ``hidden`` features of the QKV output."""
 
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
-                 device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096):
+                 device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096,
+                 fused_decode: bool = False):
         """``collective``: "peer" = the library's all-gather over peer-mapped buffers, "nccl" = ``all_gather_into_tensor``."""
         self.hidden, self.layers = hidden, []
         multi = dist.is_initialized() and dist.get_world_size(group) > 1 and not replicate
@@ -171,7 +178,7 @@ class TPDecoderLinears:
                 gen = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 4 + j)  # the same weights on every rank
                 w = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
                 amax = w.abs().amax().float().reshape(1)
-                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate, gather=gather))
+                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate, gather=gather, fused_decode=fused_decode))
                 del w
             self.layers.append(mods)
 
