@@ -68,6 +68,8 @@ bool gemv_supports(const GemmArgs &g);
 cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s);      // n <= 2: weights straight into tcgen05 kind::mxf4nvf4, activations as FP4 digit planes
 bool gemv_fp4_supports(const GemmArgs &g);
 void set_gemv_fp4_splits(int s);
+cudaError_t launch_gemv_blocked(const GemmArgs &g, cudaStream_t s);  // n <= 8, INT8 or NVFP4 activations: exact DP4A block sums
+bool gemv_blocked_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s);     // tcgen05 kind::mxf4nvf4 (E4M3 scales)
 bool gemm_w4a4_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s);    // tcgen05 kind::f16 with weights expanded to BF16 in smem

@@ -384,3 +384,17 @@ def test_w4a4_4096_cubed_against_block_sum_oracle_sample():
     print(f"4096^3 W4A4: share of outputs within 1 BF16 ulp of the block-sum oracle = {share:.6f}; equal bits = {np.mean(got == exact):.6f}")
     assert share >= 0.999
     assert abs(a1 - np.abs(d1).max()) <= 2.0 ** -7 * a1
+
+
+@pytest.mark.parametrize("bt", [L.INT8, L.NVFP4])
+def test_gemv_with_block_scaled_activations_uses_the_dp4a_kernel(bt):
+    """n <= 8 with INT8 / NVFP4 activations: exact integer block sums by DP4A (route 6), FP32 accumulation in the kernel's order."""
+    for i, (m, n, k) in enumerate([(70, 1, 64), (515, 3, 1024), (4096, 8, 4096), (33, 5, 2304)]):
+        for fa in (0, SW, AM | PR):
+            c = Case(m, n, k, bt, OUTS[i % 3], OUTS[i % 3] if i % 2 else -1, L.FP32 if i % 2 else -1, 0.75, 1.0 if not i % 2 else 0.0, fa=fa,
+                     fb=(SW | AM) if (bt == L.NVFP4 and i % 2) else 0)
+            h = build_case(c, 1200 + i)
+            exp = oracle_case(c, h, want_ref=True)
+            got, amax = run_gemm(c, h)
+            assert L.lib.nvfp4a_b200_last_route() == 6, c
+            check_bound(c, h, got, amax, exp)
