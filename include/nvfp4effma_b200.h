@@ -36,7 +36,8 @@ nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
 int nvfp4a_b200_set_tile_n(int bn);
 
 /* The kernel the calling thread's last GEMM / GEMV call launched: 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core GEMV, 4 W4A4
- * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations; 0 before any call.  Test aid, no counterpart in the reference. */
+ * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8
+ * activations; 0 before any call.  Test aid, no counterpart in the reference. */
 int nvfp4a_b200_last_route(void);
 
 /* Pins the number of k ranges (CTAs per cluster) of the FP4 tensor-core GEMV: 0 = by problem size, else 1, 2, 4 or 8; a

@@ -88,7 +88,7 @@ static nvfp4a_status check_epilogue_operands(const char *fn, int m, float beta, 
 }
 
 // kernel the last GEMM call of this thread launched (nvfp4a_b200_last_route): 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core
-// GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations
+// GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8 activations
 static thread_local int g_last_route = 0;
 
 // The workspace of nvfp4a_gemm_tc_ex holds the RMSNorm column scales of up to kWorkspaceTokens tokens while a call runs (a
@@ -107,6 +107,7 @@ static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t st
   else if (gemv && g.k > 0 && gemv_blocked_supports(g)) { g_last_route = 6; err = launch_gemv_blocked(g, stream); }
   else if (!gemv && gemm_w4a4_supports(g)) { g_last_route = 4; err = launch_gemm_w4a4(g, stream); }
   else if (!gemv && gemm_w4a16_supports(g)) { g_last_route = 5; err = launch_gemm_w4a16(g, stream); }
+  else if (!gemv && gemm_dp4a_supports(g)) { g_last_route = 7; err = launch_gemm_dp4a(g, stream); }
   else { g_last_route = 1; err = launch_gemm_generic(g, stream); }
   if (err == cudaSuccess && g.tp.world > 1 && g_last_route != 2) {
     // only the mma.sync GEMV pushes its results to the peers itself; after any other kernel a copy launch does it

@@ -72,6 +72,8 @@ cudaError_t launch_gemv_blocked(const GemmArgs &g, cudaStream_t s);  // n <= 8, 
 bool gemv_blocked_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s);     // tcgen05 kind::mxf4nvf4 (E4M3 scales)
 bool gemm_w4a4_supports(const GemmArgs &g);
+cudaError_t launch_gemm_dp4a(const GemmArgs &g, cudaStream_t s);     // W4A8, n > 8: DP4A block sums in the reference's tiled order
+bool gemm_dp4a_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s);    // tcgen05 kind::f16 with weights expanded to BF16 in smem
 bool gemm_w4a16_supports(const GemmArgs &g);
 // s_j of every token (the RMSNorm column scale of the extended epilogue) -> out[0 .. n)

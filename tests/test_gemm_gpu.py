@@ -398,3 +398,17 @@ def test_gemv_with_block_scaled_activations_uses_the_dp4a_kernel(bt):
             got, amax = run_gemm(c, h)
             assert L.lib.nvfp4a_b200_last_route() == 6, c
             check_bound(c, h, got, amax, exp)
+
+
+def test_w4a8_dp4a_gemm_is_bit_exact_in_the_tiled_order():
+    """INT8 activations, n > 8: the DP4A GEMM (route 7) sums blocks in the reference's tiled order, so D and amax equal the
+    oracle's bit for bit; tails in m and n, padded leading dimensions, every output type, bias, beta, alpha."""
+    for i, (m, n, k) in enumerate([(128, 128, 64), (130, 9, 128), (517, 300, 1024), (1000, 129, 576), (64, 2048, 256)]):
+        for fa in (0, SW, AM | PR):
+            c = Case(m, n, k, L.INT8, OUTS[i % 3], OUTS[(i + 1) % 3] if i % 2 else -1, L.BF16 if i % 2 else -1, 1.25, 0.5 if i % 2 else 1.0, fa=fa)
+            h = build_case(c, 1300 + i)
+            exp = oracle_case(c, h)
+            got, amax = run_gemm(c, h)
+            assert L.lib.nvfp4a_b200_last_route() == 7, c
+            assert np.array_equal(got.view(np.uint8), exp["D"].view(np.uint8)), c
+            assert amax == exp["amax"], c
