@@ -404,12 +404,27 @@ def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks):
     ms_dn = time_steps(down, steps, 3, stream, dist, world) / steps
     f_gu, f_dn = 2.0 * 2 * I * T * H, 2.0 * H * T * I
     tf = lambda f, ms: f / (ms * 1e-3) / 1e12
+
+    # the same gate / up GEMM with INT8 activations (W4A8): nvfp4a_gemm_ex on plain operands, exact DP4A block sums
+    xq = torch.empty(T, H, dtype=torch.int8, device=dev)
+    xsc = torch.empty(T, H // 16, dtype=torch.float32, device=dev)
+    src, dst = W.tensor(x, L.BF16), W.tensor(xq, L.INT8, xsc, 0)
+    L.check(L.lib.nvfp4a_quantize(ctypes.byref(src), H, ctypes.byref(dst), H, T, H, W.stream_ptr()))
+    t_xq, t_gu_plain = W.tensor(xq, L.INT8, xsc, H // 16), gu.tensor()
+
+    def gate_up_w4a8(i):
+        L.check(L.lib.nvfp4a_gemm_ex(2 * I, T, H, 1.0, ctypes.byref(t_gu_plain), H, ctypes.byref(t_xq), H, 0.0, None, 0, ctypes.byref(t_h), I,
+                                     ctypes.byref(t_bg), ctypes.byref(ex_gu), W.stream_ptr()))
+
+    ms_gu8 = time_steps(gate_up_w4a8, 3, 1, stream, dist, world) / 3
     return {"metric": "mlp_w4a16_tflops", "unit": "TFLOP/s", "value": tf(f_gu + f_dn, ms_gu + ms_dn) * world, "tokens": T,
             "gate_up": {"m": 2 * I, "k": H, "epilogue": "RMSNorm column scale + bias + SwiGLU + amax", "ms": ms_gu, "tflops": tf(f_gu, ms_gu)},
             "down": {"m": H, "k": I, "epilogue": "bias + second output * w2 + sums of squares + amax", "ms": ms_dn, "tflops": tf(f_dn, ms_dn)},
+            "gate_up_w4a8": {"entry": "nvfp4a_gemm_ex, INT8 activations", "kernel": "DP4A tiled GEMM (exact block sums, CUDA cores)", "ms": ms_gu8,
+                             "tflops": tf(f_gu, ms_gu8)},
             "roofline": {"bound": "tensor", "achieved": tf(f_gu + f_dn, ms_gu + ms_dn), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": tf(f_gu + f_dn, ms_gu + ms_dn) / peaks["bf16_tflops"], "traffic": None},
-            "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1}
+            "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1 + 5}
 
 
 def bench_tp(args, dev, rank, world, dist, stream, peaks):
