@@ -64,6 +64,14 @@ nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvf
                                      const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
                                      void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream);
 
+/* nvfp4a_gemm_tc / nvfp4a_gemm_tc_ex (beta = 0) with the tensor-parallel all-gather fused in (no counterpart in the reference):
+ * as nvfp4a_b200_gemv_tc_tp, for more than 8 tokens.  With BF16 activations the tcgen05 GEMM's epilogue stores every tile of
+ * D by TMA into the local buffer and into every peer's (plain TMA stores to peer memory; no multicast, no peer loads), so the
+ * gather overlaps the GEMM; a barrier launch follows.  Other operand types copy after the GEMM. */
+nvfp4a_status nvfp4a_b200_gemm_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, const nvfp4a_tensor *D,
+                                     int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex, void *workspace, void *const *buffers,
+                                     void *const *flags, int world, int rank, cudaStream_t stream);
+
 /* nvfp4a_gemm_ex that allocates nothing and still computes the RMSNorm column scales once per call: they are staged in a
  * 64 KiB device array inside the library image instead of a workspace.  No counterpart in the reference (its
  * nvfp4a_gemm_ex needs no scratch; its tensor-core entries take a caller workspace).  Same arguments and the same results,

@@ -290,3 +290,24 @@ def gemv_tp(x, w_img, w_rows, w_global, w_flags, w_smax, k, bias, out, swiglu, b
     L.check(L.lib.nvfp4a_b200_gemv_tc_tp(w_rows, T, k, 1.0, ctypes.byref(tA), ctypes.byref(tB), x.stride(0), ctypes.byref(tD), out.stride(0),
                                          ctypes.byref(tbias) if tbias is not None else None, ctypes.byref(ex), bufs, flags, world, rank, _stream()))
     return out
+
+
+def gemm_tp(x, w_img, w_rows, w_global, w_flags, w_smax, k, bias, out, swiglu, buffer_ptrs, flag_ptrs, rank):
+    """``nvfp4a_b200_gemm_tc_tp``: more than 8 rows of contiguous bfloat16 ``x`` [T, k] (used as its own activation image)
+    against a weight image; the GEMM's epilogue also stores ``out`` into every peer's buffer, then the ranks' barrier."""
+    T = x.shape[0]
+    if not (x.is_contiguous() and x.data_ptr() % 16 == 0):
+        x = x.contiguous()
+    world = len(buffer_ptrs)
+    bufs = (ctypes.c_void_p * world)(*buffer_ptrs)
+    flags = (ctypes.c_void_p * world)(*flag_ptrs)
+    tA = L.Tensor(_ptr(w_img), L.NVFP4, None, 0, _ptr(w_global), None, w_flags, w_smax)
+    tB = L.Tensor(_ptr(x), L.BF16, None, 0, None, None, 0, 0)
+    tD = L.Tensor(_ptr(out), _dense_code(out.dtype), None, 0, None, None, 0, 0)
+    tbias = L.Tensor(_ptr(bias), _dense_code(bias.dtype), None, 0, None, None, 0, 0) if bias is not None else None
+    ex = L.Epilogue()
+    ex.swiglu = int(bool(swiglu))
+    L.check(L.lib.nvfp4a_b200_gemm_tc_tp(w_rows, T, k, 1.0, ctypes.byref(tA), ctypes.byref(tB), ctypes.byref(tD), out.stride(0),
+                                         ctypes.byref(tbias) if tbias is not None else None, ctypes.byref(ex), _ptr(_workspace(w_img.device)), bufs, flags,
+                                         world, rank, _stream()))
+    return out

@@ -115,8 +115,9 @@ static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t st
     for (int p = 0; p < g.tp.world; ++p) { bufs[p] = g.tp.local_base + g.tp.delta[p]; flags[p] = g.tp.flags[p]; }
     const int esz = dense_bytes(g.e.d_dtype);
     const long long drows = (g.x.mask & kExSwiglu) ? g.m / 2 : g.m;
-    return nvfp4a_b200_tp_gather(bufs, flags, g.tp.world, g.tp.rank, g.n, (long long)g.e.ldd * esz, (long long)((uint8_t *)g.e.d - g.tp.local_base),
-                                 drows * esz, stream);
+    const bool pushed = g_last_route == 5 && gemm_w4a16_pushes(g);   // the W4A16 GEMM stored to the peers itself: only the barrier is left
+    return nvfp4a_b200_tp_gather(bufs, flags, g.tp.world, g.tp.rank, pushed ? 0 : g.n, (long long)g.e.ldd * esz,
+                                 (long long)((uint8_t *)g.e.d - g.tp.local_base), drows * esz, stream);
   }
   return cuda_fail(err, fn);
 }
@@ -200,7 +201,7 @@ static nvfp4a_status check_flags_only(const char *fn, const nvfp4a_tensor *t) {
 
 static nvfp4a_status gemm_tc_run(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, float beta,
                                  const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, void *workspace,
-                                 const EpilogueEx &ex, cudaStream_t stream) {
+                                 const EpilogueEx &ex, cudaStream_t stream, const TpPush *tp = nullptr) {
   if (!A || !B || !D || !A->data || !B->data || !D->data || !workspace)
     return fail(NVFP4A_INVALID_VALUE, "%s: A, B, D (or a data pointer) or the workspace is NULL", fn);
   if (m < 0 || n < 0 || k < 0) return fail(NVFP4A_INVALID_VALUE, "%s: negative size (m = %d, n = %d, k = %d)", fn, m, n, k);
@@ -231,6 +232,7 @@ static nvfp4a_status gemm_tc_run(const char *fn, int m, int n, int k, float alph
   } else g.B = make_b(B, k, 0, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
+  if (tp) g.tp = *tp;
   // RMSNorm column scales once per call instead of once per tile of weight rows (the tcgen05 W4A16 GEMM reads them)
   const bool stage_scales = (ex.mask & kExNorm) && n > kGemvMaxN && n <= kWorkspaceTokens && forced_route() != 1 && gemm_w4a16_supports(g);
   if (stage_scales) {
@@ -498,4 +500,30 @@ extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha
   if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
   if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemv_tc_ex and nvfp4a_b200_tp_gather", fn);
   return gemv_tc_run(fn, m, n, k, alpha, A, B, ldb, 0.f, nullptr, 0, D, ldd, bias, x, stream, world > 1 ? &tp : nullptr);
+}
+
+// nvfp4a_gemm_tc(_ex) (beta = 0) of one rank of a tensor-parallel group with the all-gather fused in: the W4A16 tcgen05 GEMM's
+// epilogue stores every tile of D into all ranks' buffers by TMA, then the ranks meet in a barrier.
+extern "C" nvfp4a_status nvfp4a_b200_gemm_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B,
+                                                const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex, void *workspace,
+                                                void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream) {
+  const char *fn = "nvfp4a_b200_gemm_tc_tp";
+  clear_error();
+  if (!buffers || !flags || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(NVFP4A_INVALID_VALUE, "%s: needs buffers, flags and 0 <= rank < world <= %d", fn, kMaxRanks);
+  TpPush tp;
+  memset(&tp, 0, sizeof tp);
+  tp.world = world; tp.rank = rank;
+  tp.local_base = (unsigned char *)buffers[rank];
+  for (int p = 0; p < world; ++p) {
+    if (!buffers[p] || !flags[p] || ((uintptr_t)buffers[p] & 15) || ((uintptr_t)flags[p] & 7))
+      return fail(NVFP4A_INVALID_VALUE, "%s: buffer / flag pointer of rank %d is NULL or misaligned", fn, p);
+    tp.delta[p] = (long long)((unsigned char *)buffers[p] - tp.local_base);
+    tp.flags[p] = (unsigned long long *)flags[p];
+  }
+  if (D && D->data && (unsigned char *)D->data < tp.local_base) return fail(NVFP4A_INVALID_VALUE, "%s: D must lie inside buffers[rank]", fn);
+  EpilogueEx x;
+  if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
+  if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemm_tc_ex and nvfp4a_b200_tp_gather", fn);
+  return gemm_tc_run(fn, m, n, k, alpha, A, B, 0.f, nullptr, 0, D, ldd, bias, workspace, x, stream, world > 1 ? &tp : nullptr);
 }

@@ -35,6 +35,12 @@ struct W4A16Args {
   int d_tma;     // the output goes through the staging tile and TMA stores (SwiGLU: 64 output rows per tile)
 };
 
+// tensor maps of D in the peers' buffers (tensor-parallel all-gather fused into the epilogue's TMA stores); n = 0: none
+struct alignas(64) PeerMaps {
+  CUtensorMap map[kMaxRanks - 1];
+  int n;
+};
+
 template <int BN>
 struct Cfg {
   static constexpr int kStages = BN == 256 ? 4 : 6;
@@ -73,7 +79,8 @@ struct RawRow {
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d, const W4A16Args g) {
+gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ PeerMaps peers,
+                  const W4A16Args g) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -317,6 +324,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
             named_barrier(1, 128);
             if (leader) {
               tma_store_2d(&tmap_d, staging, tm * 64, j0 + half * cw);
+              for (int p = 0; p < peers.n; ++p) tma_store_2d(&peers.map[p], staging, tm * 64, j0 + half * cw);   // the same tile into every peer's buffer
               bulk_commit();
             }
           }
@@ -364,6 +372,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
           named_barrier(1, 128);
           if (leader) {
             tma_store_2d(&tmap_d, staging, tm * 128, j0 + half * cw);
+            for (int p = 0; p < peers.n; ++p) tma_store_2d(&peers.map[p], staging, tm * 128, j0 + half * cw);   // the same tile into every peer's buffer
             bulk_commit();
           }
         }
@@ -448,7 +457,7 @@ done:
 }
 
 template <int BN>
-cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const W4A16Args &a, cudaStream_t s) {
+cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const PeerMaps &pm, const W4A16Args &a, cudaStream_t s) {
   using C = Cfg<BN>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -460,11 +469,19 @@ cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const W4A16
   }
   const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
   const int grid = tiles < device_sms() ? tiles : device_sms();
-  gemm_w4a16_kernel<BN><<<grid, kThreads, C::kSmemBytes, s>>>(tb, td, a);
+  gemm_w4a16_kernel<BN><<<grid, kThreads, C::kSmemBytes, s>>>(tb, td, pm, a);
   return cudaGetLastError();
 }
 
 }  // namespace
+
+// tensor parallel: true when this kernel stores D into the peers' buffers itself (its output path is the TMA store)
+bool gemm_w4a16_pushes(const GemmArgs &g) {
+  if (g.tp.world <= 1) return false;
+  const int esz = dense_bytes(g.e.d_dtype);
+  const int drows = (g.x.mask & kExSwiglu) ? g.m / 2 : g.m;
+  return ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)drows * esz) % 16 == 0;
+}
 
 bool gemm_w4a16_supports(const GemmArgs &g) {
   if (g.B.dtype != NVFP4A_BF16 || g.k < 64 || ((uintptr_t)g.B.data & 15) || g.B.ld % 8) return false;
@@ -488,7 +505,18 @@ cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s) {
   const int drows = glu ? g.m / 2 : g.m;   // SwiGLU: the output has m / 2 rows, 64 per tile
   a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)drows * esz) % 16 == 0 &&
             make_tmap_dense(&td, g.e.d, esz, (uint64_t)drows, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, glu ? 64 : 128, esz == 2 ? 32 : 16);
-  return bn == 256 ? launch_cfg<256>(tb, td, a, s) : launch_cfg<128>(tb, td, a, s);
+  PeerMaps pm;
+  memset(&pm, 0, sizeof pm);
+  if (gemm_w4a16_pushes(g)) {   // tensor parallel: the epilogue's TMA stores also go to every peer's copy of D
+    for (int p = 0; p < g.tp.world; ++p) {
+      if (p == g.tp.rank) continue;
+      if (!make_tmap_dense(&pm.map[pm.n], (uint8_t *)g.e.d + g.tp.delta[p], esz, (uint64_t)drows, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, glu ? 64 : 128,
+                           esz == 2 ? 32 : 16))
+        return cudaErrorInvalidValue;
+      ++pm.n;
+    }
+  }
+  return bn == 256 ? launch_cfg<256>(tb, td, pm, a, s) : launch_cfg<128>(tb, td, pm, a, s);
 }
 
 }  // namespace nvb

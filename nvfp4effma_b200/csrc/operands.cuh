@@ -76,6 +76,7 @@ cudaError_t launch_gemm_dp4a(const GemmArgs &g, cudaStream_t s);     // W4A8, n 
 bool gemm_dp4a_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s);    // tcgen05 kind::f16 with weights expanded to BF16 in smem
 bool gemm_w4a16_supports(const GemmArgs &g);
+bool gemm_w4a16_pushes(const GemmArgs &g);
 // s_j of every token (the RMSNorm column scale of the extended epilogue) -> out[0 .. n)
 cudaError_t launch_norm_scales(const EpilogueEx &x, int n, float *out, cudaStream_t s);
 cudaError_t launch_image_build(const Fp4Operand &src, int rows, int k, uint8_t *image, cudaStream_t s);

@@ -102,12 +102,13 @@ class TPLinear:
     replicated ``x`` [T, K] (bfloat16) and returns the full ``y``; ``forward_local`` returns this rank's columns only."""
 
     def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False,
-                 gather: Optional["PeerGather"] = None, fused_decode: bool = False):
+                 gather: Optional["PeerGather"] = None, fused_decode: bool = False, fused_prefill: bool = True):
         """``fused_decode``: up to 8 tokens, the GEMV kernel itself copies the rank's outputs to the peers and joins the
         barrier (``nvfp4a_b200_gemv_tc_tp``) instead of a second launch; measured slower at 2 GPUs, so off by default."""
         self.group = group
         self.gather = gather
         self.fused_decode = fused_decode
+        self.fused_prefill = fused_prefill   # more than 8 tokens: the GEMM stores its tiles to the peers itself
         solo = replicate or not dist.is_initialized()  # replicate: the whole weight on this rank, no collective
         self.world = 1 if solo else dist.get_world_size(group)
         self.rank = 0 if solo else dist.get_rank(group)
@@ -147,6 +148,10 @@ class TPLinear:
                 raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
             _ops.gemv_tp(x, self.image, self.rows, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias, mine, self.swiglu,
                          self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
+        elif T > 8 and self.fused_prefill and x.dtype == torch.bfloat16:
+            # the GEMM's epilogue stores every tile into all ranks' buffers (TMA stores to peer memory), then the barrier
+            _ops.gemm_tp(x, self.image, self.rows, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias, mine, self.swiglu,
+                         self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
         else:
             self.forward_local(x, out=mine)
             self.gather.push(slot, T, M, self.rank * nl, nl)
@@ -162,7 +167,7 @@ class TPDecoderLinears:
 
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
                  device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096,
-                 fused_decode: bool = False):
+                 fused_decode: bool = False, fused_prefill: bool = True):
         """``collective``: "peer" = the library's all-gather over peer-mapped buffers, "nccl" = ``all_gather_into_tensor``."""
         self.hidden, self.layers = hidden, []
         multi = dist.is_initialized() and dist.get_world_size(group) > 1 and not replicate
@@ -178,7 +183,7 @@ class TPDecoderLinears:
                 gen = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 4 + j)  # the same weights on every rank
                 w = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
                 amax = w.abs().amax().float().reshape(1)
-                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate, gather=gather, fused_decode=fused_decode))
+                mods.append(TPLinear(quantize(w, amax / (6.0 * 448.0)), group=group, swiglu=glu, replicate=replicate, gather=gather, fused_decode=fused_decode, fused_prefill=fused_prefill))
                 del w
             self.layers.append(mods)
 

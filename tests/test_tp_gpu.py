@@ -59,13 +59,14 @@ from nvfp4effma_b200.tp import TPDecoderLinears
 kw = dict(layers=2, hidden=256, intermediate=512, qkv=512, std=0.06)
 peer, nccl, solo = TPDecoderLinears(collective="peer", max_tokens=64, **kw), TPDecoderLinears(collective="nccl", **kw), TPDecoderLinears(replicate=True, **kw)
 fused = TPDecoderLinears(collective="peer", max_tokens=64, fused_decode=True, **kw)
+unfused = TPDecoderLinears(collective="peer", max_tokens=64, fused_prefill=False, **kw)
 ok = peer.collective == "peer" and nccl.collective == "nccl"
 for rep in range(2):
     for T in (1, 5, 48):
         g = torch.Generator(device="cpu").manual_seed(T)
         x = torch.randn((T, 256), generator=g).cuda().bfloat16()
         want = solo(x)
-        ok = ok and torch.equal(peer(x).clone(), want) and torch.equal(nccl(x), want) and torch.equal(fused(x).clone(), want)
+        ok = ok and torch.equal(peer(x).clone(), want) and torch.equal(nccl(x), want) and torch.equal(fused(x).clone(), want) and torch.equal(unfused(x).clone(), want)
 from nvfp4effma_b200 import workloads
 ok = ok and workloads.kernel_status() == 0
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
