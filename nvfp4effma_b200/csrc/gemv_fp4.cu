@@ -40,6 +40,7 @@ struct GemvFp4Args {
   int a_image;
   const uint8_t *sa;   // plain: block scale base; image: image base
   int sa_ld, ktiles;
+  int linear;          // plain operand with linear block scales: a TMA box brings [256 rows][16 bytes], four warps re-tile it
   const uint16_t *x; int ldx;
   Epilogue e;
   EpilogueEx ex;
@@ -55,17 +56,18 @@ constexpr int kMaxChunks = 16;                              // 256-k chunks per 
 constexpr int kTmemCols = 512;                              // accumulator [0, 256), A scales (1.0) [256, 260), B scales [272, 272 + 32 * stages), stages <= 6
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 232448 - 1024;                   // dynamic shared memory of one CTA on sm_100, less the alignment slack
-constexpr unsigned kStWaitFull = 0x201, kStWaitEmpty = 0x202, kStWaitAcc = 0x203, kStWaitPieces = 0x204;
+constexpr unsigned kStWaitFull = 0x201, kStWaitEmpty = 0x202, kStWaitAcc = 0x203, kStWaitPieces = 0x204, kStWaitRetile = 0x205;
+constexpr int kRawSfBytes = kRows * 16;                      // linear scales of one chunk as they lie in memory: [256 rows][16 bytes]
 
 // Shared memory of a CTA: [pieces | stages x 36 KiB | unit scales 512 | results splits x NTOK x 256 floats | barriers 256].
 // The MMA reads 16 KiB from the start of a pieces chunk (its M is 128 rows), which stays inside the stages.
-__host__ __device__ constexpr int fixed_bytes(int ntok, int splits) { return 512 + splits * ntok * 1024 + 256; }
+__host__ __device__ constexpr int fixed_bytes(int ntok, int splits) { return 512 + splits * ntok * 1024 + 320; }
 
 __device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }  // -126 <= e <= 127
 
 template <int NTOK>
 __global__ void __launch_bounds__(kThreads, 1)
-gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g) {
+gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_s, const GemvFp4Args g) {
   constexpr int PR = 16 * NTOK;
   const int kStages = g.stages;
   const uint32_t rank = cluster_ctarank(), splits = gridDim.x;
@@ -73,10 +75,12 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *pieces = smem;
   uint8_t *stages = smem + g.piece_bytes;
-  uint8_t *unit_sf = stages + kStages * kStageBytes;
+  const bool linear = g.linear;
+  const int stage_bytes = kStageBytes + (linear ? kRawSfBytes : 0);
+  uint8_t *unit_sf = stages + kStages * stage_bytes;
   float *res = (float *)(unit_sf + 512);                   // [splits][NTOK][256]: slot p is written by the cluster's rank p (into rank 0's memory)
   uint64_t *bars = (uint64_t *)(unit_sf + 512 + splits * NTOK * 1024);
-  uint64_t *full = bars, *empty = bars + kMaxStages, *acc_full = bars + 2 * kMaxStages, *pieces_ready = acc_full + 1;
+  uint64_t *full = bars, *empty = bars + kMaxStages, *sf_ready = bars + 2 * kMaxStages, *acc_full = bars + 3 * kMaxStages, *pieces_ready = acc_full + 1;
   uint32_t *tmem_slot = (uint32_t *)(pieces_ready + 1);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
   uint32_t *wmax = tmem_slot + 2;                          // [8 warps][NTOK] largest |x| bit pattern
@@ -122,7 +126,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 1); }
     mbar_init(acc_full, 1);
     mbar_init(pieces_ready, kDecompThreads / 32);
     *abort_flag = 0;
@@ -151,8 +155,8 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
       for (int it = 0; it < nloc; ++it) {
         const int s = it % kStages, c = c0 + it;
         if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty)) break;
-        uint8_t *sW = stages + (size_t)s * kStageBytes, *sSf = sW + kDataBytes;
-        const uint32_t sf_bytes = second ? 4096u : 2048u;
+        uint8_t *sW = stages + (size_t)s * stage_bytes, *sSf = sW + kDataBytes;
+        const uint32_t sf_bytes = linear ? (uint32_t)kRawSfBytes : (second ? 4096u : 2048u);
         mbar_arrive_expect_tx(&full[s], kDataBytes + sf_bytes);
         if (a_image) {
           // a tile index past the image reads zeros
@@ -162,9 +166,13 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
           if (second) bulk_load(sSf + 2048, sa_base + ((size_t)(2 * tm + 1) * ktiles + c) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
         } else {
           tma_load_2d(sW, &tmap_a, c * 128, tm * 256, &full[s]);
-          const size_t tile_stride = (size_t)((-sa_ld) >> 2) * 512;
-          bulk_load(sSf, sa_base + (size_t)(2 * tm) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
-          if (second) bulk_load(sSf + 2048, sa_base + (size_t)(2 * tm + 1) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
+          if (linear) {
+            tma_load_2d(sW + kStageBytes, &tmap_s, c * 4, tm * 256, &full[s]);   // 16 bytes (4 words) of 256 rows; rows past m read zeros
+          } else {
+            const size_t tile_stride = (size_t)((-sa_ld) >> 2) * 512;
+            bulk_load(sSf, sa_base + (size_t)(2 * tm) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
+            if (second) bulk_load(sSf + 2048, sa_base + (size_t)(2 * tm + 1) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
+          }
         }
       }
     }
@@ -179,10 +187,10 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
         bool ok = true;
         for (int it = 0; it < nloc; ++it) {
           const int s = it % kStages;
-          ok = wait(&full[s], (it / kStages) & 1, kStWaitFull);
+          ok = linear ? wait(&sf_ready[s], (it / kStages) & 1, kStWaitRetile) : wait(&full[s], (it / kStages) & 1, kStWaitFull);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sW = smem_u32(stages + (size_t)s * kStageBytes), sSf = sW + kDataBytes;
+          const uint32_t sW = smem_u32(stages + (size_t)s * stage_bytes), sSf = sW + kDataBytes;
           const uint32_t sfb_tmem = tmem_base + 272 + 32 * s;
           const uint64_t da = smem_desc_sw128(smem_u32(pieces) + it * (PR * 128)), db = smem_desc_sw128(sW);
 #pragma unroll
@@ -288,6 +296,28 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemvFp4Args g)
           }
         }
       }
+    } else if (linear && warp >= 5) {
+      // ---------------- warps 5, 6, 7, 9: linear block scales [256 rows][16 bytes] -> the eight 512-byte tiles of the stage ----------------
+      const int w = warp == 9 ? 3 : warp - 5;
+      for (int it = w; it < nloc; it += 4) {
+        const int s = it % kStages;
+        if (!wait(&full[s], (it / kStages) & 1, kStWaitRetile)) break;
+        uint8_t *st = stages + (size_t)s * stage_bytes;
+        const uint8_t *raw = st + kStageBytes;
+        uint8_t *sf = st + kDataBytes;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wd[q] = *(const uint32_t *)(raw + (h * 128 + 32 * q + lane) * 16 + 4 * j);
+            *(uint4 *)(sf + h * 2048 + j * 512 + lane * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_ready[s]);
+      }
     }
   }
 
@@ -383,8 +413,8 @@ static int choose_splits(int m, int k) {
 bool gemv_fp4_supports(const GemmArgs &g) {
   if (!(g.n >= 1 && g.n <= 2 && g.B.dtype == NVFP4A_BF16 && !g.A.ue && g.k >= 256 && g.k % 256 == 0)) return false;
   if (((uintptr_t)g.B.data & 15) || g.B.ld % 8) return false;
-  // plain operands: scales in aligned 512-byte tiles (the swizzled layout); linear scales go to the mma.sync GEMV
-  if (!g.A.image && (((uintptr_t)g.A.data & 15) || g.A.ld % 32 || g.A.sld >= 0 || ((uintptr_t)g.A.sc & 15))) return false;
+  // plain operands: scales in aligned 512-byte tiles (the swizzled layout), or linear with a 16-byte aligned base and pitch (TMA)
+  if (!g.A.image && (((uintptr_t)g.A.data & 15) || g.A.ld % 32 || ((uintptr_t)g.A.sc & 15) || (g.A.sld > 0 && g.A.sld % 16))) return false;
   return choose_splits(g.m, g.k) > 0;
 }
 
@@ -397,26 +427,30 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   a.status = kernel_status_device_ptr();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
   a.a_image = g.A.image;
-  CUtensorMap ta;
+  CUtensorMap ta, ts;
+  memset(&ts, 0, sizeof ts);
   if (g.A.image) {
     if (!make_tmap_bytes(&ta, g.A.data, 128, 128, 128, 128, (uint64_t)((g.m + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
     a.sa = g.A.data;
   } else {
     if (!make_tmap_bytes(&ta, g.A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)g.A.ld / 2, kRows)) return cudaErrorInvalidValue;
     a.sa = g.A.sc; a.sa_ld = g.A.sld;
+    a.linear = g.A.sld > 0;
+    if (a.linear && !make_tmap_dense(&ts, g.A.sc, 4, (uint64_t)g.k / 64, (uint64_t)g.m, (uint64_t)g.A.sld, 4, kRows)) return cudaErrorInvalidValue;
   }
   const int splits = choose_splits(g.m, g.k);
   if (splits <= 0) return cudaErrorInvalidValue;
-  void (*kern)(CUtensorMap, GemvFp4Args) = g.n == 1 ? gemv_fp4_kernel<1> : gemv_fp4_kernel<2>;
+  void (*kern)(CUtensorMap, CUtensorMap, GemvFp4Args) = g.n == 1 ? gemv_fp4_kernel<1> : gemv_fp4_kernel<2>;
   static bool attr_set[64][2] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   const int nk = g.k >> 8, nloc_max = (nk + splits - 1) / splits;
   a.piece_bytes = nloc_max * 16 * g.n * 128;
-  a.stages = (kSmemLimit - a.piece_bytes - fixed_bytes(g.n, splits)) / kStageBytes;
+  const int stage_bytes = kStageBytes + (a.linear ? kRawSfBytes : 0);
+  a.stages = (kSmemLimit - a.piece_bytes - fixed_bytes(g.n, splits)) / stage_bytes;
   if (a.stages > kMaxStages) a.stages = kMaxStages;
   if (a.stages < 2) return cudaErrorInvalidValue;
-  const int smem_bytes = 1024 + a.piece_bytes + a.stages * kStageBytes + fixed_bytes(g.n, splits);
+  const int smem_bytes = 1024 + a.piece_bytes + a.stages * stage_bytes + fixed_bytes(g.n, splits);
   if (!attr_set[dev & 63][g.n - 1]) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit + 1024);
     if (e != cudaSuccess) return e;
@@ -432,7 +466,7 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, a);
+  return cudaLaunchKernelEx(&cfg, kern, ta, ts, a);
 }
 
 }  // namespace nvb

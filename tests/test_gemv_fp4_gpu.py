@@ -97,3 +97,19 @@ def test_extended_epilogue(pin):
             assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
             v += 1
     assert kernel_status() == 0
+
+
+def test_plain_operand_with_linear_scales(pin):
+    """Linear block scales with a 16-byte aligned pitch: a TMA box brings [256 rows][16 bytes] per chunk, four warps re-tile it."""
+    from util import rand_dense, rand_fp4
+    pin(2)
+    for i, (m, n, k) in enumerate([(300, 1, 512), (1000, 2, 2048), (4096, 1, 4096)]):
+        c = Case(m, n, k, L.BF16, OUTS[i % 3], OUTS[i % 3], L.BF16 if i % 2 else -1, 1.0, 0.0)
+        h = build_case(c, 980 + i)
+        rng = np.random.default_rng(981 + i)
+        h["A"] = rand_fp4(rng, m, k, ld=h["lda"], ld_scale=k // 16, glob=0.375)   # compact scale rows: pitch k / 16, a multiple of 16
+        exp = oracle_case(c, h, want_ref=True)
+        got, amax = run_gemm(c, h)
+        assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV, c
+        check_bound(c, h, got, amax, exp)
+    assert kernel_status() == 0
