@@ -206,6 +206,8 @@ def run_ours(args, rank, world, local_rank):
     traffic = load_traffic()
     launches = 0
     only = args.only
+    if args.pair != -1:
+        assert L.lib.nvfp4a_b200_set_pair(args.pair) == 0
 
     # ---- GEMM W4A4 4096^3: rotating sets (inputs 18.9 MB + D 33.6 MB each; 3 sets > 126 MB of L2) ----
     nsets = 3
@@ -494,6 +496,8 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel linear stack extra")
     ap.add_argument("--no-tp-prefill", action="store_true", help="tensor-parallel extra: decode only")
     ap.add_argument("--tp-layers", type=int, default=32)
+    ap.add_argument("--pair", type=int, default=-1, choices=[-1, 0, 1],
+                    help="W4A4 GEMM: -1 automatic, 0 single-CTA tiles only, 1 CTA pairs wherever they apply (tuning aid)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "gemv", "quant", "mlp", "tp"],
                     help="run one workload only (for profiling captures); the JSON line then lacks the others")
     args = ap.parse_args()

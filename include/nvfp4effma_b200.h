@@ -35,6 +35,12 @@ nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
  * counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_tile_n(int bn);
 
+/* The W4A4 GEMM's CTA-pair form (tcgen05.mma.cta_group::2 on 256 x 256 tiles; taken for m > 128, n > 128 and block scales in
+ * aligned 512-byte tiles or images on both operands): -1 = automatic (at present: never -- the single-CTA form is the
+ * faster one), 0 = never, 1 = wherever it applies.  Results are bit-identical either way.  Tuning / test aid, no
+ * counterpart in the reference.  Returns 0, or -1 for another value. */
+int nvfp4a_b200_set_pair(int mode);
+
 /* The kernel the calling thread's last GEMM / GEMV call launched: 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core GEMV, 4 W4A4
  * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8
  * activations; 0 before any call.  Test aid, no counterpart in the reference. */

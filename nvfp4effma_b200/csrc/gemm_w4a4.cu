@@ -7,10 +7,17 @@
 // row (the TMA 128-byte swizzle), and the scales as 512-byte 128 x 4 tiles -- the cuBLASLt "swizzled" layout, which is what
 // tcgen05.cp.32x128b.warpx4 copies into the scale columns of tensor memory unchanged.
 //
-// Warp roles (320 threads): warp 0 lane 0 issues TMA / bulk copies; warp 1 lane 0 issues tcgen05.cp + tcgen05.mma and owns
-// the tensor memory allocation; warps 2-5 drain accumulators (one 32-lane quadrant each); warps 6-9 gather block scales
-// that are not stored as aligned 512-byte tiles (linear layout, or unaligned buffers) into the tile form, one stage each
-// in rotation.  Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
+// Warp roles (320 threads): warp 0 issues the copies of an iteration as ONE TMA instruction (lanes 0-5 name the nibble and
+// scale tensors, see the producer); warp 1 lane 0 issues tcgen05.mma (and tcgen05.cp for gathered scales) and warp 1 owns
+// the tensor memory allocation; warps 2-5 drain accumulators (one 32-lane quadrant each); warps 6-9 move the stage's
+// scale tiles from shared memory through registers into the scale columns of tensor memory (tcgen05.st, off the MMA
+// issuer's queue) -- or, for block scales that are not stored as aligned 512-byte tiles (linear layout, unaligned
+// buffers), gather them into the tile form, one stage each in rotation.  Every wait is bounded; a wait that gives up
+// raises the CTA's abort flag and the kernel status word.
+//
+// What the single-thread roles cost sets the pace of this kernel: a TMA instruction costs its issuing warp 150-200 cycles
+// whatever it moves, and a tcgen05.mma about as much, so an iteration has one of the former and four of the latter
+// (k = 64 is the largest MMA of this kind), and nothing else on those threads' paths that can be avoided.
 //
 // Semantics (reference include/nvfp4effma.h:78-92): the reference's tiled kernels round once per 16-block in FP32; the
 // tensor cores accumulate the same exact block products in their own order, so results agree within the FP32
@@ -36,17 +43,25 @@ struct W4A4Args {
   int d_tma;                   // D is stored by TMA from a shared-memory staging tile (needs 16-byte aligned D and column stride)
 };
 
-template <int BN, int ACC, int STAGES>
+template <int BN, int ACC, int STAGES, bool PAIR = false>
 struct W4A4Cfg {
-  static constexpr int kABytes = 128 * 128, kBBytes = BN * 128, kSfaBytes = 2048, kSfbBytes = BN * 16;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  // PAIR: a CTA holds 128 rows of A, HALF of the tile's B rows, and the scales of its A rows and of all BN rows of B
+  // A pair keeps the scale tiles out of the stages, in a ring of kScaleSlots slots of their own that the producer fills
+  // several iterations ahead of the operands (the scales' trip through registers into tensor memory then costs the MMA
+  // nothing), and kSfBuffers scale buffers in tensor memory instead of one per stage.
+  static constexpr int kABytes = 128 * 128, kBBytes = (PAIR ? BN / 2 : BN) * 128, kSfaBytes = 2048, kSfbBytes = BN * 16;
+  static constexpr int kStageBytes = kABytes + kBBytes + (PAIR ? 0 : kSfaBytes + kSfbBytes);
+  static constexpr int kScaleSlots = PAIR ? 8 : 0, kScaleLead = 4, kScaleSlotBytes = kSfaBytes + kSfbBytes;
   static constexpr int kSfCols = 16 + BN / 8;      // per scale buffer: A 4 groups x 4 columns, B 4 groups x BN / 32 columns
-  static constexpr int kSfBuffers = STAGES;        // one per pipeline stage
+  static constexpr int kSfBuffers = PAIR ? 5 : STAGES;   // single CTA: one per pipeline stage
   static constexpr int kAccCols = ACC * BN;
   static constexpr int kTmemCols = 512;
   static constexpr int kStagingBytes = 8192;       // epilogue staging: 128 rows x 32 (16-bit) or 16 (32-bit) columns
-  static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + kStagingBytes;
-  static_assert((3 * STAGES + 2 * ACC) * 8 + 8 <= 256, "barrier block");
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kRingBytes = STAGES * kStageBytes + kScaleSlots * kScaleSlotBytes;
+  static constexpr int kSmemBytes = kRingBytes + 1024 /* alignment slack */ + kBarrierBytes + kStagingBytes;
+  static_assert((2 * STAGES + 2 * kSfBuffers + 2 * kScaleSlots + 2 * ACC) * 8 + 8 <= kBarrierBytes, "barrier block");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
   static_assert(kAccCols + kSfBuffers * kSfCols <= kTmemCols, "tensor memory budget");
 };
 
@@ -54,39 +69,57 @@ constexpr int kThreads = 320;
 constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
                    kStatusWaitGather = 0x105, kStatusWaitSf = 0x106;
 
-template <int BN, int ACC, int STAGES>
+// PAIR: the two CTAs of a cluster work on one 256 x BN tile with tcgen05.mma.cta_group::2 -- each CTA loads its 128 rows of A
+// and half of the B rows, so a CTA pulls a third less through L2 per output than alone.  Each CTA runs its own TMA ring and
+// scale warps against its own `full` barriers and drains its own half of the accumulator; what crosses the pair: the scale
+// warps and the epilogue warps of both CTAs arrive on the even CTA's `sf_ready` / `tmem_empty` barriers (its MMA thread is
+// the only issuer), and the MMA commits arrive on `empty` / `tmem_full` in both CTAs.  PAIR takes tiled scales only.
+template <int BN, int ACC, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sa, const __grid_constant__ CUtensorMap tmap_sb,
                  const __grid_constant__ CUtensorMap tmap_d, const W4A4Args g) {
-  using Cfg = W4A4Cfg<BN, ACC, STAGES>;
+  using Cfg = W4A4Cfg<BN, ACC, STAGES, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t *bars = (uint64_t *)(smem + STAGES * Cfg::kStageBytes);
-  uint64_t *full = bars, *empty = bars + STAGES, *sf_ready = bars + 2 * STAGES, *tmem_full = bars + 3 * STAGES, *tmem_empty = tmem_full + ACC;
+  constexpr int NSF = Cfg::kSfBuffers, SD = Cfg::kScaleSlots;
+  uint8_t *scale_ring = smem + STAGES * Cfg::kStageBytes;
+  uint64_t *bars = (uint64_t *)(smem + Cfg::kRingBytes);
+  uint64_t *full = bars, *empty = bars + STAGES, *sf_ready = bars + 2 * STAGES, *sf_free = sf_ready + NSF, *sfs_full = sf_free + NSF,
+           *sfs_empty = sfs_full + SD, *tmem_full = sfs_empty + SD, *tmem_empty = tmem_full + ACC;
   uint32_t *tmem_slot = (uint32_t *)(tmem_empty + ACC);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
-  uint8_t *staging = smem + STAGES * Cfg::kStageBytes + 256;
+  uint8_t *staging = smem + Cfg::kRingBytes + Cfg::kBarrierBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gm = g.m, gn = g.n, gk = g.k, ktiles = g.ktiles;
   const bool a_image = g.a_image, b_image = g.b_image, sa_gather = g.sa_gather, sb_gather = g.sb_gather, d_tma = g.d_tma;
   const uint8_t *const sa_base = g.sa, *const sb_base = g.sb;
   const int sa_ld = g.sa_ld, sb_ld = g.sb_ld;
-  const int tiles_m = (gm + 127) / 128, tiles_n = (gn + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  // tiles_m counts row tiles of 128 (256 for a pair, whose CTA `rank` takes the 128-row tile 2 * (t % tiles_m) + rank)
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;
+  const int tiles_m = PAIR ? (gm + 255) / 256 : (gm + 127) / 128, tiles_n = (gn + BN - 1) / BN, ntiles = tiles_m * tiles_n;
+  const int tile_first = PAIR ? blockIdx.x >> 1 : blockIdx.x, tile_step = PAIR ? gridDim.x >> 1 : gridDim.x;
   const int nk = (gk + 255) / 256;
-  const bool any_gather = sa_gather || sb_gather;
+  const bool any_gather = !PAIR && (sa_gather || sb_gather);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 4); }
-    for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < NSF; ++b) { mbar_init(&sf_ready[b], PAIR ? 8 : 4); mbar_init(&sf_free[b], 1); }
+    for (int q = 0; q < SD; ++q) { mbar_init(&sfs_full[q], 1); mbar_init(&sfs_empty[q], 4); }
+    for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], PAIR ? 8 : 4); }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+    else tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -95,6 +128,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   unsigned *const status_word = g.status;
   // wait that also ends when another role has raised the abort flag
   auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+    if (mbar_try(bar, parity)) return true;   // the common case: no flag read, no clock read
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
@@ -103,53 +137,102 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   };
 
   if (warp == 0) {
-    // ---------------- producer: TMA for nibbles, bulk copies for tiled scales ----------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const int tm = t % tiles_m, tn = t / tiles_m;
-        for (int ks = 0; ks < nk; ++ks, ++it) {
-          const int s = it % STAGES;
-          bool okw;
-          okw = wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty);
-          if (!okw) goto done;
-          uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
-          uint8_t *sA = st, *sB = st + Cfg::kABytes, *sSfa = sB + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
-          const int ng = min(4, (gk - ks * 256) / 64);  // 64-value groups of this stage inside k
-          uint32_t bytes = Cfg::kABytes + Cfg::kBBytes;
-          if (!sa_gather) bytes += a_image ? 2048 : ng * 512;
-          if (!sb_gather)
-            for (int h = 0; h < BN / 128; ++h)
-              if (tn * BN + h * 128 < gn) bytes += b_image ? 2048 : ng * 512;
-          mbar_arrive_expect_tx(&full[s], bytes);
-          if (a_image) tma_load_3d(sA, &tmap_a, 0, 0, tm * ktiles + ks, &full[s]);
-          else tma_load_2d(sA, &tmap_a, ks * 128, tm * 128, &full[s]);
-          if (b_image) {
-            for (int h = 0; h < BN / 128; ++h) tma_load_3d(sB + h * 16384, &tmap_b, 0, 0, (tn * (BN / 128) + h) * ktiles + ks, &full[s]);
+    // ---------------- producer: one TMA instruction per iteration ----------------
+    // Issuing a copy instruction costs the issuing warp more than a hundred cycles whatever it moves, so every copy of an
+    // iteration -- A and B nibbles, and the 2 KiB scale tiles, which are tensors of their own ([row tile][k] of 8-byte
+    // words; a box is the four 512-byte tiles of 256 values of k, zero-filled past k) -- is issued by ONE instruction whose
+    // lanes name different tensor maps, coordinates, destinations and barriers:
+    //   lane 0: A nibbles; lanes 1, 2: B nibbles (lane 2: the second 128 rows when B is an image and a CTA holds 256 of
+    //   them); lane 3: A scales; lanes 4, 5: B scales of the tile's two 128-row halves.
+    // Single CTA: the scale tiles land in the stage, counted on `full` with the nibbles.  Pair: the nibbles of both CTAs
+    // count on the even CTA's `full`; the scale tiles go to the scale ring, kScaleLead iterations ahead of the nibbles.
+    {
+      const int my_tiles = tile_first < ntiles ? (ntiles - tile_first + tile_step - 1) / tile_step : 0;
+      const int total = my_tiles * nk;
+      const bool scale_lane = lane >= 3 && lane < 6, copy_lane = lane < 6;
+      const bool for_a = lane == 0 || lane == 3;
+      const int part = lane < 3 ? lane - 1 : lane - 4;               // B: which 128-row part this lane serves
+      const bool image = for_a ? a_image : b_image;
+      const CUtensorMap *const map = lane == 0 ? &tmap_a : lane < 3 ? &tmap_b : lane == 3 ? &tmap_sa : &tmap_sb;
+      const int lead = (PAIR && scale_lane) ? Cfg::kScaleLead : 0;   // this lane's copies run `lead` iterations ahead
+      const uint32_t nibble_bytes = Cfg::kABytes + Cfg::kBBytes;
+      // this lane's cursor: iteration l_it = (tile l_t, k step l_ks), and what the tile fixes: is there a copy, its row / tile coordinates
+      int l_it = 0, l_t = tile_first, l_ks = 0;
+      bool live = false;
+      int y0 = 0, z0 = 0;
+      uint32_t dst_off = 0;
+      int n_sf = 0;   // lane 0: scale tiles per iteration of the tile (for the byte count)
+      auto tile_setup = [&]() {
+        const int tm = PAIR ? 2 * (l_t % tiles_m) + rank : l_t % tiles_m, tn = l_t / tiles_m;
+        const bool a_live = tm * 128 < gm;   // a pair's second row tile may lie past m: zero nibbles, no scales to fetch
+        live = false; y0 = 0; z0 = 0;
+        if (lane == 0) { live = true; dst_off = 0; if (image) z0 = tm * ktiles; else y0 = tm * 128; }
+        else if (lane < 3) {
+          if (PAIR) { live = part == 0; dst_off = Cfg::kABytes; if (image) z0 = (tn * (BN / 128) + rank) * ktiles; else y0 = tn * BN + rank * (BN / 2); }
+          else if (image) { live = part < BN / 128; dst_off = Cfg::kABytes + part * 16384; z0 = (tn * (BN / 128) + part) * ktiles; }
+          else { live = part == 0; dst_off = Cfg::kABytes; y0 = tn * BN; }
+        } else if (scale_lane) {
+          const int rt = for_a ? tm : tn * (BN / 128) + part;
+          live = for_a ? (!sa_gather && a_live) : (!sb_gather && part < BN / 128 && rt * 128 < gn);
+          dst_off = (PAIR ? 0 : Cfg::kABytes + Cfg::kBBytes) + (for_a ? 0 : Cfg::kSfaBytes + part * 2048);
+          y0 = image ? rt * ktiles : rt;   // image: one row of the scale tensor per (row tile, k tile); plain: per row tile
+        }
+        n_sf = 0;
+        if (!sa_gather && a_live) ++n_sf;
+        if (!sb_gather)
+          for (int h = 0; h < BN / 128; ++h) n_sf += tn * BN + h * 128 < gn;
+      };
+      if (total > 0) tile_setup();
+      // the scale lanes of a pair start `lead` iterations early: iterations it < 0 issue scale tiles only
+      for (int it = PAIR ? -Cfg::kScaleLead : 0; it < total; ++it) {
+        const int s = it % STAGES;
+        bool okw = true;
+        if (it >= 0) okw = wait(&empty[s], ((it / STAGES) & 1) ^ 1, kStatusWaitEmpty);
+        const int sj = it + Cfg::kScaleLead, slot = PAIR ? sj % (SD ? SD : 1) : 0;   // pair: the scale iteration issued now
+        const bool scales_now = PAIR && sj < total;
+        if (scales_now) okw = okw && wait(&sfs_empty[slot], ((sj / (SD ? SD : 1)) & 1) ^ 1, kStatusWaitEmpty);
+        if (!__all_sync(0xFFFFFFFFu, okw)) goto done;
+        if (lane == 0) {
+          if (PAIR) {
+            if (it >= 0 && rank == 0) mbar_arrive_expect_tx(&full[s], 2 * nibble_bytes);
           } else {
-            tma_load_2d(sB, &tmap_b, ks * 128, tn * BN, &full[s]);
+            mbar_arrive_expect_tx(&full[s], nibble_bytes + n_sf * 2048);
           }
-          if (!sa_gather) {
-            if (a_image) bulk_load(sSfa, sa_base + ((size_t)tm * ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-            else bulk_load(sSfa, sa_base + ((size_t)tm * ((-sa_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
+        }
+        if (PAIR && lane == 3 && scales_now) {
+          // lane 3's cursor stands at iteration sj: its tile's scale tile count (A's may be missing past m)
+          mbar_arrive_expect_tx(&sfs_full[slot], n_sf * 2048);
+        }
+        __syncwarp();
+        const bool mine = copy_lane && live && (lead ? scales_now : it >= 0);
+        if (mine) {
+          uint32_t dst, bar;   // pair: barrier addresses in the cluster's window (the nibbles' in the even CTA, the scales' here)
+          if (PAIR && scale_lane) {
+            dst = smem_u32(scale_ring + slot * Cfg::kScaleSlotBytes + dst_off);
+            bar = mbar_addr_rank(&sfs_full[slot], rank);
+          } else {
+            dst = smem_u32(smem + (size_t)s * Cfg::kStageBytes + dst_off);
+            bar = PAIR ? mbar_addr_rank(&full[s], 0) : smem_u32(&full[s]);
           }
-          if (!sb_gather) {
-            for (int h = 0; h < BN / 128; ++h) {
-              const int rt = tn * (BN / 128) + h;
-              if (rt * 128 >= gn) continue;
-              if (b_image) bulk_load(sSfb + h * 2048, sb_base + ((size_t)rt * ktiles + ks) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-              else bulk_load(sSfb + h * 2048, sb_base + ((size_t)rt * ((-sb_ld) >> 2) + ks * 4) * 512, ng * 512, &full[s]);
-            }
-          }
+          int x, y, z;
+          if (scale_lane) { x = image ? 0 : l_ks * 256; y = image ? y0 + l_ks : y0; z = 0; }
+          else { x = image ? 0 : l_ks * 128; y = y0; z = image ? z0 + l_ks : 0; }
+          if (PAIR) tma_load_3d_pair(dst, map, x, y, z, bar);
+          else tma_load_3d_at(dst, map, x, y, z, bar);
+        }
+        // advance this lane's cursor (scale lanes of a pair run from iteration 0 while it < 0 ... they start at l_it = 0 when it = -lead)
+        if (lead ? scales_now : it >= 0) {
+          ++l_it;
+          if (++l_ks == nk) { l_ks = 0; l_t += tile_step; if (l_it < total) tile_setup(); }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_mxf4nvf4(128, BN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_mxf4nvf4(PAIR ? 256 : 128, BN);
       uint32_t it = 0, tile_i = 0;
-      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+      for (int t = tile_first; t < ntiles; t += tile_step, ++tile_i) {
         const int acc = tile_i % ACC;
         bool okw;
         okw = wait(&tmem_empty[acc], ((tile_i / ACC) & 1) ^ 1, kStatusWaitTmemEmpty);
@@ -160,12 +243,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int s = it % STAGES;
           // tiled scales: four warps have put the stage's scale columns into tensor memory (which implies the operands landed);
           // gathered scales: this thread copies them from shared memory itself
-          okw = any_gather ? wait(&full[s], (it / STAGES) & 1, kStatusWaitFull) : wait(&sf_ready[s], (it / STAGES) & 1, kStatusWaitSf);
+          const int b = PAIR ? it % NSF : s;   // scale buffer in tensor memory
+          if (PAIR) okw = wait(&full[s], (it / STAGES) & 1, kStatusWaitFull) && wait(&sf_ready[b], (it / NSF) & 1, kStatusWaitSf);
+          else okw = any_gather ? wait(&full[s], (it / STAGES) & 1, kStatusWaitFull) : wait(&sf_ready[s], (it / STAGES) & 1, kStatusWaitSf);
           if (!okw) goto done;
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
           const uint32_t sA = st, sB = st + Cfg::kABytes, sSfa = sB + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;
-          const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + s * Cfg::kSfCols;
+          const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + b * Cfg::kSfCols;
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
           const int ng = min(4, (gk - ks * 256) / 64);
           const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
@@ -177,11 +262,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int h = 0; h < BN / 128; ++h)
                 tmem_cp_32x128b_warpx4(sfb_tmem + (BN / 32) * j + 4 * h, smem_desc_sf(sSfb + h * 2048 + j * 512));
             }
-            mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+            if (PAIR) mma_mxf4nvf4_pair(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
+            else mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, (ks | j) != 0);
           }
-          tc_commit(&empty[s]);
+          if (PAIR) { tc_commit_pair(&empty[s]); tc_commit_pair(&sf_free[b]); }
+          else tc_commit(&empty[s]);
         }
-        tc_commit(&tmem_full[acc]);
+        if (PAIR) tc_commit_pair(&tmem_full[acc]);
+        else tc_commit(&tmem_full[acc]);
       }
     }
   } else if (warp < 6) {
@@ -203,8 +291,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const float colp0 = (gb && !gb_stride) ? gb[0] : 1.f;
     float amax = 0.f;
     uint32_t tile_i = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
-      const int tm = t % tiles_m, tn = t / tiles_m, acc = tile_i % ACC;
+    for (int t = tile_first; t < ntiles; t += tile_step, ++tile_i) {
+      const int tm = PAIR ? 2 * (t % tiles_m) + rank : t % tiles_m, tn = t / tiles_m, acc = tile_i % ACC;
       const int i = tm * 128 + quad * 32 + lane;
       const bool row_ok = i < gm;
       const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
@@ -295,7 +383,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       auto release_acc = [&]() {  // every column is in registers: the MMA warp may start the next tile on this accumulator
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_rank(&tmem_empty[acc], 0);
+          else mbar_arrive(&tmem_empty[acc]);
+        }
       };
       uint32_t ra[32], rb[32];
       tmem_ld32(acc_addr, ra);
@@ -320,35 +411,49 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // tcgen05.cp.32x128b.warpx4 would produce); each of the four warps writes its own quadrant, off the MMA issuer's queue.
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t it = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    for (int t = tile_first; t < ntiles; t += tile_step) {
+      const bool a_live = !PAIR || (2 * (t % tiles_m) + rank) * 128 < gm;
       for (int ks = 0; ks < nk; ++ks, ++it) {
-        const int s = it % STAGES;
-        if (!wait(&full[s], (it / STAGES) & 1, kStatusWaitGather)) goto done;
+        // single CTA: the tiles came with stage s; pair: they lie in slot it % SD of the scale ring
+        const int s = it % STAGES, slot = it % (SD ? SD : 1), b = PAIR ? it % NSF : s;
+        if (PAIR ? !wait(&sfs_full[slot], (it / (SD ? SD : 1)) & 1, kStatusWaitGather) : !wait(&full[s], (it / STAGES) & 1, kStatusWaitGather)) goto done;
         const uint8_t *st = smem + (size_t)s * Cfg::kStageBytes;
-        const uint8_t *sSfa = st + Cfg::kABytes + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
-        const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + s * Cfg::kSfCols + lane_base;
+        const uint8_t *sSfa = PAIR ? scale_ring + slot * Cfg::kScaleSlotBytes : st + Cfg::kABytes + Cfg::kBBytes, *sSfb = sSfa + Cfg::kSfaBytes;
+        const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + b * Cfg::kSfCols + lane_base;
         const int ng = min(4, (gk - ks * 256) / 64);
+        uint4 va[4], vb[BN / 128][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) va[j] = (j < ng && a_live) ? *(const uint4 *)(sSfa + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int h = 0; h < BN / 128; ++h)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) vb[h][j] = j < ng ? *(const uint4 *)(sSfb + h * 2048 + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
+        if (PAIR) {   // the slot is free again; the tensor memory buffer must have been read by the MMAs that last used it
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sfs_empty[slot]);
+          if (!wait(&sf_free[b], ((it / NSF) & 1) ^ 1, kStatusWaitGather)) goto done;
+          tc_fence_after();
+        }
         uint32_t r[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 v = j < ng ? *(const uint4 *)(sSfa + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
-          r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
-        }
+        for (int j = 0; j < 4; ++j) { r[4 * j] = va[j].x; r[4 * j + 1] = va[j].y; r[4 * j + 2] = va[j].z; r[4 * j + 3] = va[j].w; }
         tmem_st16(sf_tmem, r);
 #pragma unroll
         for (int part = 0; part < BN / 128; ++part) {   // B: group j occupies BN / 32 columns: [half 0: 4 | half 1: 4]
 #pragma unroll
           for (int q = 0; q < 4; ++q) {                 // register quad q of this part = columns 4 q .. 4 q + 3 of the 16
             const int col = part * 16 + 4 * q, j = col / (BN / 32), h = (col % (BN / 32)) / 4;
-            const uint4 v = j < ng ? *(const uint4 *)(sSfb + h * 2048 + j * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
-            r[4 * q] = v.x; r[4 * q + 1] = v.y; r[4 * q + 2] = v.z; r[4 * q + 3] = v.w;
+            r[4 * q] = vb[h][j].x; r[4 * q + 1] = vb[h][j].y; r[4 * q + 2] = vb[h][j].z; r[4 * q + 3] = vb[h][j].w;
           }
           tmem_st16(sf_tmem + 16 + part * 16, r);
         }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sf_ready[s]);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_rank(&sf_ready[b], 0);
+          else mbar_arrive(&sf_ready[s]);
+        }
       }
     }
   } else {
@@ -357,7 +462,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int w = warp - 6;
     const ScalePos pa{sa_ld}, pb{sb_ld};
     uint32_t it = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    for (int t = tile_first; t < ntiles; t += tile_step) {
       const int tm = t % tiles_m, tn = t / tiles_m;
       for (int ks = 0; ks < nk; ++ks, ++it) {
         if ((int)(it & 3) != w) continue;
@@ -390,11 +495,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   }
 done:
+  __syncwarp();   // lanes that left a role's loop early rejoin their warp before the aligned barriers below
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still arrive on its barriers
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -445,29 +553,63 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Block scales in 512-byte tiles as a tensor of 8-byte words: `rows` rows (one per 128-row tile of the operand; one per
+// image tile for an image) of row_bytes bytes, `stride` bytes apart; a box is 2 KiB of one row (the four tiles of 256
+// values of k), zero-filled where it passes the end of the row.  Rank 3 like the nibble maps, so that one instruction
+// can issue both.
+static bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {row_bytes / 8, rows, 1};
+  cuuint64_t strides[2] = {stride, stride * rows};
+  cuuint32_t box[3] = {256, 1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool gemm_w4a4_supports(const GemmArgs &g) {
   return g.B.dtype == NVFP4A_NVFP4 && !g.A.ue && !g.B.q.ue && !g.x.mask && g.k >= 64 && encode_fn() != nullptr;
 }
 
-template <int BN, int ACC, int STAGES>
-static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &td, const W4A4Args &a, cudaStream_t s) {
-  using Cfg = W4A4Cfg<BN, ACC, STAGES>;
+template <int BN, int ACC, int STAGES, bool PAIR>
+static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb, const CUtensorMap &td,
+                              const W4A4Args &a, cudaStream_t s) {
+  using Cfg = W4A4Cfg<BN, ACC, STAGES, PAIR>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_kernel<BN, ACC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_kernel<BN, ACC, STAGES, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev & 63] = true;
   }
+  if (PAIR) {   // clusters of two CTAs, one pair per 256 x BN tile in flight
+    const int tiles = ((a.m + 255) / 256) * ((a.n + BN - 1) / BN), pairs = device_sms() / 2;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(2 * (tiles < pairs ? tiles : pairs), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<BN, ACC, STAGES, PAIR>, ta, tb, tsa, tsb, td, a);
+  }
   const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
   const int grid = tiles < device_sms() ? tiles : device_sms();
-  gemm_w4a4_kernel<BN, ACC, STAGES><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ta, tb, td, a);
+  gemm_w4a4_kernel<BN, ACC, STAGES, PAIR><<<grid, kThreads, Cfg::kSmemBytes, s>>>(ta, tb, tsa, tsb, td, a);
   return cudaGetLastError();
 }
 
 static int g_w4a4_bn = 0;  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
 void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
+// -1 = automatic; 0 / 1 pin the CTA-pair kernel off / on where it applies (nvfp4a_b200_set_pair).  Automatic currently means
+// off: at 4096^3 the pair form takes 64 us against 58 us (its producer warp, with two rings to feed, is the slower issuer).
+static int g_w4a4_pair = -1;
+void set_w4a4_pair(int mode) { g_w4a4_pair = mode; }
 
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   W4A4Args a;
@@ -477,23 +619,35 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   a.status = kernel_status_device_ptr();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
   const int bn = g_w4a4_bn ? g_w4a4_bn : (g.n > 128 ? 256 : 128);
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tsa, tsb;
+  memset(&tsa, 0, sizeof tsa);
+  memset(&tsb, 0, sizeof tsb);
   const Fp4Operand &A = g.A, &B = g.B.q;
   a.a_image = A.image; a.b_image = B.image;
   auto tiled_ok = [](const Fp4Operand &o) { return o.sld < 0 && ((uintptr_t)o.sc & 15) == 0; };
+  // the CTA-pair kernel: 256 x 256 tiles, scales in aligned tiles (or images) on both sides, more than one row tile
+  const bool pair = bn == 256 && g_w4a4_pair == 1 && g.m > 128 && (A.image || tiled_ok(A)) && (B.image || tiled_ok(B));
   if (A.image) {
-    if (!make_tmap_bytes(&ta, A.data, 128, 128, 128, 128, (uint64_t)((g.m + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    const uint64_t tiles = (uint64_t)((g.m + 127) / 128) * a.ktiles;
+    if (!make_tmap_bytes(&ta, A.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    if (!make_tmap_scales(&tsa, (const uint8_t *)A.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
     a.sa = A.data; a.sa_gather = 0;
   } else {
-    if (!make_tmap_bytes(&ta, A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)A.ld / 2, 128)) return cudaErrorInvalidValue;
+    if (!make_tmap_bytes(&ta, A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)A.ld / 2, 128, 1, (uint64_t)A.ld / 2 * g.m)) return cudaErrorInvalidValue;
     a.sa = A.sc; a.sa_ld = A.sld; a.sa_gather = tiled_ok(A) ? 0 : 1;
+    if (!a.sa_gather && !make_tmap_scales(&tsa, A.sc, (uint64_t)((-A.sld) >> 2) * 512, (uint64_t)(g.m + 127) / 128, (uint64_t)((-A.sld) >> 2) * 512))
+      return cudaErrorInvalidValue;
   }
   if (B.image) {
-    if (!make_tmap_bytes(&tb, B.data, 128, 128, 128, 128, (uint64_t)((g.n + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    const uint64_t tiles = (uint64_t)((g.n + 127) / 128) * a.ktiles;
+    if (!make_tmap_bytes(&tb, B.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    if (!make_tmap_scales(&tsb, (const uint8_t *)B.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
     a.sb = B.data; a.sb_gather = 0;
   } else {
-    if (!make_tmap_bytes(&tb, B.data, (uint64_t)g.k / 2, (uint64_t)g.n, (uint64_t)B.ld / 2, bn)) return cudaErrorInvalidValue;
+    if (!make_tmap_bytes(&tb, B.data, (uint64_t)g.k / 2, (uint64_t)g.n, (uint64_t)B.ld / 2, pair ? 128 : bn, 1, (uint64_t)B.ld / 2 * g.n)) return cudaErrorInvalidValue;
     a.sb = B.sc; a.sb_ld = B.sld; a.sb_gather = tiled_ok(B) ? 0 : 1;
+    if (!a.sb_gather && !make_tmap_scales(&tsb, B.sc, (uint64_t)((-B.sld) >> 2) * 512, (uint64_t)(g.n + 127) / 128, (uint64_t)((-B.sld) >> 2) * 512))
+      return cudaErrorInvalidValue;
   }
   // D through TMA when its base and column stride are 16-byte aligned; otherwise plain stores from registers
   CUtensorMap td;
@@ -501,8 +655,9 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   const int esz = dense_bytes(g.e.d_dtype);
   a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
             make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
-  if (bn == 256) return launch_cfg<256, 1, 4>(ta, tb, td, a, s);
-  return launch_cfg<128, 2, 6>(ta, tb, td, a, s);
+  if (pair) return launch_cfg<256, 1, 5, true>(ta, tb, tsa, tsb, td, a, s);
+  if (bn == 256) return launch_cfg<256, 1, 4, false>(ta, tb, tsa, tsb, td, a, s);
+  return launch_cfg<128, 2, 6, false>(ta, tb, tsa, tsb, td, a, s);
 }
 
 }  // namespace nvb
@@ -516,6 +671,12 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
   cudaError_t e = cudaMemcpy(status, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && reset) e = cudaMemset(p, 0, sizeof(unsigned int));
   return cuda_fail(e, "nvfp4a_b200_kernel_status");
+}
+
+extern "C" int nvfp4a_b200_set_pair(int mode) {
+  if (mode < -1 || mode > 1) return -1;
+  nvb::set_w4a4_pair(mode);
+  return 0;
 }
 
 extern "C" int nvfp4a_b200_set_tile_n(int bn) {

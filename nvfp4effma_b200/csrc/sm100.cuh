@@ -30,16 +30,33 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
 // Polls the barrier's phase `parity`; gives up (false) after kMaxWaitCycles SM clock cycles -- about two seconds, far
 // longer than any healthy wait of these kernels.
 constexpr long long kMaxWaitCycles = 4000000000ll;
+constexpr uint32_t kWaitHintNs = 1000000u;   // one millisecond per parked poll
+// one poll of the barrier's phase `parity`
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;   // the common case costs no clock read
   const uint32_t addr = smem_u32(bar);
   const long long start = clock64();
   for (;;) {
+    // The time hint lets the hardware park the thread until the phase completes (or the hint runs out) instead of having
+    // it spin: a spinning warp takes issue slots from the warps of its scheduler that have work (the epilogue warps).
     uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity), "r"(kWaitHintNs) : "memory");
     if (done) return true;
     if (clock64() - start > kMaxWaitCycles) return false;
   }
+}
+// arrive on the barrier that sits at `own_bar`'s address in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_rank(uint64_t *own_bar, uint32_t rank) {
+  uint32_t addr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(own_bar)), "r"(rank));
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.cp / mma operand reads)
@@ -80,6 +97,22 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
+// CTA pair: the copy lands in this CTA's shared memory, its bytes are counted on the barrier at `own_bar`'s address in the
+// pair's even CTA (rank 0 of a cluster of two), whose MMA thread waits for both CTAs' operands on that one barrier.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar_addr) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+}
+// the same with the barrier given as a shared-memory address (lanes of one instruction may name different barriers)
+__device__ __forceinline__ void tma_load_3d_at(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar_addr) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_addr_rank(uint64_t *own_bar, uint32_t rank) {
+  uint32_t addr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(own_bar)), "r"(rank));
+  return addr;
+}
 // contiguous copy: both addresses 16-byte aligned, bytes a multiple of 16
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -107,11 +140,24 @@ __device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t cols) {  // 
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {  // whole warp
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+// CTA pair (cta_group::2): one warp of EACH of the two CTAs issues these, with the same shared memory slot offset
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *slot, uint32_t cols) {  // whole warp
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {  // whole warp
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // arrives on the barrier once every tcgen05 operation this thread issued before has completed
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// pair MMAs: arrives on the barrier at this address in both CTAs of the pair (cluster of two: ranks 0 and 1)
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 // 32 lanes x 32 consecutive columns of 32 bits -> 32 registers per thread (warp w reads lanes 32 (w % 4) ..)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
@@ -188,6 +234,15 @@ __device__ __forceinline__ void mma_mxf4nvf4(uint32_t d_tmem, uint64_t a_desc, u
                                              uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// The same over a CTA pair, issued by one thread of the even CTA: M = 256 (128 rows of A from each CTA's shared memory), B's
+// N rows half from each CTA, D and the block scales at the same tensor memory addresses in both CTAs (each CTA holds the
+// scales of its own 128 rows of A and of ALL N rows of B).
+__device__ __forceinline__ void mma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                                  uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {

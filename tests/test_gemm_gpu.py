@@ -261,6 +261,33 @@ def test_w4a4_tcgen05_kernel(bn, fa, fb):
         L.lib.nvfp4a_b200_set_tile_n(0)
 
 
+def test_w4a4_cta_pair_kernel_matches_the_single_cta_kernel():
+    """The CTA-pair form (tcgen05.mma.cta_group::2, 256 x 256 tiles) against the bound and, bit for bit, against the single-CTA
+    kernel, which feeds the same block products to the tensor cores in the same k order: odd numbers of 128-row tiles, tails
+    in m / n / k, several tiles per pair (the barrier phases wrap), every epilogue input."""
+    sizes = [(256, 256, 256), (129, 130, 64), (384, 512, 1024), (1100, 1300, 512), (257, 129, 320), (2304, 2100, 1344), (4096, 4096, 2048)]
+    try:
+        for i, (m, n, k) in enumerate(sizes):
+            c = Case(m, n, k, L.NVFP4, OUTS[i % 3], -1 if i % 4 == 1 else OUTS[i % 3], L.BF16 if i % 2 else -1, 1.25 if i % 2 else 1.0,
+                     1.0 if i % 4 == 1 else 0.0, fa=SW, fb=SW | (PR if i % 3 == 2 else 0))
+            h = build_case(c, 900 + i)
+            if i in (2, 6):   # dense D (ldd = m): the epilogue stores by TMA
+                h["ldd"] = m
+                h["Dinit"] = np.frombuffer(b"\xA5" * (m * n * esize(c.dt)), dtype=np.float32 if c.dt == L.FP32 else np.uint16).copy()
+            exp = oracle_case(c, h, want_ref=True) if m * n <= 1500 * 1500 else None
+            res = []
+            for mode in (1, 0):
+                assert L.lib.nvfp4a_b200_set_pair(mode) == 0
+                got, amax = run_gemm(c, h)
+                assert L.lib.nvfp4a_b200_last_route() == 4 and kernel_status() == 0
+                if exp is not None:
+                    check_bound(c, h, got, amax, exp)
+                res.append((got, amax))
+            assert np.array_equal(res[0][0], res[1][0]) and res[0][1] == res[1][1], (m, n, k)
+    finally:
+        L.lib.nvfp4a_b200_set_pair(-1)
+
+
 def make_image(kind, dfp4, rows, k, ld):
     nbytes = L.lib.nvfp4a_tc_image_bytes(kind, L.NVFP4, rows, k)
     img = torch.full((nbytes + 16,), 0xEE, dtype=torch.uint8, device="cuda")
