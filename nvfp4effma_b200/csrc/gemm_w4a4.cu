@@ -65,7 +65,7 @@ struct W4A4Cfg {
   static_assert(kAccCols + kSfBuffers * kSfCols <= kTmemCols, "tensor memory budget");
 };
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 448;
 constexpr unsigned kStatusWaitFull = 0x101, kStatusWaitEmpty = 0x102, kStatusWaitTmemFull = 0x103, kStatusWaitTmemEmpty = 0x104,
                    kStatusWaitGather = 0x105, kStatusWaitSf = 0x106;
 
@@ -107,7 +107,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], any_gather ? 2 : 1); mbar_init(&empty[s], 1); }
     for (int b = 0; b < NSF; ++b) { mbar_init(&sf_ready[b], PAIR ? 8 : 4); mbar_init(&sf_free[b], 1); }
     for (int q = 0; q < SD; ++q) { mbar_init(&sfs_full[q], 1); mbar_init(&sfs_empty[q], 4); }
-    for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], PAIR ? 8 : 4); }
+    for (int a = 0; a < ACC; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], PAIR ? 16 : 8); }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
@@ -272,9 +272,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         else tc_commit(&tmem_full[acc]);
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 6 || warp >= 10) {
     // ---------------- epilogue: TMEM -> registers -> (staging tile -> TMA store | direct stores) ----------------
+    // Two groups of four warps (2-5 and 10-13, one warp per 32-lane quadrant in each) take alternate 32-column chunks of the
+    // accumulator, each with its own 4 KiB staging tile, named barrier and store-issuing lane: the groups' TMEM loads,
+    // arithmetic, shared-memory stores and waits for the TMA unit overlap on the four schedulers.
     // Everything the loops need is held in plain locals (see the note on kernel parameters above).
+    const int group = warp >= 10, bar_id = 1 + group;
+    uint8_t *const stg = staging + group * 4096;
     const int quad = warp & 3;
     const float *const ga = g.e.ga, *const gb = g.e.gb;
     const int ga_stride = g.e.ga_stride, gb_stride = g.e.gb_stride;
@@ -285,8 +290,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int ldd = g.e.ldd, d_dtype = g.e.d_dtype;
     float *const amax_out = g.e.amax;
     const int esz = dense_bytes(d_dtype);
-    const int cw = esz == 2 ? 32 : 16;          // columns per staging round: 128 rows x cw columns = 8 KiB
-    const bool leader = warp == 2 && lane == 0; // issues and tracks the TMA stores
+    const int cw = esz == 2 ? 16 : 8;           // columns per staging round: 128 rows x cw columns = 4 KiB
+    const bool leader = (warp == 2 || warp == 10) && lane == 0; // issues and tracks its group's TMA stores
     const bool fast = beta == 0.f && gb_stride == 0;  // one scale per lane, no C: the common case
     const float colp0 = (gb && !gb_stride) ? gb[0] : 1.f;
     float amax = 0.f;
@@ -298,11 +303,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
       const float bias = (row_ok && biasptr) ? load_dense(bias_dtype, biasptr, i) : 0.f;
       const float s_lane = __fmul_rn(__fmul_rn(rowp, colp0), gf);
-      // the four epilogue warps decide together whether to go on: none may be left alone at a named barrier
+      // the four warps of a group decide together whether to go on: none may be left alone at a named barrier
       bool okw;
       okw = wait(&tmem_full[acc], (tile_i / ACC) & 1, kStatusWaitTmemFull);
       if (!okw) *abort_flag = 1;
-      named_barrier(1, 128);
+      named_barrier(bar_id, 128);
       if (*abort_flag) goto done;
       tc_fence_after();
       const int nchunks = min(BN / 32, (gn - tn * BN + 31) / 32);
@@ -360,22 +365,34 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           return;
         }
-        for (int half = 0; half < 32 / cw; ++half) {
-          if (leader) bulk_wait_read_all();   // the previous store has finished reading the staging tile
-          named_barrier(1, 128);
-          const int rr = quad * 32 + lane;
-          if (esz == 2) {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) ((uint16_t *)staging)[jj * 128 + rr] = (uint16_t)r[jj];
-          } else {
-#pragma unroll
-            for (int jj = 0; jj < 16; ++jj) ((uint32_t *)staging)[jj * 128 + rr] = half ? r[16 + jj] : r[jj];
-          }
+        const int rr = quad * 32 + lane;
+        auto round_begin = [&]() {
+          if (leader) bulk_wait_read_all();   // the group's previous store has finished reading its staging tile
+          named_barrier(bar_id, 128);
+        };
+        auto round_end = [&](int col) {
           fence_proxy_async_smem();
-          named_barrier(1, 128);
+          named_barrier(bar_id, 128);
           if (leader) {
-            tma_store_2d(&tmap_d, staging, tm * 128, j0 + half * cw);
+            tma_store_2d(&tmap_d, stg, tm * 128, col);
             bulk_commit();
+          }
+        };
+        if (esz == 2) {
+#pragma unroll
+          for (int rd = 0; rd < 2; ++rd) {
+            round_begin();
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) ((uint16_t *)stg)[jj * 128 + rr] = (uint16_t)r[rd * 16 + jj];
+            round_end(j0 + rd * 16);
+          }
+        } else {
+#pragma unroll
+          for (int rd = 0; rd < 4; ++rd) {
+            round_begin();
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) ((uint32_t *)stg)[jj * 128 + rr] = r[rd * 8 + jj];
+            round_end(j0 + rd * 8);
           }
         }
       };
@@ -389,17 +406,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       };
       uint32_t ra[32], rb[32];
-      tmem_ld32(acc_addr, ra);
-      for (int c = 0; c < nchunks; c += 2) {
+      if (group < nchunks) tmem_ld32(acc_addr + group * 32, ra);
+      else release_acc();   // no chunk of this tile for the group
+      for (int c = group; c < nchunks; c += 4) {
         tmem_ld_wait();
-        if (c + 1 < nchunks) tmem_ld32(acc_addr + (c + 1) * 32, rb);
+        if (c + 2 < nchunks) tmem_ld32(acc_addr + (c + 2) * 32, rb);
         else release_acc();
         drain(ra, c);
-        if (c + 1 < nchunks) {
+        if (c + 2 < nchunks) {
           tmem_ld_wait();
-          if (c + 2 < nchunks) tmem_ld32(acc_addr + (c + 2) * 32, ra);
+          if (c + 4 < nchunks) tmem_ld32(acc_addr + (c + 4) * 32, ra);
           else release_acc();
-          drain(rb, c + 1);
+          drain(rb, c + 2);
         }
       }
     }
@@ -654,7 +672,7 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   memset(&td, 0, sizeof td);
   const int esz = dense_bytes(g.e.d_dtype);
   a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
-            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 32 : 16);
+            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 16 : 8);
   if (pair) return launch_cfg<256, 1, 5, true>(ta, tb, tsa, tsb, td, a, s);
   if (bn == 256) return launch_cfg<256, 1, 4, false>(ta, tb, tsa, tsb, td, a, s);
   return launch_cfg<128, 2, 6, false>(ta, tb, tsa, tsb, td, a, s);

@@ -151,28 +151,32 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   if (warp == 0) {
     // ---------------- producer ----------------
-    if (lane == 0) {
-      for (int it = 0; it < nloc; ++it) {
-        const int s = it % kStages, c = c0 + it;
-        if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty)) break;
-        uint8_t *sW = stages + (size_t)s * stage_bytes, *sSf = sW + kDataBytes;
-        const uint32_t sf_bytes = linear ? (uint32_t)kRawSfBytes : (second ? 4096u : 2048u);
-        mbar_arrive_expect_tx(&full[s], kDataBytes + sf_bytes);
+    // A copy instruction costs the issuing warp 150-200 cycles whatever it moves, and the ring's first stages are all
+    // requested before anything else can happen: lanes 0 and 1 issue the stage's two tensor copies in one instruction,
+    // lanes 2 and 3 the bulk copies of the scale tiles in another.  All lanes wait on `empty` together.
+    for (int it = 0; it < nloc; ++it) {
+      const int s = it % kStages, c = c0 + it;
+      const bool okw = wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty);
+      if (!__all_sync(0xFFFFFFFFu, okw)) break;
+      uint8_t *sW = stages + (size_t)s * stage_bytes, *sSf = sW + kDataBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&full[s], kDataBytes + (linear ? (uint32_t)kRawSfBytes : (second ? 4096u : 2048u)));
+      __syncwarp();
+      if (lane < 2) {
         if (a_image) {
           // a tile index past the image reads zeros
-          tma_load_3d(sW, &tmap_a, 0, 0, (2 * tm) * ktiles + c, &full[s]);
-          tma_load_3d(sW + 16384, &tmap_a, 0, 0, second ? (2 * tm + 1) * ktiles + c : 0x7FFFFFF, &full[s]);
-          bulk_load(sSf, sa_base + ((size_t)(2 * tm) * ktiles + c) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-          if (second) bulk_load(sSf + 2048, sa_base + ((size_t)(2 * tm + 1) * ktiles + c) * kImgTileBytes + kImgDataBytes, 2048, &full[s]);
-        } else {
+          const int z = lane == 0 ? (2 * tm) * ktiles + c : (second ? (2 * tm + 1) * ktiles + c : 0x7FFFFFF);
+          tma_load_3d(sW + lane * 16384, &tmap_a, 0, 0, z, &full[s]);
+        } else if (lane == 0) {
           tma_load_2d(sW, &tmap_a, c * 128, tm * 256, &full[s]);
-          if (linear) {
-            tma_load_2d(sW + kStageBytes, &tmap_s, c * 4, tm * 256, &full[s]);   // 16 bytes (4 words) of 256 rows; rows past m read zeros
-          } else {
-            const size_t tile_stride = (size_t)((-sa_ld) >> 2) * 512;
-            bulk_load(sSf, sa_base + (size_t)(2 * tm) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
-            if (second) bulk_load(sSf + 2048, sa_base + (size_t)(2 * tm + 1) * tile_stride + (size_t)c * 2048, 2048, &full[s]);
-          }
+        } else if (linear) {
+          tma_load_2d(sW + kStageBytes, &tmap_s, c * 4, tm * 256, &full[s]);   // 16 bytes (4 words) of 256 rows; rows past m read zeros
+        }
+      } else if (lane < 4 && !linear) {
+        const int h = lane - 2;
+        if (h == 0 || second) {
+          const uint8_t *src = a_image ? sa_base + ((size_t)(2 * tm + h) * ktiles + c) * kImgTileBytes + kImgDataBytes
+                                       : sa_base + (size_t)(2 * tm + h) * ((size_t)((-sa_ld) >> 2) * 512) + (size_t)c * 2048;
+          bulk_load(sSf + h * 2048, src, 2048, &full[s]);
         }
       }
     }
