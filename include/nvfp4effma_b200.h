@@ -41,6 +41,12 @@ int nvfp4a_b200_set_tile_n(int bn);
  * counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_pair(int mode);
 
+/* Orientation of the W4A4 GEMM on the tensor cores: 1 = B of the call (tokens) on the MMA's M side whenever D is a 16-bit
+ * matrix that TMA can store (16-byte aligned base and column pitch, m a multiple of 8), so that a thread holds consecutive
+ * elements of D; -1 (default) = the same unless the other orientation needs fewer rounds of tiles; 0 = always A on the M side.  Results lie within the same bound either way.  Tuning / test aid, no
+ * counterpart in the reference.  Returns 0, or -1 for another value. */
+int nvfp4a_b200_set_swap(int mode);
+
 /* The kernel the calling thread's last GEMM / GEMV call launched: 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core GEMV, 4 W4A4
  * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8
  * activations; 0 before any call.  Test aid, no counterpart in the reference. */

@@ -74,6 +74,7 @@ _PROTOS = {
     "nvfp4a_b200_kernel_status": (_i, [C.POINTER(C.c_uint), _i]),
     "nvfp4a_b200_set_tile_n": (_i, [_i]),
     "nvfp4a_b200_set_pair": (_i, [_i]),
+    "nvfp4a_b200_set_swap": (_i, [_i]),
     "nvfp4a_b200_set_gemv_splits": (_i, [_i]),
     "nvfp4a_b200_last_route": (_i, []),
     "nvfp4a_b200_gemv_tc_tp": (_i, [_i, _i, _i, _f, _T, _T, _i, _T, _i, _T, _E, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _s]),

@@ -40,6 +40,7 @@ struct W4A4Args {
   int ktiles;                  // image: 256-k tiles per row tile
   Epilogue e;
   unsigned *status;
+  int transposed;              // the operands were swapped: TMEM lanes are tokens (B of the call), columns are A's rows
   int d_tma;                   // D is stored by TMA from a shared-memory staging tile (needs 16-byte aligned D and column stride)
 };
 
@@ -94,6 +95,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gm = g.m, gn = g.n, gk = g.k, ktiles = g.ktiles;
   const bool a_image = g.a_image, b_image = g.b_image, sa_gather = g.sa_gather, sb_gather = g.sb_gather, d_tma = g.d_tma;
+  const bool transposed = g.transposed;
   const uint8_t *const sa_base = g.sa, *const sb_base = g.sb;
   const int sa_ld = g.sa_ld, sb_ld = g.sb_ld;
   // tiles_m counts row tiles of 128 (256 for a pair, whose CTA `rank` takes the 128-row tile 2 * (t % tiles_m) + rank)
@@ -300,8 +302,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int tm = PAIR ? 2 * (t % tiles_m) + rank : t % tiles_m, tn = t / tiles_m, acc = tile_i % ACC;
       const int i = tm * 128 + quad * 32 + lane;
       const bool row_ok = i < gm;
-      const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
-      const float bias = (row_ok && biasptr) ? load_dense(bias_dtype, biasptr, i) : 0.f;
+      const float rowp = (row_ok && !transposed) ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
+      const float bias = (row_ok && biasptr && !transposed) ? load_dense(bias_dtype, biasptr, i) : 0.f;
       const float s_lane = __fmul_rn(__fmul_rn(rowp, colp0), gf);
       // the four warps of a group decide together whether to go on: none may be left alone at a named barrier
       bool okw;
@@ -311,6 +313,66 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (*abort_flag) goto done;
       tc_fence_after();
       const int nchunks = min(BN / 32, (gn - tn * BN + 31) / 32);
+      // Swapped operands: this lane is token jt and the accumulator's columns are 32 consecutive rows of D, which lie side by
+      // side in memory -- scaled, rounded, packed two to a word and staged with four 16-byte stores per lane (swizzled as the
+      // TMA unit expects, so they meet no bank conflict), against 32 two-byte stores the other way round.  Every warp stages
+      // and stores its own 32 tokens: no barrier between warps, eight independent store pipelines.
+      const int jt = i;   // (the lane's index on the M side is a token here)
+      const float tokp = (transposed && row_ok && gb) ? gb[(size_t)jt * gb_stride] : 1.f;
+      const float ga0 = (ga && !ga_stride) ? ga[0] : 1.f;
+      const bool fast_t = beta == 0.f && ga_stride == 0 && !biasptr;
+      const float s_tok = __fmul_rn(__fmul_rn(__fmul_rn(alpha, ga0), tokp), gf);
+      auto drain_t = [&](uint32_t (&r)[32], int c) {
+        const int i0 = tn * BN + c * 32;
+        const int nvalid = min(32, gn - i0);
+        if (fast_t) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(__fmul_rn(__uint_as_float(r[jj]), s_tok));
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int ii = i0 + jj;
+            const bool in = jj < nvalid;
+            const float rp = __fmul_rn(alpha, (ga && in) ? ga[(size_t)ii * ga_stride] : 1.f);
+            float v = __fmul_rn(__uint_as_float(r[jj]), __fmul_rn(__fmul_rn(rp, tokp), gf));
+            if (biasptr && in) v = __fadd_rn(v, load_dense(bias_dtype, biasptr, ii));
+            if (beta != 0.f && in && row_ok) v = __fmaf_rn(beta, load_dense(c_dtype, cptr, (size_t)jt * ldc + ii), v);
+            r[jj] = __float_as_uint(v);
+          }
+        }
+        if (amax_out && row_ok) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            if (jj < nvalid) amax = fmaxf(amax, fabsf(__uint_as_float(r[jj])));
+        }
+        if (d_dtype == NVFP4A_BF16) {
+          round32_to_bf16(r);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) r[jj] = (uint32_t)__half_as_ushort(__float2half_rn(__uint_as_float(r[jj])));
+        }
+        // every warp on its own: 32 tokens x 16 elements (1 KiB, 32-byte rows in the TMA unit's 32-byte swizzle) per store
+        uint8_t *const mine = staging + (group * 4 + quad) * 1024, *const row = mine + lane * 32;
+        const int sw = (lane >> 2) & 1;
+#pragma unroll
+        for (int rd = 0; rd < 2; ++rd) {
+          if (lane == 0) bulk_wait_read_all();   // this warp's previous store has finished reading its staging tile
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int b = rd * 16 + q * 8;
+            *(uint4 *)(row + ((q ^ sw) << 4)) = make_uint4(r[b] | (r[b + 1] << 16), r[b + 2] | (r[b + 3] << 16), r[b + 4] | (r[b + 5] << 16),
+                                                           r[b + 6] | (r[b + 7] << 16));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_d, mine, i0 + rd * 16, tm * 128 + quad * 32);
+            bulk_commit();
+          }
+        }
+      };
+      const int cstep = 2, cfirst = group;
       // The accumulator leaves tensor memory 32 columns at a time; the load of the next 32 is in flight while these are
       // scaled, rounded and staged (two register sets alternate).
       auto drain = [&](uint32_t (&r)[32], int c) {
@@ -406,22 +468,24 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       };
       uint32_t ra[32], rb[32];
-      if (group < nchunks) tmem_ld32(acc_addr + group * 32, ra);
+      if (cfirst < nchunks) tmem_ld32(acc_addr + cfirst * 32, ra);
       else release_acc();   // no chunk of this tile for the group
-      for (int c = group; c < nchunks; c += 4) {
+      for (int c = cfirst; c < nchunks; c += 2 * cstep) {
         tmem_ld_wait();
-        if (c + 2 < nchunks) tmem_ld32(acc_addr + (c + 2) * 32, rb);
+        if (c + cstep < nchunks) tmem_ld32(acc_addr + (c + cstep) * 32, rb);
         else release_acc();
-        drain(ra, c);
-        if (c + 2 < nchunks) {
+        if (transposed) drain_t(ra, c);
+        else drain(ra, c);
+        if (c + cstep < nchunks) {
           tmem_ld_wait();
-          if (c + 4 < nchunks) tmem_ld32(acc_addr + (c + 4) * 32, ra);
+          if (c + 2 * cstep < nchunks) tmem_ld32(acc_addr + (c + 2 * cstep) * 32, ra);
           else release_acc();
-          drain(rb, c + 2);
+          if (transposed) drain_t(rb, c + cstep);
+          else drain(rb, c + cstep);
         }
       }
     }
-    if (leader) bulk_wait_all();
+    if (lane == 0) bulk_wait_all();   // (a lane that issued no store has nothing to wait for)
     if (amax_out) warp_amax_commit(amax_out, amax);
   } else if (!any_gather) {
     // ---------------- scale warps: the stage's 512-byte scale tiles, shared memory -> registers -> tensor memory ----------------
@@ -559,7 +623,7 @@ bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uin
 }
 
 bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t stride,
-                     uint32_t box_inner, uint32_t box_outer) {
+                     uint32_t box_inner, uint32_t box_outer, int swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {inner, outer};
@@ -567,7 +631,7 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
-            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -629,50 +693,70 @@ void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
 static int g_w4a4_pair = -1;
 void set_w4a4_pair(int mode) { g_w4a4_pair = mode; }
 
+static int g_w4a4_swap = -1;  // 1: tokens on the MMA's M side whenever D can be stored that way; -1: unless that costs a round of tiles; 0: never
+void set_w4a4_swap(int mode) { g_w4a4_swap = mode; }
+
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   W4A4Args a;
   memset(&a, 0, sizeof a);
-  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.k = g.k;
   a.e = g.e;
   a.status = kernel_status_device_ptr();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
-  const int bn = g_w4a4_bn ? g_w4a4_bn : (g.n > 128 ? 256 : 128);
+  // D through TMA when its base and column stride are 16-byte aligned; otherwise plain stores from registers
+  const int esz = dense_bytes(g.e.d_dtype);
+  const bool d_tma_ok = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0;
+  // Swapped roles: B of the call (tokens) feeds the MMA's M side (tensor memory lanes) and A (output rows) its N side, so that a
+  // lane's accumulator columns are consecutive elements of D in memory.  Needs a 16-bit D that TMA can store.
+  // Automatic: swapped unless the other orientation needs fewer rounds of tiles over the SMs.
+  auto rounds = [&](int lanes_rows, int col_rows) {
+    const int bn_ = g_w4a4_bn ? g_w4a4_bn : (col_rows > 128 ? 256 : 128);
+    const long long tiles = (long long)((lanes_rows + 127) / 128) * ((col_rows + bn_ - 1) / bn_);
+    return (tiles + device_sms() - 1) / device_sms() * bn_;   // rounds weighted by the tile's width
+  };
+  const bool swap = g_w4a4_swap != 0 && esz == 2 && d_tma_ok && (g_w4a4_swap == 1 || rounds(g.n, g.m) <= rounds(g.m, g.n));
+  a.transposed = swap;
+  const Fp4Operand &X = swap ? g.B.q : g.A, &Y = swap ? g.A : g.B.q;   // X: rows on lanes (128 per tile); Y: rows on columns (BN per tile)
+  const int xm = swap ? g.n : g.m, yn = swap ? g.m : g.n;
+  a.m = xm; a.n = yn;
+  const int bn = g_w4a4_bn ? g_w4a4_bn : (yn > 128 ? 256 : 128);
   CUtensorMap ta, tb, tsa, tsb;
   memset(&tsa, 0, sizeof tsa);
   memset(&tsb, 0, sizeof tsb);
-  const Fp4Operand &A = g.A, &B = g.B.q;
-  a.a_image = A.image; a.b_image = B.image;
+  a.a_image = X.image; a.b_image = Y.image;
   auto tiled_ok = [](const Fp4Operand &o) { return o.sld < 0 && ((uintptr_t)o.sc & 15) == 0; };
   // the CTA-pair kernel: 256 x 256 tiles, scales in aligned tiles (or images) on both sides, more than one row tile
-  const bool pair = bn == 256 && g_w4a4_pair == 1 && g.m > 128 && (A.image || tiled_ok(A)) && (B.image || tiled_ok(B));
-  if (A.image) {
-    const uint64_t tiles = (uint64_t)((g.m + 127) / 128) * a.ktiles;
-    if (!make_tmap_bytes(&ta, A.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
-    if (!make_tmap_scales(&tsa, (const uint8_t *)A.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
-    a.sa = A.data; a.sa_gather = 0;
+  const bool pair = bn == 256 && g_w4a4_pair == 1 && xm > 128 && (X.image || tiled_ok(X)) && (Y.image || tiled_ok(Y));
+  if (X.image) {
+    const uint64_t tiles = (uint64_t)((xm + 127) / 128) * a.ktiles;
+    if (!make_tmap_bytes(&ta, X.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    if (!make_tmap_scales(&tsa, (const uint8_t *)X.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    a.sa = X.data; a.sa_gather = 0;
   } else {
-    if (!make_tmap_bytes(&ta, A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)A.ld / 2, 128, 1, (uint64_t)A.ld / 2 * g.m)) return cudaErrorInvalidValue;
-    a.sa = A.sc; a.sa_ld = A.sld; a.sa_gather = tiled_ok(A) ? 0 : 1;
-    if (!a.sa_gather && !make_tmap_scales(&tsa, A.sc, (uint64_t)((-A.sld) >> 2) * 512, (uint64_t)(g.m + 127) / 128, (uint64_t)((-A.sld) >> 2) * 512))
+    if (!make_tmap_bytes(&ta, X.data, (uint64_t)g.k / 2, (uint64_t)xm, (uint64_t)X.ld / 2, 128, 1, (uint64_t)X.ld / 2 * xm)) return cudaErrorInvalidValue;
+    a.sa = X.sc; a.sa_ld = X.sld; a.sa_gather = tiled_ok(X) ? 0 : 1;
+    if (!a.sa_gather && !make_tmap_scales(&tsa, X.sc, (uint64_t)((-X.sld) >> 2) * 512, (uint64_t)(xm + 127) / 128, (uint64_t)((-X.sld) >> 2) * 512))
       return cudaErrorInvalidValue;
   }
-  if (B.image) {
-    const uint64_t tiles = (uint64_t)((g.n + 127) / 128) * a.ktiles;
-    if (!make_tmap_bytes(&tb, B.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
-    if (!make_tmap_scales(&tsb, (const uint8_t *)B.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
-    a.sb = B.data; a.sb_gather = 0;
+  if (Y.image) {
+    const uint64_t tiles = (uint64_t)((yn + 127) / 128) * a.ktiles;
+    if (!make_tmap_bytes(&tb, Y.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    if (!make_tmap_scales(&tsb, (const uint8_t *)Y.data + kImgDataBytes, 2048, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    a.sb = Y.data; a.sb_gather = 0;
   } else {
-    if (!make_tmap_bytes(&tb, B.data, (uint64_t)g.k / 2, (uint64_t)g.n, (uint64_t)B.ld / 2, pair ? 128 : bn, 1, (uint64_t)B.ld / 2 * g.n)) return cudaErrorInvalidValue;
-    a.sb = B.sc; a.sb_ld = B.sld; a.sb_gather = tiled_ok(B) ? 0 : 1;
-    if (!a.sb_gather && !make_tmap_scales(&tsb, B.sc, (uint64_t)((-B.sld) >> 2) * 512, (uint64_t)(g.n + 127) / 128, (uint64_t)((-B.sld) >> 2) * 512))
+    if (!make_tmap_bytes(&tb, Y.data, (uint64_t)g.k / 2, (uint64_t)yn, (uint64_t)Y.ld / 2, pair ? 128 : bn, 1, (uint64_t)Y.ld / 2 * yn)) return cudaErrorInvalidValue;
+    a.sb = Y.sc; a.sb_ld = Y.sld; a.sb_gather = tiled_ok(Y) ? 0 : 1;
+    if (!a.sb_gather && !make_tmap_scales(&tsb, Y.sc, (uint64_t)((-Y.sld) >> 2) * 512, (uint64_t)(yn + 127) / 128, (uint64_t)((-Y.sld) >> 2) * 512))
       return cudaErrorInvalidValue;
   }
-  // D through TMA when its base and column stride are 16-byte aligned; otherwise plain stores from registers
   CUtensorMap td;
   memset(&td, 0, sizeof td);
-  const int esz = dense_bytes(g.e.d_dtype);
-  a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)g.m * esz) % 16 == 0 &&
-            make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 16 : 8);
+  if (swap) {   // boxes of 16 consecutive elements of D (32 bytes) for 32 tokens, staged in the 32-byte swizzle
+    if (!make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 16, 32, 32)) return cudaErrorInvalidValue;
+    a.d_tma = 1;
+  } else {
+    a.d_tma = d_tma_ok && make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 16 : 8);
+  }
   if (pair) return launch_cfg<256, 1, 5, true>(ta, tb, tsa, tsb, td, a, s);
   if (bn == 256) return launch_cfg<256, 1, 4, false>(ta, tb, tsa, tsb, td, a, s);
   return launch_cfg<128, 2, 6, false>(ta, tb, tsa, tsb, td, a, s);
@@ -694,6 +778,12 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
 extern "C" int nvfp4a_b200_set_pair(int mode) {
   if (mode < -1 || mode > 1) return -1;
   nvb::set_w4a4_pair(mode);
+  return 0;
+}
+
+extern "C" int nvfp4a_b200_set_swap(int mode) {
+  if (mode < -1 || mode > 1) return -1;
+  nvb::set_w4a4_swap(mode);
   return 0;
 }
 

@@ -261,7 +261,7 @@ bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uin
 // dense matrix [outer][inner] of 2- or 4-byte elements, `stride` bytes between outer indices, box = box_inner x box_outer,
 // no swizzle (the epilogue's store of D)
 bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t stride,
-                     uint32_t box_inner, uint32_t box_outer);
+                     uint32_t box_inner, uint32_t box_outer, int swizzle = 0);
 // kernel status word: 0 = healthy; kernels that gave up a wait write a non-zero code (see nvfp4a_b200_kernel_status)
 unsigned int *kernel_status_device_ptr();
 

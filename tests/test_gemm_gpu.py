@@ -288,6 +288,33 @@ def test_w4a4_cta_pair_kernel_matches_the_single_cta_kernel():
         L.lib.nvfp4a_b200_set_pair(-1)
 
 
+def test_w4a4_swapped_orientation_matches_the_bound_and_the_other_orientation():
+    """D that TMA can store (16-bit, 16-byte aligned pitch) runs with the tokens on the MMA's M side; the same cases with the
+    orientation pinned the other way must agree within the bound too: bias, beta * C, per-row globals on either operand, FP16
+    and BF16, tails in m / n / k, padded pitch."""
+    sizes = [(128, 128, 256), (136, 40, 64), (200, 300, 192), (1104, 1300, 512), (264, 129, 320), (2304, 520, 1344)]
+    try:
+        for i, (m, n, k) in enumerate(sizes):
+            dt = L.BF16 if i % 2 == 0 else L.FP16
+            c = Case(m, n, k, L.NVFP4, dt, -1 if i % 3 == 0 else dt, L.BF16 if i % 2 else -1, 1.25 if i % 2 else 1.0,
+                     0.0 if i % 3 == 0 else 0.5, fa=(SW if i % 2 else 0) | (PR if i in (2, 5) else 0), fb=(SW if i < 4 else 0) | (PR if i in (3, 5) else 0))
+            h = build_case(c, 950 + i)
+            h["ldd"] = m + (8 if i % 2 else 0)
+            fill = np.frombuffer(b"\xA5" * (h["ldd"] * n * 2), dtype=np.uint16).copy()
+            h["Dinit"] = fill
+            exp = oracle_case(c, h, want_ref=True)
+            res = []
+            for mode in (1, 0):
+                assert L.lib.nvfp4a_b200_set_swap(mode) == 0
+                got, amax = run_gemm(c, h)
+                assert L.lib.nvfp4a_b200_last_route() == 4 and kernel_status() == 0
+                check_bound(c, h, got, amax, exp)
+                res.append(got)
+            print(f"{c}: equal bits between orientations: {np.mean(res[0] == res[1]):.6f}")
+    finally:
+        L.lib.nvfp4a_b200_set_swap(-1)
+
+
 def make_image(kind, dfp4, rows, k, ld):
     nbytes = L.lib.nvfp4a_tc_image_bytes(kind, L.NVFP4, rows, k)
     img = torch.full((nbytes + 16,), 0xEE, dtype=torch.uint8, device="cuda")
