@@ -233,6 +233,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ---------------- MMA issuer ----------------
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = idesc_mxf4nvf4(PAIR ? 256 : 128, BN);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t da0 = smem_desc_sw128(smem0);
+      const int nfull = gk / 256;   // iterations with all four 64-value groups
       uint32_t it = 0, tile_i = 0;
       for (int t = tile_first; t < ntiles; t += tile_step, ++tile_i) {
         const int acc = tile_i % ACC;
@@ -250,13 +253,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           else okw = any_gather ? wait(&full[s], (it / STAGES) & 1, kStatusWaitFull) : wait(&sf_ready[s], (it / STAGES) & 1, kStatusWaitSf);
           if (!okw) goto done;
           tc_fence_after();
-          const uint32_t st = smem_u32(smem + (size_t)s * Cfg::kStageBytes);
-          const uint32_t sA = st, sB = st + Cfg::kABytes, sSfa = sB + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;
+          // descriptors of a stage = those of stage 0 plus the stage's offset in the address field's 16-byte units
+          const uint64_t da = da0 + (uint32_t)s * (uint32_t)(Cfg::kStageBytes >> 4), db = da + (Cfg::kABytes >> 4);
           const uint32_t sf_tmem = tmem_base + Cfg::kAccCols + b * Cfg::kSfCols;
           const uint32_t sfa_tmem = sf_tmem, sfb_tmem = sf_tmem + 16;
-          const int ng = min(4, (gk - ks * 256) / 64);
-          const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sB);
+          const uint32_t sSfa = smem0 + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes, sSfb = sSfa + Cfg::kSfaBytes;   // gathered scales only
+          const int ng = ks < nfull ? 4 : (gk - ks * 256) / 64;
           // per 64 values of k: (the scale tiles of that group, then) its MMA, 32 bytes further along each 128-byte row
+          if (!any_gather && ks < nfull) {   // the common iteration, straight-line: nothing but the four MMAs on this thread's path
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (PAIR) mma_mxf4nvf4_pair(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, j ? 1u : (uint32_t)(ks != 0));
+              else mma_mxf4nvf4(d_tmem, da + 2 * j, db + 2 * j, idesc, sfa_tmem + 4 * j, sfb_tmem + (BN / 32) * j, j ? 1u : (uint32_t)(ks != 0));
+            }
+          } else
           for (int j = 0; j < ng; ++j) {
             if (any_gather) {
               tmem_cp_32x128b_warpx4(sfa_tmem + 4 * j, smem_desc_sf(sSfa + j * 512));
