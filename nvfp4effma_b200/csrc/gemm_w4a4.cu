@@ -478,18 +478,30 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       };
       uint32_t ra[32], rb[32];
-      if (cfirst < nchunks) tmem_ld32(acc_addr + cfirst * 32, ra);
-      else release_acc();   // no chunk of this tile for the group
+      // The accumulator goes back to the MMA thread as soon as the warp's last load has landed, before the chunks still in
+      // registers are drained: a drain waits on the TMA unit between its stores.
+      bool released = false;
+      auto last_load = [&]() { tmem_ld_wait(); release_acc(); released = true; };
+      if (cfirst < nchunks) {
+        tmem_ld32(acc_addr + cfirst * 32, ra);
+        if (cfirst + cstep >= nchunks) last_load();
+      } else {
+        release_acc();   // no chunk of this tile for the group
+      }
       for (int c = cfirst; c < nchunks; c += 2 * cstep) {
-        tmem_ld_wait();
-        if (c + cstep < nchunks) tmem_ld32(acc_addr + (c + cstep) * 32, rb);
-        else release_acc();
+        if (!released) tmem_ld_wait();
+        if (c + cstep < nchunks) {
+          tmem_ld32(acc_addr + (c + cstep) * 32, rb);
+          if (c + 2 * cstep >= nchunks) last_load();
+        }
         if (transposed) drain_t(ra, c);
         else drain(ra, c);
         if (c + cstep < nchunks) {
-          tmem_ld_wait();
-          if (c + 2 * cstep < nchunks) tmem_ld32(acc_addr + (c + 2 * cstep) * 32, ra);
-          else release_acc();
+          if (!released) tmem_ld_wait();
+          if (c + 2 * cstep < nchunks) {
+            tmem_ld32(acc_addr + (c + 2 * cstep) * 32, ra);
+            if (c + 3 * cstep >= nchunks) last_load();
+          }
           if (transposed) drain_t(rb, c + cstep);
           else drain(rb, c + cstep);
         }
