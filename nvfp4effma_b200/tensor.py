@@ -1,68 +1,124 @@
-"""Tensor containers of the Python surface: ``NVFP4Tensor``, ``Int8Tensor``, ``TCWeight`` and the ``NVFP4Linear`` module.
+"""Containers of the Python surface: ``NVFP4Tensor``, ``Int8Tensor``, ``TCWeight`` and the ``NVFP4Linear`` module.
 
-They mirror the classes of the reference's Python package (binds/python/nvfp4effma/tensor.py:14-323 there): same
-constructor arguments, attribute names, checkpoint buffer names (``weight`` / ``weight_scale`` / ``weight_scale_2``) and
-errors, so code written against the reference keeps working.  Inference only; no autograd.
+The names, constructor arguments, attributes and checkpoint buffer names (``weight`` / ``weight_scale`` /
+``weight_scale_2``) are those of the reference's Python package (binds/python/nvfp4effma/tensor.py there), so code written
+against it keeps working; the implementation is this library's own.  All three containers are validated by one set of
+helpers (``_expect_dtype``, ``_same_device``, ``_block_count``) and hand their buffers to the operator layer as an
+``Fp4Operand`` tuple.  Inference only; no autograd.
 """
 import math
-from typing import Optional, Tuple
+from typing import NamedTuple, Optional, Tuple
 
 import torch
 
+from . import _abi as A
 from . import _lib as L
-from . import _ops
+from ._ops import ops
+
+_SCALE_BOUNDS = (0, 256, 448, 114688)
+_ACTS = ("exact", "int8", "nvfp4")
+_FLOATS = (torch.bfloat16, torch.float16, torch.float32)
+
+
+class Fp4Operand(NamedTuple):
+    """What the operators take for one NVFP4 matrix: 2-D nibbles, 2-D scale codes (uint8), the global, flag bits, bound, columns."""
+    data: torch.Tensor
+    scales: torch.Tensor
+    glob: Optional[torch.Tensor]
+    flags: int
+    scale_max: int
+    cols: int
+
+    @property
+    def rows(self) -> int:
+        return self.data.shape[0]
+
+
+# ---- validation shared by the containers ------------------------------------------------------------------------------------------
+def _expect_dtype(what: str, t: torch.Tensor, *allowed: torch.dtype):
+    if t.dtype not in allowed:
+        names = " or ".join(str(a).replace("torch.", "") for a in allowed)
+        raise TypeError(f"{what} holds {t.dtype}; it has to be {names}")
+
+
+def _same_device(*named: Tuple[str, Optional[torch.Tensor]]):
+    present = [(n, t) for n, t in named if t is not None]
+    first_name, first = present[0]
+    for name, t in present[1:]:
+        if t.device != first.device:
+            raise ValueError(f"{name} is on {t.device} but {first_name} is on {first.device}")
+
+
+def _block_count(what: str, values: int) -> int:
+    if values % 16:
+        raise ValueError(f"{what}: {values} values do not divide into blocks of 16")
+    return values // 16
+
+
+def _leading_rows(t: torch.Tensor) -> int:
+    return math.prod(t.shape[:-1])
 
 
 class NVFP4Tensor:
-    """An NVFP4 tensor of logical shape ``[..., cols]``: ``value = e2m1 * block_scale * global``."""
+    """An NVFP4 tensor of logical shape ``[..., cols]``: element = e2m1 nibble x block scale x global.
+
+    ``data``: uint8, two values per byte (the even column in the low nibble).  ``scales``: one code per 16 values of a row --
+    ``float8_e4m3fn`` (uint8 is accepted and re-viewed) or, with ``ue5m3``, uint8 -- either laid out like ``data``
+    (``[..., >= cols / 16]``, or any 2-D buffer with at least as many rows and columns) or, with ``swizzled``, the padded
+    128 x 4-tile buffer of the whole matrix.  The global is a float32 decode factor (``global_scale``) or an amax (``amax``,
+    decode factor amax / (6 x scale_max)), one value or one per row.
+    """
 
     def __init__(self, data: torch.Tensor, scales: torch.Tensor, global_scale: Optional[torch.Tensor] = None, *,
                  amax: Optional[torch.Tensor] = None, scale_max: int = 0, swizzled: bool = False, ue5m3: bool = False,
                  cols: Optional[int] = None, columnwise: Optional["NVFP4Tensor"] = None, block: Optional[Tuple[int, int]] = None):
-        if data.dtype != torch.uint8:
-            raise TypeError(f"data must be torch.uint8 (two E2M1 values per byte), got {data.dtype}")
+        _expect_dtype("NVFP4 data", data, torch.uint8)
         if ue5m3:
-            if scales.dtype != torch.uint8:
-                raise TypeError(f"UE5M3 scales are stored as torch.uint8, got {scales.dtype}")
-        elif scales.dtype == torch.uint8:
-            scales = scales.view(torch.float8_e4m3fn)
-        elif scales.dtype != torch.float8_e4m3fn:
-            raise TypeError(f"scales must be torch.float8_e4m3fn (or uint8), got {scales.dtype}")
-        if global_scale is not None and amax is not None:
-            raise ValueError("give either global_scale (a decode factor) or amax, not both")
-        g = global_scale if global_scale is not None else amax
-        if g is not None and (g.dtype != torch.float32 or g.numel() < 1):
-            raise TypeError("global_scale / amax must be a float32 tensor")
-        if data.dim() < 1:
-            raise ValueError("data must have at least one dimension")
-        self.cols = int(cols) if cols is not None else 2 * data.shape[-1]
-        if self.cols > 2 * data.shape[-1] or self.cols % 16:
-            raise ValueError(f"cols = {self.cols}: a multiple of 16 with at most 2 * data.shape[-1] = {2 * data.shape[-1]} values")
-        rows = math.prod(data.shape[:-1])
-        if swizzled:
-            want = _ops.swizzled_scale_shape(rows, self.cols)
-            if tuple(scales.shape) != want:
-                raise ValueError(f"swizzled scales of a [{rows}, {self.cols}] matrix are {list(want)}, got {tuple(scales.shape)}")
-        elif scales.dim() == data.dim() and scales.shape[:-1] == data.shape[:-1]:
-            if scales.shape[-1] < self.cols // 16:
-                raise ValueError(f"scales {tuple(scales.shape)} have fewer than cols / 16 = {self.cols // 16} columns")
-        elif scales.dim() != 2 or scales.shape[0] < rows or scales.shape[1] < self.cols // 16:
-            raise ValueError(f"data {tuple(data.shape)} and scales {tuple(scales.shape)} do not describe the same matrix")
-        if g is not None and g.numel() not in (1, rows):
-            raise ValueError(f"the global has {g.numel()} elements: 1 (per tensor) or {rows} (one per row)")
-        if not (data.device == scales.device and (g is None or g.device == data.device)):
-            raise ValueError("data, scales and the global must be on one device")
-        if scale_max not in (0, 256, 448, 114688):
-            raise ValueError(f"scale_max must be 0, 256, 448 or 114688, got {scale_max}")
+            _expect_dtype("UE5M3 block scales", scales, torch.uint8)
+        else:
+            _expect_dtype("E4M3 block scales", scales, torch.float8_e4m3fn, torch.uint8)
+            if scales.dtype == torch.uint8:
+                scales = scales.view(torch.float8_e4m3fn)
+        if amax is not None and global_scale is not None:
+            raise ValueError("a tensor has ONE global: pass the decode factor as global_scale or the amax as amax")
+        glob = amax if amax is not None else global_scale
+        if glob is not None:
+            _expect_dtype("the global", glob, torch.float32)
+        if data.dim() == 0:
+            raise ValueError("NVFP4 data needs a last dimension to hold the packed values")
+        held = 2 * data.shape[-1]
+        self.cols = held if cols is None else int(cols)
+        nblocks = _block_count("cols", self.cols)
+        if self.cols > held:
+            raise ValueError(f"cols = {self.cols} exceeds the {held} values the last dimension of data holds")
+        rows = _leading_rows(data)
+        self._check_scale_shape(data, scales, rows, nblocks, swizzled)
+        if glob is not None and glob.numel() != 1 and glob.numel() != rows:
+            raise ValueError(f"{glob.numel()} global values for {rows} rows: there is one per tensor or one per row")
+        _same_device(("data", data), ("scales", scales), ("the global", glob))
+        if scale_max not in _SCALE_BOUNDS:
+            raise ValueError(f"scale_max = {scale_max} is not one of {_SCALE_BOUNDS}")
         self.data, self.scales = data, scales
-        self.global_scale = g.reshape(-1) if g is not None else None
+        self.global_scale = None if glob is None else glob.reshape(-1)
         self.global_is_amax = amax is not None
-        self.scale_max, self.swizzled, self.ue5m3 = scale_max, swizzled, ue5m3
+        self.scale_max, self.swizzled, self.ue5m3 = scale_max, bool(swizzled), bool(ue5m3)
         self.columnwise, self.block = columnwise, block
 
+    def _check_scale_shape(self, data, scales, rows, nblocks, swizzled):
+        got = tuple(scales.shape)
+        if swizzled:
+            if got != A.padded_scale_shape(rows, self.cols):
+                raise ValueError(f"swizzled scales of {rows} x {self.cols} values fill a {A.padded_scale_shape(rows, self.cols)} buffer, got {got}")
+            return
+        alongside = scales.dim() == data.dim() and got[:-1] == tuple(data.shape[:-1])
+        plain_2d = scales.dim() == 2 and got[0] >= rows
+        if not (alongside or plain_2d) or got[-1] < nblocks:
+            raise ValueError(f"scales of shape {got} cannot hold {rows} x {nblocks} block scales for data of shape {tuple(data.shape)}")
+
+    # ---- what the tensor is ------------------------------------------------------------------------------------------------------
     @property
     def shape(self) -> Tuple[int, ...]:
-        return (*self.data.shape[:-1], self.cols)
+        return tuple(self.data.shape[:-1]) + (self.cols,)
 
     def dim(self) -> int:
         return self.data.dim()
@@ -73,7 +129,7 @@ class NVFP4Tensor:
 
     @property
     def rows(self) -> int:
-        return math.prod(self.data.shape[:-1])
+        return _leading_rows(self.data)
 
     @property
     def per_row(self) -> bool:
@@ -85,15 +141,20 @@ class NVFP4Tensor:
 
     @property
     def flags(self) -> int:
-        return ((L.SCALES_SWIZZLED if self.swizzled else 0) | (L.SCALES_UE5M3 if self.ue5m3 else 0) |
-                (L.GLOBAL_AMAX if self.global_is_amax else 0) | (L.GLOBAL_PER_ROW if self.per_row else 0))
+        bits = ((self.swizzled, L.SCALES_SWIZZLED), (self.ue5m3, L.SCALES_UE5M3), (self.global_is_amax, L.GLOBAL_AMAX), (self.per_row, L.GLOBAL_PER_ROW))
+        return sum(bit for on, bit in bits if on)
 
-    def _flat(self):
-        """(data 2-D, scales 2-D, global, flags, scale_max, cols) as ``_ops`` takes them."""
-        d = self.data.reshape(-1, self.data.shape[-1]) if self.data.dim() != 2 else self.data
-        s = self.scales if self.scales.dim() == 2 else self.scales.reshape(-1, self.scales.shape[-1])
-        return d, s, self.global_scale, self.flags, self.scale_max, self.cols
+    def _operand(self) -> Fp4Operand:
+        data = self.data if self.data.dim() == 2 else self.data.reshape(self.rows, self.data.shape[-1])
+        scales = self.scales if self.scales.dim() == 2 else self.scales.reshape(-1, self.scales.shape[-1])
+        return Fp4Operand(data, scales.view(torch.uint8), self.global_scale, self.flags, self.scale_max, self.cols)
 
+    def _rebuilt(self, data, scale_codes, *, swizzled, cols, block) -> "NVFP4Tensor":
+        """A tensor with this one's global, bound and scale type over other buffers."""
+        kind = {"amax": self.global_scale} if self.global_is_amax else {"global_scale": self.global_scale}
+        return NVFP4Tensor(data, scale_codes, scale_max=self.scale_max, swizzled=swizzled, ue5m3=self.ue5m3, cols=cols, block=block, **kind)
+
+    # ---- construction ------------------------------------------------------------------------------------------------------------
     @classmethod
     def from_float(cls, x: torch.Tensor, global_scale: Optional[torch.Tensor] = None, **recipe) -> "NVFP4Tensor":
         from .api import quantize
@@ -101,97 +162,96 @@ class NVFP4Tensor:
 
     @classmethod
     def from_te(cls, t) -> "NVFP4Tensor":
-        """Adopt, without a copy, a Transformer Engine NVFP4 tensor through TE's attribute names (``_rowwise_data``,
-        ``_rowwise_scale_inv``, ``_amax_rowwise`` and the ``_columnwise_*`` ones, ``_with_gemm_swizzled_scales``,
-        ``_nvfp4_e4m3_max``, ``_scale_dtype``).  A tensor holding only the columnwise half becomes the tensor of the transpose."""
+        """Wraps a Transformer Engine NVFP4 tensor without copying, reading TE's private attributes: ``_rowwise_data`` /
+        ``_rowwise_scale_inv`` / ``_amax_rowwise``, their ``_columnwise_*`` twins, ``_with_gemm_swizzled_scales``,
+        ``_nvfp4_e4m3_max`` and ``_scale_dtype``.  With only the column-wise half present the result is the tensor of the transpose."""
         swizzled = bool(getattr(t, "_with_gemm_swizzled_scales", False))
         ue5m3 = "ue5m3" in str(getattr(t, "_scale_dtype", "")).lower()
         bound = int(getattr(t, "_nvfp4_e4m3_max", 0) or 0)
-        halves = []
-        for prefix, amax_name in (("_rowwise", "_amax_rowwise"), ("_columnwise", "_amax_columnwise")):
-            data = getattr(t, prefix + "_data", None)
-            if data is None:
-                halves.append(None)
-                continue
-            sc = getattr(t, prefix + "_scale_inv")
-            sc = sc.reshape(sc.shape[0], -1) if swizzled else sc
-            a = getattr(t, amax_name, None)
-            halves.append(cls(data, sc.view(torch.uint8) if ue5m3 else sc, amax=a.float() if a is not None else None, scale_max=bound,
-                              swizzled=swizzled, ue5m3=ue5m3))
-        row, col = halves
-        if row is None and col is None:
-            raise ValueError("the tensor holds neither rowwise nor columnwise NVFP4 data")
-        if row is None:
-            return col
-        row.columnwise = col
-        return row
 
+        def half(which):
+            data = getattr(t, f"_{which}_data", None)
+            if data is None:
+                return None
+            codes = getattr(t, f"_{which}_scale_inv")
+            if swizzled:
+                codes = codes.reshape(codes.shape[0], -1)
+            stat = getattr(t, f"_amax_{which}", None)
+            return cls(data, codes.view(torch.uint8) if ue5m3 else codes, amax=None if stat is None else stat.float(), scale_max=bound,
+                       swizzled=swizzled, ue5m3=ue5m3)
+
+        rowwise, colwise = half("rowwise"), half("columnwise")
+        if rowwise is None:
+            if colwise is None:
+                raise ValueError("this Transformer Engine tensor carries no NVFP4 data in either direction")
+            return colwise
+        rowwise.columnwise = colwise
+        return rowwise
+
+    # ---- operations --------------------------------------------------------------------------------------------------------------
     def dequantize(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         from .api import dequantize
         return dequantize(self, dtype)
 
-    def _like(self, data, scales, swizzled, cols, block):
-        g = self.global_scale
-        return NVFP4Tensor(data, scales, None if self.global_is_amax else g, amax=g if self.global_is_amax else None,
-                           scale_max=self.scale_max, swizzled=swizzled, ue5m3=self.ue5m3, cols=cols, block=block)
-
     def with_scale_layout(self, swizzled: bool) -> "NVFP4Tensor":
-        """The same tensor with its block scales in the linear or the swizzled GEMM layout (both halves, if present)."""
-        out = self
-        if swizzled != self.swizzled:
-            d, s, _, _, _, cols = self._flat()
-            sc = _ops.swizzle_scales(s.view(torch.uint8), d.shape[0], cols, swizzled)
-            out = self._like(self.data, sc if self.ue5m3 else sc.view(torch.float8_e4m3fn), swizzled, cols, self.block)
-        if self.columnwise is not None and self.columnwise.swizzled != swizzled:
-            if out is self:
-                out = self._like(self.data, self.scales, self.swizzled, self.cols, self.block)
-            out.columnwise = self.columnwise.with_scale_layout(swizzled)
-        return out
+        """This tensor with its block scales in the linear (False) or the GEMM-swizzled (True) layout; a column-wise half
+        follows.  Returns ``self`` when nothing has to change."""
+        swizzled = bool(swizzled)
+        mine_ok = self.swizzled == swizzled
+        col_ok = self.columnwise is None or self.columnwise.swizzled == swizzled
+        if mine_ok and col_ok:
+            return self
+        if mine_ok:
+            result = self._rebuilt(self.data, self.scales, swizzled=swizzled, cols=self.cols, block=self.block)
+        else:
+            op = self._operand()
+            codes = ops.swizzle_scales(op.scales, op.rows, op.cols, swizzled)
+            result = self._rebuilt(self.data, codes, swizzled=swizzled, cols=self.cols, block=self.block)
+        if self.columnwise is not None:
+            result.columnwise = self.columnwise.with_scale_layout(swizzled)
+        return result
 
     def transpose_2d(self) -> "NVFP4Tensor":
-        """Transpose of a 16 x 16-tile tensor: exactly the columnwise quantization of the original."""
+        """The transpose of a tensor quantized in 16 x 16 tiles (a tile's scale serves both directions), bit-identical to
+        the column-wise quantization of the original."""
         if self.block is not None and tuple(self.block) != (16, 16):
-            raise ValueError("transpose_2d needs a tensor quantized with 16 x 16 tiles")
+            raise ValueError(f"only 16 x 16-tile tensors transpose exactly; this one has {self.block[0]} x {self.block[1]} blocks")
         if self.per_row:
-            raise ValueError("per-row globals do not transpose")
-        d, s, _, flags, smax, cols = self._flat()
-        dt, st = _ops.transpose(d, s.view(torch.uint8), flags, smax, cols)
-        return self._like(dt, st if self.ue5m3 else st.view(torch.float8_e4m3fn), self.swizzled, d.shape[0], (16, 16))
+            raise ValueError("a tensor with one global per row has no transpose in this format")
+        op = self._operand()
+        data_t, codes_t = ops.transpose(op.data, op.scales, op.flags, op.scale_max, op.cols)
+        return self._rebuilt(data_t, codes_t, swizzled=self.swizzled, cols=op.rows, block=(16, 16))
 
     def __repr__(self):
-        parts = [f"shape={self.shape}", f"device={self.device}"]
+        bits = [f"shape={self.shape}", f"device={self.device}"]
         if self.global_scale is not None:
-            kind = "amax" if self.global_is_amax else "global_scale"
-            parts.append(f"{kind}={'per row' if self.per_row else f'{float(self.global_scale):.6g}'}")
-        for flag, text in ((self.swizzled, "swizzled scales"), (self.ue5m3, "UE5M3 scales")):
-            if flag:
-                parts.append(text)
+            name = "amax" if self.global_is_amax else "global_scale"
+            bits.append(f"{name}=<{self.global_scale.numel()} per-row values>" if self.per_row else f"{name}={self.global_scale.item():.6g}")
+        bits += [label for on, label in ((self.swizzled, "scales=swizzled"), (self.ue5m3, "scales=ue5m3")) if on]
         if self.scale_max:
-            parts.append(f"scale_max={self.scale_max}")
+            bits.append(f"scale_max={self.scale_max}")
         if self.block is not None:
-            parts.append(f"block={self.block[0]}x{self.block[1]}")
+            bits.append("block=%dx%d" % tuple(self.block))
         if self.columnwise is not None:
-            parts.append("+ columnwise")
-        return f"NVFP4Tensor({', '.join(parts)})"
+            bits.append("columnwise=yes")
+        return "NVFP4Tensor(" + ", ".join(bits) + ")"
 
 
 class Int8Tensor:
-    """int8 activations with one FP32 scale per 16 values of the last dimension (W4A8): ``value = data * scale``."""
+    """INT8 activations for W4A8: ``data`` int8 ``[..., cols]`` and one float32 ``scales`` value per 16 values
+    (``[..., cols / 16]``); ``dtype`` is the dense type the activations came from (the default result type of ``linear``)."""
 
     def __init__(self, data: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype = torch.bfloat16):
-        if data.dtype != torch.int8:
-            raise TypeError(f"data must be torch.int8, got {data.dtype}")
-        if scales.dtype != torch.float32:
-            raise TypeError(f"scales must be torch.float32, got {scales.dtype}")
-        if dtype not in (torch.bfloat16, torch.float16, torch.float32):
-            raise TypeError(f"dtype must be bfloat16, float16 or float32, got {dtype}")
-        if data.dim() < 1 or data.shape[-1] % 16:
-            raise ValueError(f"data must be [..., cols] with cols a multiple of 16, got {tuple(data.shape)}")
-        want = (*data.shape[:-1], data.shape[-1] // 16)
-        if tuple(scales.shape) != want:
-            raise ValueError(f"scales of a {tuple(data.shape)} tensor are {want}, got {tuple(scales.shape)}")
-        if data.device != scales.device:
-            raise ValueError("data and scales must be on one device")
+        _expect_dtype("INT8 data", data, torch.int8)
+        _expect_dtype("INT8 block scales", scales, torch.float32)
+        if dtype not in _FLOATS:
+            raise TypeError(f"dtype = {dtype}: the source type is bfloat16, float16 or float32")
+        if data.dim() == 0:
+            raise ValueError("INT8 data needs a last dimension")
+        nblocks = _block_count("INT8 data", data.shape[-1])
+        if tuple(scales.shape) != tuple(data.shape[:-1]) + (nblocks,):
+            raise ValueError(f"data of shape {tuple(data.shape)} takes scales of shape {tuple(data.shape[:-1]) + (nblocks,)}, not {tuple(scales.shape)}")
+        _same_device(("data", data), ("scales", scales))
         self.data, self.scales, self.dtype = data, scales, dtype
 
     @property
@@ -211,26 +271,27 @@ class Int8Tensor:
         return quantize_int8(x)
 
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        k = self.data.shape[-1]
-        v = self.data.float().reshape(-1, k // 16, 16) * self.scales.reshape(-1, k // 16, 1)
-        return v.reshape(self.data.shape).to(dtype or self.dtype)
+        """data x scale, one float32 product per element, rounded to ``dtype`` (default: the source type)."""
+        per_value = self.scales.unsqueeze(-1).expand(*self.scales.shape, 16).reshape(self.data.shape)
+        return (self.data.to(torch.float32) * per_value).to(self.dtype if dtype is None else dtype)
 
     def __repr__(self):
-        return f"Int8Tensor(shape={self.shape}, device={self.device}, dtype={self.dtype})"
+        return f"Int8Tensor(shape={self.shape}, from={str(self.dtype).replace('torch.', '')}, device={self.device})"
 
 
 class TCWeight:
-    """An NVFP4 weight ``[N, K]`` with its image, built once here; serves the tensor-core GEMM and, up to 8 rows of ``x``, the
-    GEMV.  ``act``: ``"exact"`` (bfloat16 activations, W4A16), ``"int8"`` or ``"nvfp4"`` (W4A8 / W4A4)."""
+    """A 2-D NVFP4 weight ``[N, K]`` together with its image (``nvfp4a_tc_image``), which is built here, once.  ``linear``
+    runs the GEMV on the image up to 8 rows of ``x`` and the image GEMM beyond.  ``act`` names the activations the image
+    is meant for: "exact" = bfloat16 as they are (W4A16), "int8" (W4A8), "nvfp4" (W4A4)."""
 
     def __init__(self, weight: NVFP4Tensor, act: str = "exact"):
         if not isinstance(weight, NVFP4Tensor) or weight.dim() != 2:
-            raise TypeError("weight must be a 2-D NVFP4Tensor")
-        if act not in ("exact", "int8", "nvfp4"):
-            raise ValueError(f"act must be 'exact', 'int8' or 'nvfp4', got {act!r}")
-        d, s, _, f, _, k = weight._flat()
+            raise TypeError("TCWeight wraps a 2-D NVFP4Tensor [out_features, in_features]")
+        if act not in _ACTS:
+            raise ValueError(f"act = {act!r}; choose from {_ACTS}")
+        op = weight._operand()
         self.weight, self.act = weight, act
-        self.image = _ops.tc_image(0 if act == "exact" else 2, d, s.view(torch.uint8), f, k)
+        self.image = ops.tc_image(L.TC_A16 if act == "exact" else L.TC_A8, op.data, op.scales, op.flags, op.cols)
 
     @property
     def shape(self) -> Tuple[int, ...]:
@@ -241,55 +302,63 @@ class TCWeight:
 
 
 class NVFP4Linear(torch.nn.Module):
-    """``y = x @ W.T + bias`` with an NVFP4 weight ``[out_features, in_features]`` (in_features a multiple of 64)."""
+    """``x @ W.T + bias`` with ``W`` [out_features, in_features] held in NVFP4 (in_features a multiple of 64).  The buffers
+    carry the names of ModelOpt NVFP4 checkpoints: ``weight`` (nibbles), ``weight_scale`` (E4M3 block scales),
+    ``weight_scale_2`` (the global decode factor)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype: torch.dtype = torch.bfloat16,
                  act: str = "auto"):
         super().__init__()
         if in_features % 64:
-            raise ValueError(f"in_features ({in_features}) must be a multiple of 64")
-        self.act = act
-        self.in_features, self.out_features = in_features, out_features
-        self.register_buffer("weight", torch.zeros(out_features, in_features // 2, dtype=torch.uint8, device=device))
-        self.register_buffer("weight_scale", torch.zeros(out_features, in_features // 16, dtype=torch.float8_e4m3fn, device=device))
-        self.register_buffer("weight_scale_2", torch.ones(1, dtype=torch.float32, device=device))
-        self.bias = torch.nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device), requires_grad=False) if bias else None
+            raise ValueError(f"in_features = {in_features}: the GEMM kernels need a multiple of 64")
+        self.in_features, self.out_features, self.act = in_features, out_features, act
+        new = dict(device=device)
+        self.register_buffer("weight", torch.zeros((out_features, in_features // 2), dtype=torch.uint8, **new))
+        self.register_buffer("weight_scale", torch.zeros((out_features, in_features // 16), dtype=torch.float8_e4m3fn, **new))
+        self.register_buffer("weight_scale_2", torch.ones(1, dtype=torch.float32, **new))
+        self.bias = torch.nn.Parameter(torch.zeros(out_features, dtype=dtype, **new), requires_grad=False) if bias else None
 
     @classmethod
     def from_linear(cls, linear: torch.nn.Linear, global_scale: Optional[torch.Tensor] = None, act: str = "auto") -> "NVFP4Linear":
-        """Quantize ``linear`` (a CUDA module) into the ModelOpt checkpoint layout: 1 x 16 blocks, linear scales, a global
-        decode factor (amax / (6 * 448) unless given)."""
-        w = linear.weight.detach()
-        m = cls(linear.in_features, linear.out_features, linear.bias is not None, device=w.device,
-                dtype=linear.bias.dtype if linear.bias is not None else w.dtype, act=act)
+        """The NVFP4 version of a CUDA ``nn.Linear``: 1 x 16 blocks, linear E4M3 scales, and as global the decode factor
+        ``max |W| / (6 x 448)`` (1 for an all-zero weight) unless one is given."""
+        source = linear.weight.detach()
+        has_bias = linear.bias is not None
+        layer = cls(linear.in_features, linear.out_features, has_bias, device=source.device, dtype=linear.bias.dtype if has_bias else source.dtype,
+                    act=act)
         if global_scale is None:
-            a = w.abs().amax().float().reshape(1)
-            global_scale = torch.where(a > 0, a / (6.0 * 448.0), torch.ones_like(a))
-        q = NVFP4Tensor.from_float(w, global_scale)
-        m.weight.copy_(q.data)
-        m.weight_scale.copy_(q.scales)
-        m.weight_scale_2.copy_(q.global_scale)
-        if linear.bias is not None:
-            m.bias.data.copy_(linear.bias.detach())
-        return m
+            peak = source.abs().max().to(torch.float32).reshape(1)
+            global_scale = torch.where(peak > 0, peak / (6.0 * 448.0), torch.ones_like(peak))
+        packed = NVFP4Tensor.from_float(source, global_scale)
+        with torch.no_grad():
+            layer.weight.copy_(packed.data)
+            layer.weight_scale.copy_(packed.scales)
+            layer.weight_scale_2.copy_(packed.global_scale)
+            if has_bias:
+                layer.bias.copy_(linear.bias.detach())
+        return layer
 
     def nvfp4_weight(self) -> NVFP4Tensor:
         return NVFP4Tensor(self.weight, self.weight_scale, self.weight_scale_2)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from .api import linear
-        bias = self.bias if self.bias is None or self.bias.dtype == x.dtype else self.bias.to(x.dtype)
+        bias = self.bias
+        if bias is not None and bias.dtype != x.dtype:
+            bias = bias.to(x.dtype)
         return linear(x, self.nvfp4_weight(), bias, act=self.act)
 
     def extra_repr(self):
-        return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, NVFP4, act={self.act}"
+        return f"{self.in_features} -> {self.out_features}, bias={self.bias is not None}, weight=NVFP4, act={self.act}"
 
 
 def quantize_linear_(module: torch.nn.Module, *, act: str = "auto") -> torch.nn.Module:
-    """Replace, in place, every ``nn.Linear`` inside ``module`` whose in_features is a multiple of 64 by an ``NVFP4Linear``."""
-    for name, child in list(module.named_children()):
-        if isinstance(child, torch.nn.Linear) and child.in_features % 64 == 0:
-            setattr(module, name, NVFP4Linear.from_linear(child, act=act))
+    """Walks ``module`` and swaps, in place, each ``nn.Linear`` whose in_features is a multiple of 64 for an ``NVFP4Linear``
+    built from it; other layers (and linears of other widths) stay as they are.  Returns ``module``."""
+    for name, child in module.named_children():
+        convertible = isinstance(child, torch.nn.Linear) and child.in_features % 64 == 0
+        if convertible:
+            module.add_module(name, NVFP4Linear.from_linear(child, act=act))
         else:
             quantize_linear_(child, act=act)
     return module

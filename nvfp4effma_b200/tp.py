@@ -17,8 +17,11 @@ from typing import List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+import ctypes
+
+from . import _abi as A
 from . import _lib as L
-from . import _ops
+from ._ops import ops
 from .tensor import NVFP4Tensor
 
 ROW_ALIGN = 128
@@ -69,6 +72,69 @@ def gather_features(y_shard: torch.Tensor, group=None, out: Optional[torch.Tenso
     return out
 
 
+# ---- calls into the C ABI that the operator layer does not cover (SwiGLU on images, the fused all-gather entries) -------------
+def _ptr_array(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def _image_tensor(image, glob, flags, scale_max):
+    return L.Tensor(A.addr(image), L.NVFP4, None, 0, A.addr(glob), None, flags, scale_max)
+
+
+def _swiglu_descriptor(on):
+    ex = L.Epilogue()
+    ex.swiglu = int(bool(on))
+    return ex
+
+
+def _tp_gather(buffer_ptrs, flag_ptrs, rank, rows, row_pitch_bytes, col_offset_bytes, shard_bytes):
+    """``nvfp4a_b200_tp_gather``: push this rank's columns of a peer-mapped activation buffer to every peer, then barrier."""
+    L.check(L.lib.nvfp4a_b200_tp_gather(_ptr_array(buffer_ptrs), _ptr_array(flag_ptrs), len(buffer_ptrs), rank, rows, row_pitch_bytes,
+                                        col_offset_bytes, shard_bytes, A.stream()))
+
+
+def _local_gemv(x, layer, out):
+    """Up to 8 tokens against this rank's image: ``nvfp4a_gemv_tc(_ex)`` writing ``out`` [T, rows (/ 2 with SwiGLU)]."""
+    x = A.matrix(x, 64, "x")
+    a, b, d = _image_tensor(layer.image, layer.global_scale, layer.flags, layer.scale_max), A.dense_tensor(x), A.dense_tensor(out)
+    bias = A.dense_tensor(layer.bias) if layer.bias is not None else None
+    ex = _swiglu_descriptor(layer.swiglu)
+    L.check(L.lib.nvfp4a_gemv_tc_ex(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), x.stride(0), 0.0, None, 0,
+                                    ctypes.byref(d), out.stride(0), A.ref(bias), ctypes.byref(ex), A.stream()))
+    return out
+
+
+def _local_gemm(x, layer, out):
+    """More than 8 tokens: ``nvfp4a_gemm_tc(_ex)`` with contiguous bfloat16 ``x`` serving as its own activation image."""
+    if not (x.is_contiguous() and x.data_ptr() % 16 == 0):
+        x = x.contiguous()
+    a, b, d = _image_tensor(layer.image, layer.global_scale, layer.flags, layer.scale_max), A.dense_tensor(x), A.dense_tensor(out)
+    bias = A.dense_tensor(layer.bias) if layer.bias is not None else None
+    ex = _swiglu_descriptor(layer.swiglu)
+    L.check(L.lib.nvfp4a_gemm_tc_ex(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), 0.0, None, 0, ctypes.byref(d),
+                                    out.stride(0), A.ref(bias), ctypes.byref(ex), A.addr(A.workspace(x.device)), A.stream()))
+    return out
+
+
+def _fused_call(entry, x, layer, out, buffer_ptrs, flag_ptrs, rank):
+    """``nvfp4a_b200_gemv_tc_tp`` / ``nvfp4a_b200_gemm_tc_tp``: ``out`` (a view into this rank's peer-mapped buffer) is also
+    written into every peer's buffer and the ranks meet in a barrier."""
+    gemv = entry == "gemv"
+    x = A.matrix(x, 64, "x") if gemv else (x if x.is_contiguous() and x.data_ptr() % 16 == 0 else x.contiguous())
+    a, b, d = _image_tensor(layer.image, layer.global_scale, layer.flags, layer.scale_max), A.dense_tensor(x), A.dense_tensor(out)
+    bias = A.dense_tensor(layer.bias) if layer.bias is not None else None
+    ex = _swiglu_descriptor(layer.swiglu)
+    tail = (_ptr_array(buffer_ptrs), _ptr_array(flag_ptrs), len(buffer_ptrs), rank, A.stream())
+    if gemv:
+        st = L.lib.nvfp4a_b200_gemv_tc_tp(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), x.stride(0), ctypes.byref(d),
+                                          out.stride(0), A.ref(bias), ctypes.byref(ex), *tail)
+    else:
+        st = L.lib.nvfp4a_b200_gemm_tc_tp(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), out.stride(0),
+                                          A.ref(bias), ctypes.byref(ex), A.addr(A.workspace(x.device)), *tail)
+    L.check(st)
+    return out
+
+
 class PeerGather:
     """Activation buffers that exist at the same place on every GPU of the node (torch symmetric memory: peer-mapped device
     memory) and the library's own all-gather over them: a rank writes its columns of ``y`` into its local buffer, one launch
@@ -92,7 +158,7 @@ class PeerGather:
         return self.bufs[slot][:T * M].view(T, M)
 
     def push(self, slot: int, T: int, M: int, col0: int, cols: int):
-        _ops.tp_gather(self.buf_ptrs[slot], self.flag_ptrs, self.rank, T, M * 2, col0 * 2, cols * 2)
+        _tp_gather(self.buf_ptrs[slot], self.flag_ptrs, self.rank, T, M * 2, col0 * 2, cols * 2)
 
 
 class TPLinear:
@@ -117,10 +183,10 @@ class TPLinear:
         self.out_features, self.in_features = weight.shape[0] // (2 if swiglu else 1), weight.shape[1]
         self.swiglu = swiglu
         shard = shard_rows(weight, self.world, self.rank)
-        d, s, g, f, smax, k = shard._flat()
-        self.rows = d.shape[0]
-        self.global_scale, self.flags, self.scale_max = g, f, smax
-        self.image = _ops.tc_image(0, d, s.view(torch.uint8), f, k)
+        op = shard._operand()
+        self.rows = op.rows
+        self.global_scale, self.flags, self.scale_max = op.glob, op.flags, op.scale_max
+        self.image = ops.tc_image(L.TC_A16, op.data, op.scales, op.flags, op.cols)
         a, b = shard_bounds(weight.shape[0], self.world, self.rank)
         self.bias = bias[a:b].contiguous() if bias is not None else None
 
@@ -128,12 +194,9 @@ class TPLinear:
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
             raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
         T = x.shape[0]
-        if T <= 8:
-            return _ops.linear(x, None, None, 0, 0, None, None, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias,
-                               torch.bfloat16, out, w_img=self.image, w_rows=self.rows, swiglu=self.swiglu)
-        xi = _ops.tc_image(1, x, None, 0, self.in_features)
-        return _ops.linear_tc(xi, 2, None, 0, 0, T, self.image, self.global_scale, self.flags, self.scale_max, self.rows, self.in_features,
-                              self.bias, torch.bfloat16, out, swiglu=self.swiglu)
+        if out is None:
+            out = torch.empty((T, self.rows // (2 if self.swiglu else 1)), dtype=torch.bfloat16, device=x.device)
+        return _local_gemv(x, self, out) if T <= 8 else _local_gemm(x, self, out)
 
     def forward(self, x: torch.Tensor, slot: int = 0) -> torch.Tensor:
         if self.world == 1:
@@ -146,12 +209,10 @@ class TPLinear:
         if T <= 8 and self.fused_decode:   # the GEMV's last CTA stores to every rank and joins the barrier itself
             if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
                 raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
-            _ops.gemv_tp(x, self.image, self.rows, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias, mine, self.swiglu,
-                         self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
+            _fused_call("gemv", x, self, mine, self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
         elif T > 8 and self.fused_prefill and x.dtype == torch.bfloat16:
             # the GEMM's epilogue stores every tile into all ranks' buffers (TMA stores to peer memory), then the barrier
-            _ops.gemm_tp(x, self.image, self.rows, self.global_scale, self.flags, self.scale_max, self.in_features, self.bias, mine, self.swiglu,
-                         self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
+            _fused_call("gemm", x, self, mine, self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
         else:
             self.forward_local(x, out=mine)
             self.gather.push(slot, T, M, self.rank * nl, nl)
