@@ -30,6 +30,16 @@ int nvfp4a_b200_set_route(int route);
  * This call SYNCHRONISES the device, copies the word to *status (0 = healthy) and clears it when reset != 0. */
 nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
 
+/* Measured ceiling of the block-scaled FP4 tensor-core instruction (no counterpart in the reference, which has no sm_100 kernel):
+ * every SM's MMA thread issues 4 * iters tcgen05.mma kind::mxf4nvf4 of 128 x bn x 64 (pair != 0: cta_group::2, 256 x bn x 64 per SM
+ * pair) back to back on one resident operand stage -- no loads, no epilogue; commit_each bit 0: one tcgen05.commit per four, bit 1: the twelve
+ * 512-byte scale tiles of a stage copied into tensor memory by tcgen05.cp before each four.
+ * cycles (device, 2 x unsigned long long per CTA of the launch: one CTA per SM) receives, for CTAs that issue, the SM clocks from the
+ * first issue to the last issue and to the completion of all MMAs.  The launch is timed by the caller (CUDA events); its flop count
+ * is SMs * 4 * iters * 2 * 128 * bn * 64.  Measurement aid: the numbers under profiles/ that the W4A4 GEMM's fraction is quoted
+ * against come from this call. */
+nvfp4a_status nvfp4a_b200_mma_ceiling(int bn, int pair, int iters, int commit_each, unsigned long long *cycles, cudaStream_t stream);
+
 /* Pins the token-tile width of the W4A4 tcgen05 GEMM: 0 = by problem size, 128 (two accumulators in tensor memory, the
  * epilogue overlaps the next tile) or 256 (one accumulator, less shared-memory traffic per flop).  Tuning / test aid, no
  * counterpart in the reference.  Returns 0, or -1 for another value. */

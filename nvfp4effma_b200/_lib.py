@@ -82,6 +82,7 @@ _PROTOS = {
     "nvfp4a_b200_tp_gather": (_i, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _i, C.c_longlong, C.c_longlong, C.c_longlong, _s]),
     "nvfp4a_b200_gemm_ex_static": (_i, _GEMM + [_E, _s]),
     "nvfp4a_b200_static_scratch_tokens": (_i, []),
+    "nvfp4a_b200_mma_ceiling": (_i, [_i, _i, _i, _i, _v, _s]),
 }
 EXPORTS = tuple(_PROTOS)
 

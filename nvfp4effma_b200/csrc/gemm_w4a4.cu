@@ -653,7 +653,7 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
-            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -661,7 +661,7 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
 // image tile for an image) of row_bytes bytes, `stride` bytes apart; a box is 2 KiB of one row (the four tiles of 256
 // values of k), zero-filled where it passes the end of the row.  Rank 3 like the nibble maps, so that one instruction
 // can issue both.
-static bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride) {
+bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {row_bytes / 8, rows, 1};
@@ -718,7 +718,11 @@ void set_w4a4_pair(int mode) { g_w4a4_pair = mode; }
 static int g_w4a4_swap = -1;  // 1: tokens on the MMA's M side whenever D can be stored that way; -1: unless that costs a round of tiles; 0: never
 void set_w4a4_swap(int mode) { g_w4a4_swap = mode; }
 
+bool gemm_w4a4_pair_applies(const GemmArgs &g, bool force);
+cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s);
+
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
+  if (g_w4a4_pair != 0 && g_w4a4_swap != 0 && !g_w4a4_bn && gemm_w4a4_pair_applies(g, g_w4a4_pair == 1)) return launch_gemm_w4a4_pair(g, s);
   W4A4Args a;
   memset(&a, 0, sizeof a);
   a.k = g.k;

@@ -205,6 +205,10 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t 
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {   // both CTAs of a pair, each from its own shared memory
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // ---- UMMA descriptors --------------------------------------------------------------------------------------------------------
 // Shared memory matrix descriptor (64 bit): start address >> 4 in bits [0, 14), leading byte offset >> 4 in [16, 30),
 // stride byte offset >> 4 in [32, 46), descriptor version 1 in [46, 48), layout type in [61, 64)
@@ -262,6 +266,9 @@ bool make_tmap_bytes(CUtensorMap *map, const void *base, uint64_t row_bytes, uin
 // no swizzle (the epilogue's store of D)
 bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t stride,
                      uint32_t box_inner, uint32_t box_outer, int swizzle = 0);
+// Block scales stored as 512-byte tiles (the swizzled layout), as a tensor of 8-byte words: `rows` rows of row_bytes bytes `stride`
+// bytes apart; a box is 2 KiB of one row (the four tiles of 256 values of k), zero-filled past the end of the row.
+bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride);
 // kernel status word: 0 = healthy; kernels that gave up a wait write a non-zero code (see nvfp4a_b200_kernel_status)
 unsigned int *kernel_status_device_ptr();
 
