@@ -17,7 +17,7 @@ OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libnvfp4effma.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC,-ffp-contract=off",
-         "-Xptxas", "-v", "--expt-relaxed-constexpr"]
+         "-Xptxas", "-v", "--expt-relaxed-constexpr"] + os.environ.get("NVFP4A_NVCC_FLAGS", "").split()
 
 
 def _newest_header():

@@ -12,17 +12,23 @@
 // (columns), so that a lane's accumulator columns are consecutive elements of column-major D.
 //
 // Per CTA, 16 warps:
-//   warp 0      operand producer: the stage's two nibble tiles (its 128 M rows, its 128 of the 256 N rows) by ONE TMA
-//               instruction of two lanes; both CTAs' bytes are counted on the even CTA's `full` barrier
-//   warp 1      lane 0 of the EVEN CTA issues the MMAs for the pair; the warp owns the tensor memory allocation
-//   warp 2      scale producer: the stage's three 2 KiB scale tiles into a ring of their own, several stages ahead
+//   warp 0      operand producer: the stage's two nibble tiles (its 128 M rows, its half of the N rows).  Both CTAs' bytes are
+//               counted on the even CTA's `full` barrier, on which the scale warps of both CTAs arrive too, so the MMA warp
+//               waits once per stage.
+//   warp 1      MMA warp of the EVEN CTA: the whole warp runs the loop and one elected lane issues a stage's four MMAs and
+//               its commit in one statement.  Issued from inside a one-lane branch, every tcgen05.mma costs about 150 cycles
+//               whatever its shape -- more than the 128 the tensor pipe needs for it (measured; see sm100.cuh).  The warp owns
+//               the tensor memory allocation.
+//   warps 2, 3  scale producers (alternate stages): the stage's three 2 KiB scale tiles into a ring of their own, several
+//               stages ahead of the operands
 //   warps 4-7   scale warps: shared memory -> registers -> tensor memory (tcgen05.st; one 32-lane quadrant each), so the
-//               MMA thread never waits for scales and issues nothing but MMAs (tcgen05.cp on its queue costs the tensor
-//               pipe about 27 cycles per 512-byte tile: measured)
-//   warps 8-15  epilogue: quadrant = warp % 4, column half = (warp - 8) / 4.  A warp pulls its 32 x 128 accumulator block
-//               out of tensor memory in four loads, hands the accumulator back as soon as the last has landed, and
-//               stores two 32 x 64 boxes from its own 4 KiB staging tile (128-byte TMA swizzle: conflict-free 16-byte
-//               shared-memory stores), the second after the next tile's MMAs are already running.
+//               MMA warp never waits for scales and issues nothing but MMAs (tcgen05.cp on its queue costs the tensor pipe
+//               about 27 cycles per 512-byte tile: measured)
+//   warps 8-15  epilogue (168 registers each, taken from the other eight warps by setmaxnreg): quadrant = warp % 4, column
+//               half = (warp - 8) / 4.  A warp pulls its whole 32 x 128 accumulator block into registers with four loads and
+//               hands the accumulator back at once; scaling, rounding and the two 32 x 64 box stores from its 4 KiB staging
+//               tile (128-byte TMA swizzle: conflict-free 16-byte shared-memory stores) run under the next tile's MMAs.
+// Tiles that would fill at most half of the SM pairs in the last round are cut into two 128-wide halves.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
 //
 // Edges need no special code: TMA loads outside an operand read zeros (zero nibbles under zero scales contribute nothing),
@@ -39,6 +45,7 @@ struct PairArgs {
   int xm, yn, k;             // rows of the M-side operand (tokens), rows of the N-side operand (weight rows), k
   int x_image, y_image;      // operand is an image (3-D maps: one tile per z)
   int ktiles;                // image: 256-k tiles per row tile
+  int nfull, nhalf;          // tiles 0 .. nfull - 1 are 256 columns wide, the nhalf tiles after them 128 (two per 256-wide tile)
   const float *g_tok;        // global of the M-side operand (the call's B): NULL = 1
   int g_tok_stride;          // 0: one value, 1: one per token
   const float *g_w;          // global of the N-side operand (the call's A), one value: NULL = 1
@@ -54,11 +61,24 @@ constexpr int kPStagingBytes = 8 * 4096, kPBarrierBytes = 512;
 constexpr int kPairSmem = kPairStages * kPStage + kPStagingBytes + kPairSlots * kSlotBytes + kPBarrierBytes + 1024;
 static_assert(kPairSmem <= 232448, "shared memory budget");
 static_assert(kPAccCols + kPairStages * kPSfCols <= 512, "tensor memory budget");
-constexpr unsigned kPStatFull = 0x111, kPStatEmpty = 0x112, kPStatTmemFull = 0x113, kPStatTmemEmpty = 0x114, kPStatScale = 0x115, kPStatSf = 0x116;
+constexpr unsigned kPStatFull = 0x111, kPStatEmpty = 0x112, kPStatTmemFull = 0x113, kPStatTmemEmpty = 0x114, kPStatScale = 0x115;
+
+
+// Tile t of the schedule: the 256 tokens [256 tx, +256) against `width` N-side rows starting at the 128-row tile y128.  The tiles
+// that would fill only part of the last round over the SM pairs are cut in two 128-wide halves, so that round costs half.
+struct PairTile { int tx, y128, width; };
+__device__ __forceinline__ PairTile pair_tile(int t, int tiles_x, int nfull) {
+  if (t < nfull) return PairTile{t % tiles_x, 2 * (t / tiles_x), 256};
+  const int h = t - nfull, f = nfull + (h >> 1);
+  return PairTile{f % tiles_x, 2 * (f / tiles_x) + (h & 1), 128};
+}
+
+
+
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
-                      const __grid_constant__ CUtensorMap tmap_sx, const __grid_constant__ CUtensorMap tmap_sy,
+                      const __grid_constant__ CUtensorMap tmap_y64, const __grid_constant__ CUtensorMap tmap_sx, const __grid_constant__ CUtensorMap tmap_sy,
                       const __grid_constant__ CUtensorMap tmap_d, const PairArgs g) {
   constexpr int S = kPairStages, SD = kPairSlots;
   extern __shared__ uint8_t smem_raw[];
@@ -66,15 +86,15 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   uint8_t *staging = smem + S * kPStage;
   uint8_t *scale_ring = staging + kPStagingBytes;
   uint64_t *bars = (uint64_t *)(scale_ring + SD * kSlotBytes);
-  uint64_t *full = bars, *empty = full + S, *sf_ready = empty + S, *sfs_full = sf_ready + S, *sfs_empty = sfs_full + SD,
-           *tmem_full = sfs_empty + SD, *tmem_empty = tmem_full + 1;
+  uint64_t *full = bars, *empty = full + S, *sfs_full = empty + S, *sfs_empty = sfs_full + SD, *tmem_full = sfs_empty + SD,
+           *tmem_empty = tmem_full + 1;
   uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 1);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = (int)cluster_ctarank();
   const int xm = g.xm, yn = g.yn, ktiles = g.ktiles;
-  const int tiles_x = (xm + 255) / 256, ntiles = tiles_x * ((yn + 255) / 256);
+  const int tiles_x = (xm + 255) / 256, nfull = g.nfull, ntiles = nfull + g.nhalf;
   const int tile_first = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
   const int nk = (g.k + 255) / 256;
   const int my_tiles = tile_first < ntiles ? (ntiles - tile_first + tile_step - 1) / tile_step : 0;
@@ -82,7 +102,7 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   unsigned *const status_word = g.status;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 8); }
+    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 9); mbar_init(&empty[s], 1); }
     for (int q = 0; q < SD; ++q) { mbar_init(&sfs_full[q], 1); mbar_init(&sfs_empty[q], 4); }
     mbar_init(tmem_full, 1);
     mbar_init(tmem_empty, 16);
@@ -90,6 +110,7 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     fence_barrier_init();
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_y);
+    prefetch_tensormap(&tmap_y64);
     prefetch_tensormap(&tmap_sx);
     prefetch_tensormap(&tmap_sy);
     prefetch_tensormap(&tmap_d);
@@ -109,123 +130,128 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     return false;
   };
 
+  // The epilogue warps hold a 32 x 128 accumulator block in registers at once (so that the accumulator goes back to the MMA thread
+  // after four loads, before any arithmetic); the registers come from the eight warps that need few.
+  if (warp < 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // ---------------- operand producer ----------------
-    // lane 0: this CTA's 128 rows of the M side; lane 1: its 128 of the tile's 256 N-side rows.  Bytes of both CTAs count on
-    // the even CTA's barrier, whose MMA thread reads both CTAs' shared memory.
-    const bool image = lane == 0 ? g.x_image : g.y_image;
-    const CUtensorMap *const map = lane == 0 ? &tmap_x : &tmap_y;
-    const uint32_t dst_off = lane == 0 ? 0 : kXBytes;
+    // The stage's two nibble tiles: this CTA's 128 rows of the M side, and its half of the tile's N-side rows (128 of 256, or 64
+    // of 128).  Bytes of both CTAs count on the even CTA's barrier, whose MMA warp reads both CTAs' shared memory.  The whole warp
+    // runs the loop and one elected lane issues (see tma_load_3d_pair_elect).
+    const bool x_image = g.x_image, y_image = g.y_image;
     int t = tile_first, ks = 0;
-    int row_tile = 0;   // this lane's 128-row tile of its operand
+    const CUtensorMap *map_y = &tmap_y;
+    int x_tile = 0, y_tile = 0, y_row = 0;   // 128-row tile of each operand and, for the N side, the first row inside it
+    uint32_t stage_bytes = 0;
     auto tile_setup = [&]() {
-      const int tx = t % tiles_x, ty = t / tiles_x;
-      row_tile = lane == 0 ? 2 * tx + rank : 2 * ty + rank;
+      const PairTile p = pair_tile(t, tiles_x, nfull);
+      stage_bytes = 2u * (kXBytes + p.width * 64);
+      x_tile = 2 * p.tx + rank;
+      if (p.width == 256) { map_y = &tmap_y; y_tile = p.y128 + rank; y_row = 0; }
+      else { map_y = &tmap_y64; y_tile = p.y128; y_row = rank * 64; }
     };
     if (total > 0) tile_setup();
     for (int it = 0; it < total; ++it) {
       const int s = it % S;
-      if (!wait(&empty[s], ((it / S) & 1) ^ 1, kPStatEmpty)) break;
-      if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&full[s], 2 * kPStage);
-      __syncwarp();
-      if (lane < 2) {
-        const uint32_t dst = smem_u32(smem + (size_t)s * kPStage + dst_off);
-        const uint32_t bar = mbar_addr_rank(&full[s], 0);
-        if (image) tma_load_3d_pair(dst, map, 0, 0, row_tile * ktiles + ks, bar);
-        else tma_load_3d_pair(dst, map, ks * 128, row_tile * 128, 0, bar);
-      }
+      if (!__all_sync(0xFFFFFFFFu, wait(&empty[s], ((it / S) & 1) ^ 1, kPStatEmpty))) break;
+      if (rank == 0) mbar_arrive_expect_tx_elect(&full[s], stage_bytes);
+      const uint32_t dst = smem_u32(smem + (size_t)s * kPStage), bar = mbar_addr_rank(&full[s], 0);
+      if (x_image) tma_load_3d_pair_elect(dst, &tmap_x, 0, 0, x_tile * ktiles + ks, bar);
+      else tma_load_3d_pair_elect(dst, &tmap_x, ks * 128, x_tile * 128, 0, bar);
+      if (y_image) tma_load_3d_pair_elect(dst + kXBytes, map_y, 0, y_row, y_tile * ktiles + ks, bar);
+      else tma_load_3d_pair_elect(dst + kXBytes, map_y, ks * 128, y_tile * 128 + y_row, 0, bar);
       if (++ks == nk) { ks = 0; t += tile_step; tile_setup(); }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (even CTA) ----------------
-    if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = idesc_mxf4nvf4(256, 256);
+    // The WHOLE warp runs this loop and one elected lane issues each instruction: descriptors, tensor memory addresses and loop
+    // state then stay on the uniform datapath, from which tcgen05 instructions take their operands.  Issued from inside a
+    // one-lane branch, every MMA costs about 150 cycles whatever its shape (measured with nvfp4a_b200_mma_ceiling) -- more than
+    // the 128 cycles the tensor pipe needs for 128 x 256 x 64.
+    if (rank == 0) {
       const uint64_t da0 = smem_desc_sw128(smem_u32(smem));
       int it = 0;
       for (int tile_i = 0; tile_i < my_tiles; ++tile_i) {
-        if (!wait(tmem_empty, (tile_i & 1) ^ 1, kPStatTmemEmpty)) goto done;
+        const int width = pair_tile(tile_first + tile_i * tile_step, tiles_x, nfull).width;
+        const uint32_t idesc = idesc_mxf4nvf4(256, width), sfb_step = (uint32_t)width >> 5;
+        if (!__all_sync(0xFFFFFFFFu, wait(tmem_empty, (tile_i & 1) ^ 1, kPStatTmemEmpty))) goto done;
         tc_fence_after();
         for (int ks = 0; ks < nk; ++ks, ++it) {
           const int s = it % S;
           const uint32_t par = (it / S) & 1;
-          if (!wait(&sf_ready[s], par, kPStatSf) || !wait(&full[s], par, kPStatFull)) goto done;
+          // one barrier per stage: the operand bytes of both CTAs and the eight scale warps' arrivals (scales in tensor memory)
+          if (!__all_sync(0xFFFFFFFFu, wait(&full[s], par, kPStatFull))) goto done;
           tc_fence_after();
           const uint64_t da = da0 + (uint32_t)s * (uint32_t)(kPStage >> 4), db = da + (kXBytes >> 4);
-          const uint32_t sfa = tmem_base + kPAccCols + s * kPSfCols, sfb = sfa + 16;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)   // 64 values of k each: 32 bytes further along every 128-byte row
-            mma_mxf4nvf4_pair(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa + 4 * j, sfb + 8 * j, j ? 1u : (uint32_t)(ks != 0));
-          tc_commit_pair(&empty[s]);   // both CTAs: stage s and scale buffer s are free once these MMAs have read them
+          const uint32_t sfa = tmem_base + kPAccCols + s * kPSfCols;
+          // the stage's four MMAs (64 values of k each: 32 bytes further along every 128-byte row) and the commit that frees stage s
+          // and scale buffer s in both CTAs once they have been read
+          mma4_commit_pair_elect(tmem_base, da, db, idesc, sfa, sfa + 16, sfb_step, (uint32_t)(ks != 0), &empty[s]);
         }
-        tc_commit_pair(tmem_full);
+        tc_commit_pair_elect(tmem_full);
       }
     }
-  } else if (warp == 2) {
-    // ---------------- scale producer ----------------
-    // lane 0: the scale tiles of this CTA's 128 M-side rows; lanes 1, 2: those of the tile's two 128-row halves of the N side
-    // (every CTA needs all of them in its tensor memory).  A box is the four 512-byte tiles of 256 values of k.
+  } else if (warp == 2 || warp == 3) {
+    // ---------------- scale producers ----------------
+    // Per stage: the scale tiles of this CTA's 128 M-side rows (lane 0) and those of ALL of the tile's N-side rows (lanes 1, 2: every
+    // CTA needs them in its tensor memory), one TMA instruction of up to three lanes; a box is the four 512-byte tiles of 256 values
+    // of k.  The ring has its own slots and barriers, so the scales run several stages ahead of the operands and their trip
+    // through registers into tensor memory costs the MMAs nothing.  Issuing a TMA instruction occupies a warp for a few hundred
+    // cycles, so two warps take alternate stages.
     const bool image = lane == 0 ? g.x_image : g.y_image;
     const CUtensorMap *const map = lane == 0 ? &tmap_sx : &tmap_sy;
-    const uint32_t dst_off = lane == 0 ? 0 : 2048 * lane;
-    int t = tile_first, ks = 0, row_tile = 0;
-    auto tile_setup = [&]() {
-      const int tx = t % tiles_x, ty = t / tiles_x;
-      row_tile = lane == 0 ? 2 * tx + rank : 2 * ty + (lane - 1);
-    };
-    if (total > 0) tile_setup();
-    for (int it = 0; it < total; ++it) {
-      const int q = it % SD;
+    for (int it = warp - 2; it < total; it += 2) {
+      const int q = it % SD, ks = it % nk;
+      const PairTile p = pair_tile(tile_first + (it / nk) * tile_step, tiles_x, nfull);
+      const int boxes = 1 + p.width / 128, row_tile = lane == 0 ? 2 * p.tx + rank : p.y128 + lane - 1;
       if (!wait(&sfs_empty[q], ((it / SD) & 1) ^ 1, kPStatScale)) break;
-      if (lane == 0) mbar_arrive_expect_tx(&sfs_full[q], kSlotBytes);
+      if (lane == 0) mbar_arrive_expect_tx(&sfs_full[q], 2048u * boxes);
       __syncwarp();
-      if (lane < 3) {
-        const uint32_t dst = smem_u32(scale_ring + q * kSlotBytes + dst_off);
-        const uint32_t bar = mbar_addr_rank(&sfs_full[q], rank);
+      if (lane < boxes) {
+        const uint32_t dst = smem_u32(scale_ring + q * kSlotBytes) + 2048 * lane, bar = mbar_addr_rank(&sfs_full[q], rank);
         if (image) tma_load_3d_pair(dst, map, 0, row_tile * ktiles + ks, 0, bar);
         else tma_load_3d_pair(dst, map, ks * 256, row_tile, 0, bar);
       }
-      if (++ks == nk) { ks = 0; t += tile_step; tile_setup(); }
     }
   } else if (warp >= 4 && warp < 8) {
     // ---------------- scale warps ----------------
     // A 512-byte tile's 16 bytes at offset 16 l are what lane l of every quadrant holds in four scale columns; each of the four
     // warps writes its own quadrant.  Buffer s of tensor memory is free when the MMAs of the stage's previous round are done.
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int ks = 0, tile_i = 0;
+    bool wide = total > 0 && pair_tile(tile_first, tiles_x, nfull).width == 256;
     for (int it = 0; it < total; ++it) {
       const int q = it % SD, s = it % S;
       if (!wait(&sfs_full[q], (it / SD) & 1, kPStatScale)) break;
       const uint8_t *src = scale_ring + q * kSlotBytes + lane * 16;
-      uint4 va[4], vb[2][4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) va[j] = *(const uint4 *)(src + j * 512);
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) vb[h][j] = *(const uint4 *)(src + 2048 + h * 2048 + j * 512);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sfs_empty[q]);
-      if (!wait(&empty[s], ((it / S) & 1) ^ 1, kPStatScale)) break;
+      if (!wait(&empty[s], ((it / S) & 1) ^ 1, kPStatScale)) break;   // scale buffer s: the MMAs of the stage's previous round have read it
       tc_fence_after();
       const uint32_t sf = tmem_base + kPAccCols + s * kPSfCols + lane_base;
-      uint32_t r[16];
+      // groups of four 512-byte tiles -> 16 scale columns each: the M side's; then the N side's -- 256 rows: k groups 0-1 and 2-3, per
+      // 64 values of k [rows 0-127: 4 columns | rows 128-255: 4 columns]; 128 rows: the four k groups, 4 columns each
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { r[4 * j] = va[j].x; r[4 * j + 1] = va[j].y; r[4 * j + 2] = va[j].z; r[4 * j + 3] = va[j].w; }
-      tmem_st16(sf, r);
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {   // N-side columns: per 64 values of k [rows 0-127: 4 columns | rows 128-255: 4 columns]
+      for (int part = 0; part < 3; ++part) {
+        if (part == 2 && !wide) break;
+        uint32_t r[16];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const int j = 2 * part + (c >> 1), h = c & 1;
-          r[4 * c] = vb[h][j].x; r[4 * c + 1] = vb[h][j].y; r[4 * c + 2] = vb[h][j].z; r[4 * c + 3] = vb[h][j].w;
+          const int off = part == 0 ? c * 512 : wide ? 2048 + (c & 1) * 2048 + (2 * (part - 1) + (c >> 1)) * 512 : 2048 + c * 512;
+          const uint4 v = *(const uint4 *)(src + off);
+          r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
         }
-        tmem_st16(sf + 16 + part * 16, r);
+        tmem_st16(sf + 16 * part, r);
       }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_rank(&sf_ready[s], 0);
+      if (lane == 0) mbar_arrive(&sfs_empty[q]);
+      if (lane == 0) mbar_arrive_rank(&full[s], 0);
+      if (++ks == nk) { ks = 0; ++tile_i; wide = pair_tile(tile_first + tile_i * tile_step, tiles_x, nfull).width == 256; }
     }
-  } else if (warp >= 8) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
     // ---------------- epilogue ----------------
     const int ew = warp - 8, quad = ew & 3, half = ew >> 2;
     uint8_t *const box = staging + ew * 4096, *const row = box + lane * 128;
@@ -234,12 +260,14 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     const int g_tok_stride = g.g_tok_stride, d_dtype = g.d_dtype;
     const float gf = g.gf, s_uniform = __fmul_rn(g.alpha, g.g_w ? g.g_w[0] : 1.f);
     float *const amax_out = g.amax;
-    const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
+    const uint32_t acc_lanes = tmem_base + ((uint32_t)(quad * 32) << 16);
     float amax = 0.f;
     int tile_i = 0;
     for (int t = tile_first; t < ntiles; t += tile_step, ++tile_i) {
-      const int tx = t % tiles_x, ty = t / tiles_x;
-      const int tok0 = tx * 256 + rank * 128 + quad * 32, tok = tok0 + lane, col0 = ty * 256 + half * 128;
+      const PairTile p = pair_tile(t, tiles_x, nfull);
+      const bool wide = p.width == 256;          // this warp's block: 128 columns of a 256-wide tile, 64 of a 128-wide one
+      const int tok0 = p.tx * 256 + rank * 128 + quad * 32, tok = tok0 + lane, col0 = p.y128 * 128 + half * (p.width >> 1);
+      const uint32_t acc_addr = acc_lanes + half * (p.width >> 1);
       const float tokp = (g_tok && tok < xm) ? g_tok[(size_t)tok * g_tok_stride] : 1.f;
       const float s_tok = __fmul_rn(__fmul_rn(s_uniform, tokp), gf);
       // scale, amax, round, pack: 32 accumulator columns -> 64 bytes of the lane's row of the box, as four swizzled 16-byte stores
@@ -278,25 +306,28 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       bool okw = wait(tmem_full, tile_i & 1, kPStatTmemFull);
       if (!__all_sync(0xFFFFFFFFu, okw)) break;
       tc_fence_after();
-      uint32_t ra[32], rb[32];
-      tmem_ld32(acc_addr, ra);
-      tmem_ld32(acc_addr + 32, rb);
-      box_free();
-      tmem_ld_wait();
-      stage32(ra, 0);
-      tmem_ld32(acc_addr + 64, ra);
-      stage32(rb, 4);
-      tmem_ld32(acc_addr + 96, rb);
-      store_box(col0);
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32(acc_addr, r0);
+      tmem_ld32(acc_addr + 32, r1);
+      if (wide) {
+        tmem_ld32(acc_addr + 64, r2);
+        tmem_ld32(acc_addr + 96, r3);
+      }
       tmem_ld_wait();
       // every column of this warp's block is in registers: the accumulator goes back to the MMA thread
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_rank(tmem_empty, 0);
       box_free();
-      stage32(ra, 0);
-      stage32(rb, 4);
-      store_box(col0 + 64);
+      stage32(r0, 0);
+      stage32(r1, 4);
+      store_box(col0);
+      if (wide) {
+        box_free();
+        stage32(r2, 0);
+        stage32(r3, 4);
+        store_box(col0 + 64);
+      }
     }
     if (lane == 0) bulk_wait_all();
     if (amax_out) warp_amax_commit(amax_out, amax);
@@ -340,18 +371,19 @@ cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s) {
   a.d_dtype = g.e.d_dtype;
   a.amax = g.e.amax;
   a.status = kernel_status_device_ptr();
-  CUtensorMap tx, ty, tsx, tsy, td;
-  auto maps = [&](const Fp4Operand &o, int rows, CUtensorMap *tn, CUtensorMap *ts) {
-    if (o.image) {
-      const uint64_t tiles = (uint64_t)((rows + 127) / 128) * a.ktiles;
-      return make_tmap_bytes(tn, o.data, 128, 128, 128, 128, tiles, kImgTileBytes) &&
-             make_tmap_scales(ts, (const uint8_t *)o.data + kImgDataBytes, 2048, tiles, kImgTileBytes);
-    }
-    const uint64_t tile_row_bytes = (uint64_t)((-o.sld) >> 2) * 512;
-    return make_tmap_bytes(tn, o.data, (uint64_t)g.k / 2, (uint64_t)rows, (uint64_t)o.ld / 2, 128, 1, (uint64_t)o.ld / 2 * rows) &&
-           make_tmap_scales(ts, o.sc, tile_row_bytes, (uint64_t)(rows + 127) / 128, tile_row_bytes);
+  CUtensorMap tx, ty, ty64, tsx, tsy, td;
+  auto nibble_map = [&](const Fp4Operand &o, int rows, int box_rows, CUtensorMap *tn) {
+    if (o.image) return make_tmap_bytes(tn, o.data, 128, 128, 128, box_rows, (uint64_t)((rows + 127) / 128) * a.ktiles, kImgTileBytes);
+    return make_tmap_bytes(tn, o.data, (uint64_t)g.k / 2, (uint64_t)rows, (uint64_t)o.ld / 2, box_rows, 1, (uint64_t)o.ld / 2 * rows);
   };
-  if (!maps(X, a.xm, &tx, &tsx) || !maps(Y, a.yn, &ty, &tsy)) return cudaErrorInvalidValue;
+  auto scale_map = [&](const Fp4Operand &o, int rows, CUtensorMap *ts) {
+    if (o.image) return make_tmap_scales(ts, (const uint8_t *)o.data + kImgDataBytes, 2048, (uint64_t)((rows + 127) / 128) * a.ktiles, kImgTileBytes);
+    const uint64_t tile_row_bytes = (uint64_t)((-o.sld) >> 2) * 512;
+    return make_tmap_scales(ts, o.sc, tile_row_bytes, (uint64_t)(rows + 127) / 128, tile_row_bytes);
+  };
+  if (!nibble_map(X, a.xm, 128, &tx) || !nibble_map(Y, a.yn, 128, &ty) || !nibble_map(Y, a.yn, 64, &ty64) || !scale_map(X, a.xm, &tsx) ||
+      !scale_map(Y, a.yn, &tsy))
+    return cudaErrorInvalidValue;
   if (!make_tmap_dense(&td, g.e.d, 2, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * 2, 64, 32, 128)) return cudaErrorInvalidValue;
   static std::atomic<unsigned long long> attr_set{0};
   int dev = 0;
@@ -361,7 +393,11 @@ cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     attr_set.fetch_or(1ull << (dev & 63));
   }
-  const int tiles = ((a.xm + 255) / 256) * ((a.yn + 255) / 256), pairs = device_sms() / 2;
+  // The 256-wide tiles that would occupy at most half of the SM pairs in the last round are cut into two 128-wide halves each.
+  const int tiles256 = ((a.xm + 255) / 256) * ((a.yn + 255) / 256), pairs = device_sms() / 2;
+  const int rest = tiles256 % pairs, cut = (tiles256 > pairs && rest > 0 && 2 * rest <= pairs) ? rest : 0;
+  a.nfull = tiles256 - cut; a.nhalf = 2 * cut;
+  const int tiles = a.nfull + a.nhalf;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3(2 * (tiles < pairs ? tiles : pairs), 1, 1);
@@ -372,7 +408,11 @@ cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s) {
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_w4a4_pair_kernel, tx, ty, tsx, tsy, td, a);
+  return cudaLaunchKernelEx(&cfg, gemm_w4a4_pair_kernel, tx, ty, ty64, tsx, tsy, td, a);
 }
 
 }  // namespace nvb
+
+
+
+

@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(kCeilThreads, 1) mma_ceiling_kernel(int bn, in
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *sf_smem = smem + kCeilABytes + kCeilBBytes;   // twelve 512-byte scale tiles (A: 4, B: 8), all 0x38
   uint64_t *bar_done = (uint64_t *)(sf_smem + kCeilSfBytes), *bar_step = bar_done + 1;
-  uint32_t *tmem_slot = (uint32_t *)(bar_step + 1);
+  uint64_t *bar_ring = bar_step + 1;
+  uint32_t *tmem_slot = (uint32_t *)(bar_ring + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = PAIR ? (int)cluster_ctarank() : 0;
 
@@ -33,6 +34,7 @@ __global__ void __launch_bounds__(kCeilThreads, 1) mma_ceiling_kernel(int bn, in
   if (threadIdx.x == 0) {
     mbar_init(bar_done, 1);
     mbar_init(bar_step, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_ring[i], 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -60,13 +62,48 @@ __global__ void __launch_bounds__(kCeilThreads, 1) mma_ceiling_kernel(int bn, in
   else __syncthreads();
   tc_fence_after();
 
-  if (warp == 1 && lane == 0 && rank == 0) {
+  if (warp == 1 && rank == 0 && (commit_each & 16)) {
+    // the whole warp runs the loop; one elected lane issues (see mma_mxf4nvf4_elect)
+    const uint32_t idesc = idesc_mxf4nvf4(PAIR ? 256 : 128, bn);
+    const uint64_t da = smem_desc_sw128(smem_u32(smem)), db = smem_desc_sw128(smem_u32(smem + kCeilABytes));
+    const uint32_t sfa = tmem_base + 256, sfb = sfa + 16, sfb_step = (uint32_t)((bn + 127) / 128) * 4;
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int it = 0; it < iters; ++it) {
+      if (commit_each & 4) tc_fence_after();
+      if (commit_each & 8) { if (it >= 3 && !mbar_wait(&bar_ring[(it - 3) & 3], ((it - 3) >> 2) & 1)) { ok = false; break; } tc_fence_after(); }
+      const uint32_t rot = (commit_each & 32) ? (uint32_t)(it & 1) * 4u : 0u;   // alternate between two descriptor pairs, as stages do
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (PAIR) mma_mxf4nvf4_pair_elect(tmem_base, da + 2 * j + rot, db + 2 * j + rot, idesc, sfa + 4 * j, sfb + sfb_step * j, (uint32_t)((it | j) != 0));
+        else mma_mxf4nvf4_elect(tmem_base, da + 2 * j + rot, db + 2 * j + rot, idesc, sfa + 4 * j, sfb + sfb_step * j, (uint32_t)((it | j) != 0));
+      }
+      if (commit_each & 8) {
+        if (PAIR) tc_commit_pair_elect(&bar_ring[it & 3]);
+        else tc_commit_elect(&bar_ring[it & 3]);
+      } else if (commit_each & 1) {
+        if (PAIR) tc_commit_pair_elect(bar_step);
+        else tc_commit_elect(bar_step);
+      }
+    }
+    const long long t1 = clock64();
+    if (PAIR) tc_commit_pair_elect(bar_done);
+    else tc_commit_elect(bar_done);
+    if (!mbar_wait(bar_done, 0) || !ok) atomicCAS(status, 0u, 0x501u);
+    const long long t2 = clock64();
+    if (lane == 0) {
+      cycles[2 * blockIdx.x] = (unsigned long long)(t1 - t0);
+      cycles[2 * blockIdx.x + 1] = (unsigned long long)(t2 - t0);
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
     const uint32_t idesc = idesc_mxf4nvf4(PAIR ? 256 : 128, bn);
     const uint64_t da = smem_desc_sw128(smem_u32(smem)), db = smem_desc_sw128(smem_u32(smem + kCeilABytes));
     const uint32_t sfa = tmem_base + 256, sfb = sfa + 16, sfb_step = (uint32_t)((bn + 127) / 128) * 4;
     const long long t0 = clock64();
     const uint32_t sf_addr = smem_u32(sf_smem);
     for (int it = 0; it < iters; ++it) {
+      if (commit_each & 4) tc_fence_after();   // as after a barrier wait in the GEMM's main loop
+      if (commit_each & 8) { if (it >= 3 && !mbar_wait(&bar_ring[(it - 3) & 3], ((it - 3) >> 2) & 1)) break; tc_fence_after(); }   // wait for the MMAs of three iterations ago
       if (commit_each & 2) {   // the stage's scale tiles copied from shared memory by this thread (tcgen05.cp), as a GEMM without scale warps would
 #pragma unroll
         for (int q = 0; q < 12; ++q) {
@@ -80,7 +117,10 @@ __global__ void __launch_bounds__(kCeilThreads, 1) mma_ceiling_kernel(int bn, in
         if (PAIR) mma_mxf4nvf4_pair(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa + 4 * j, sfb + sfb_step * j, (uint32_t)((it | j) != 0));
         else mma_mxf4nvf4(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa + 4 * j, sfb + sfb_step * j, (uint32_t)((it | j) != 0));
       }
-      if (commit_each & 1) {   // as the GEMM's main loop does to hand a stage back; nobody waits on this barrier
+      if (commit_each & 8) {
+        if (PAIR) tc_commit_pair(&bar_ring[it & 3]);
+        else tc_commit(&bar_ring[it & 3]);
+      } else if (commit_each & 1) {   // as the GEMM's main loop does to hand a stage back; nobody waits on this barrier
         if (PAIR) tc_commit_pair(bar_step);
         else tc_commit(bar_step);
       }

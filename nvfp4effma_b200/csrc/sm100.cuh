@@ -103,6 +103,23 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
   asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
 }
+// Issued by one elected lane of a CONVERGED warp (the whole warp runs the surrounding loop): coordinates, addresses and the
+// descriptor pointer then stay on the uniform datapath from which the TMA instruction takes its operands.  Inside a one-lane
+// branch the same instruction costs its warp several times as many cycles.
+__device__ __forceinline__ void tma_load_3d_pair_elect(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar_addr) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n\t}"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_elect(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar_addr) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n\t}"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint64_t *bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 // the same with the barrier given as a shared-memory address (lanes of one instruction may name different barriers)
 __device__ __forceinline__ void tma_load_3d_at(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar_addr) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -248,6 +265,51 @@ __device__ __forceinline__ void mma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t a_de
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// The same instructions issued by ONE elected lane of a converged warp: the whole warp runs the surrounding loop, so that the
+// compiler keeps descriptors, addresses and loop state on the uniform datapath, where tcgen05 instructions take their operands.
+__device__ __forceinline__ void mma_mxf4nvf4_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                                   uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                                        uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// One pipeline stage of a block-scaled FP4 GEMM in one statement, issued by one elected lane of a converged warp: four MMAs over the
+// stage's four 64-value k groups (descriptors 32 bytes apart, A-side scale columns 4 apart, B-side `sfb_step` apart), the first
+// accumulating or not as `accumulate` says, then the commit that hands the stage back.  One election serves all five instructions.
+#define NVB_MMA4_BODY(GROUP, COMMIT)                                                                                               \
+  asm volatile("{\n\t.reg .pred p, q, t;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 t, %3, %3;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"      \
+               "@q tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"     \
+               "@q tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %7, %8, %3, [%9], [%10], t;\n\t"    \
+               "@q tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %11, %12, %3, [%13], [%14], t;\n\t" \
+               "@q tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %15, %16, %3, [%17], [%18], t;\n\t" \
+               COMMIT "\n\t}"                                                                                                     \
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb),                              \
+                 "l"(a_desc + 2), "l"(b_desc + 2), "r"(sfa + 4), "r"(sfb + sfb_step),                                                 \
+                 "l"(a_desc + 4), "l"(b_desc + 4), "r"(sfa + 8), "r"(sfb + 2 * sfb_step),                                             \
+                 "l"(a_desc + 6), "l"(b_desc + 6), "r"(sfa + 12), "r"(sfb + 3 * sfb_step), "r"(smem_u32(bar)), "h"((uint16_t)3) : "memory")
+__device__ __forceinline__ void mma4_commit_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                       uint32_t sfb_step, uint32_t accumulate, uint64_t *bar) {
+  NVB_MMA4_BODY("2", "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%19], %20;");
+}
+__device__ __forceinline__ void mma4_commit_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                  uint32_t sfb_step, uint32_t accumulate, uint64_t *bar) {
+  NVB_MMA4_BODY("1", "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%19];");
+}
+__device__ __forceinline__ void tc_commit_elect(uint64_t *bar) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_elect(uint64_t *bar) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
