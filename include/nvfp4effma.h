@@ -78,6 +78,10 @@ typedef struct {
  * Accumulation: FP32.  Columns n <= 8 run the streaming GEMV kernel (fixed split-k order, deterministic); larger n
  * run the tcgen05 kernels, whose sums follow the tensor cores' order.  Either way results agree with the exact
  * block-sum definition of the reference (ref include/nvfp4effma.h:78-92) within an FP32 accumulation bound.
+ * Block scales on the tensor-core routes: the FP4 tensor cores read E4M3 block scales as UNSIGNED (UE4M3).  Codes with the sign bit
+ * set -- which the reference decodes as negative factors (ref src/nvfp4effma.cuh:56-60) but which neither quantizer ever emits -- give
+ * other results on the tcgen05 routes (NVFP4 B with n > 8, and the FP4 tensor-core GEMV) than the reference.  Tensors that carry such
+ * codes must be run with nvfp4a_b200_set_route(1), whose CUDA-core kernels decode them exactly as the reference does.
  * ref include/nvfp4effma.h:93 */
 nvfp4a_status nvfp4a_gemm(int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda,
                           const nvfp4a_tensor *B, int ldb, float beta, const nvfp4a_tensor *C, int ldc,

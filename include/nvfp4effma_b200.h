@@ -25,10 +25,23 @@ int nvfp4a_b200_set_route(int route);
 
 /* Health word of the tensor-core kernels (no counterpart in the reference, whose device-side waits are unbounded:
  * src/tensors/mma.cuh:108-114, src/tensors/gemm_tc.cuh:555 there).  Every wait inside this library's kernels gives up
- * after about a second; the kernel then records which wait it was (0x101 operands not delivered, 0x102 stage never
- * released, 0x103 accumulator never completed, 0x104 accumulator never drained, 0x105 scale gather; 0x2xx the FP4 GEMV, 0x3xx the W4A16 GEMM, 0x401 a peer missing at the tensor-parallel barrier) and returns.
+ * after about a second; the kernel then records what it was waiting for and returns.  The first such record of a device stays in
+ * the word: bits 0-11 the wait (0x101 operands not delivered, 0x102 stage never released, 0x103 accumulator never completed, 0x104
+ * accumulator never drained, 0x105 scale gather, 0x11x the same of the CTA-pair W4A4 kernel; 0x2xx the FP4 GEMV; 0x3xx the W4A16
+ * GEMM; 0x401 a peer missing at the tensor-parallel barrier; 0x501 the ceiling measurement), bits 12-31 the sequence number
+ * (mod 2^20) of the launch that gave up -- nvfp4a_b200_last_launch() returns the number of the calling thread's latest launch of
+ * such a kernel, so a caller can tell its own call from another stream's.  Kernels are asynchronous: the entry point that
+ * launched a kernel which later gives up has long returned NVFP4A_OK, and the kernel's outputs are then incomplete.  Callers that
+ * need to know poll this word at a point where synchronising is acceptable (the end of a forward pass, outside stream capture).
  * This call SYNCHRONISES the device, copies the word to *status (0 = healthy) and clears it when reset != 0. */
 nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int reset);
+unsigned int nvfp4a_b200_last_launch(void);
+
+/* Test aid (no counterpart in the reference): the number of SM clock cycles a tensor-parallel barrier (nvfp4a_b200_tp_gather and the
+ * fused entries) waits for its peers before it records 0x401 and returns; at least 1000, by default 2e9 (about a second -- ranks
+ * that drift further apart than that, e.g. during first-call module loads, trip it).  Process-wide.  Returns 0, or -1 for a
+ * value below 1000. */
+int nvfp4a_b200_set_wait_limit(long long cycles);
 
 /* Measured ceiling of the block-scaled FP4 tensor-core instruction (no counterpart in the reference, which has no sm_100 kernel):
  * every SM's MMA thread issues 4 * iters tcgen05.mma kind::mxf4nvf4 of 128 x bn x 64 (pair != 0: cta_group::2, 256 x bn x 64 per SM
@@ -81,7 +94,9 @@ nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const *flags, in
  * kernel (no counterpart in the reference): D->data points into buffers[rank]; every output is also stored at the same place
  * of each peer's buffer (plain peer stores), and the kernel's last CTA joins the ranks' barrier of nvfp4a_b200_tp_gather
  * (same buffers / flags, same rules).  When the problem runs on another kernel than the mma.sync GEMV, the push is a
- * second launch; the result is the same.  ex may be NULL; a second output (d2) is not supported here. */
+ * second launch; the result is the same.  ex may be NULL; a second output (d2) is not supported here.  With world > 1, D's base, its
+ * column pitch (ldd elements) and one shard row (m, or m / 2 with SwiGLU, elements) must be multiples of 16 bytes: anything else
+ * is NVFP4A_INVALID_VALUE before a kernel is launched. */
 nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
                                      const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
                                      void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream);

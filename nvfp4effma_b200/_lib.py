@@ -83,6 +83,8 @@ _PROTOS = {
     "nvfp4a_b200_gemm_ex_static": (_i, _GEMM + [_E, _s]),
     "nvfp4a_b200_static_scratch_tokens": (_i, []),
     "nvfp4a_b200_mma_ceiling": (_i, [_i, _i, _i, _i, _v, _s]),
+    "nvfp4a_b200_last_launch": (C.c_uint, []),
+    "nvfp4a_b200_set_wait_limit": (_i, [C.c_longlong]),
 }
 EXPORTS = tuple(_PROTOS)
 

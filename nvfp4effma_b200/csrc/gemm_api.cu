@@ -9,6 +9,7 @@
 //   anything else                                       -> exact CUDA-core GEMM (gemm_generic.cu)
 #include <stdio.h>
 #include <stdlib.h>
+#include <atomic>
 #include "operands.cuh"
 
 namespace nvb {
@@ -22,13 +23,15 @@ static bool dense_dt(nvfp4a_dtype t) { return t >= NVFP4A_BF16 && t <= NVFP4A_FP
 
 // Route override (nvfp4a_b200_set_route): 0 = automatic, 1 = always the exact CUDA-core kernel, 2 = automatic without the
 // FP4 tensor-core GEMV.  The environment variable NVFP4A_B200_ROUTE=generic sets the initial value to 1.
-static int g_route = -1;
+static std::atomic<int> g_route{-1};
 static int forced_route() {
-  if (g_route < 0) {
+  int r = g_route.load();
+  if (r < 0) {
     const char *v = getenv("NVFP4A_B200_ROUTE");
-    g_route = v && !strcmp(v, "generic") ? 1 : 0;
+    r = v && !strcmp(v, "generic") ? 1 : 0;
+    g_route = r;
   }
-  return g_route;
+  return r;
 }
 
 static Epilogue make_epilogue(float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, float beta, const nvfp4a_tensor *C, int ldc,
@@ -138,7 +141,7 @@ static BOperand make_b(const nvfp4a_tensor *B, int ldb, int ldsb, int k, bool im
 // nvfp4a_gemm / nvfp4a_gemm_ex
 static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb,
                               float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias,
-                              const EpilogueEx &ex, cudaStream_t stream) {
+                              const EpilogueEx &ex, cudaStream_t stream, bool validate_only = false) {
   if (!A || !B || !D || !A->data || !B->data || !D->data) return fail(NVFP4A_INVALID_VALUE, "%s: A, B or D (or its data pointer) is NULL", fn);
   if (m < 0 || n < 0 || k < 0) return fail(NVFP4A_INVALID_VALUE, "%s: negative size (m = %d, n = %d, k = %d)", fn, m, n, k);
   if (A->dtype != NVFP4A_NVFP4) return fail(NVFP4A_NOT_SUPPORTED, "%s: A must be NVFP4 (dtype %d)", fn, (int)A->dtype);
@@ -178,6 +181,7 @@ static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, 
   g.B = make_b(B, ldb, ldsb, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
+  if (validate_only) return NVFP4A_OK;
   return dispatch(fn, g, stream);
 }
 
@@ -295,14 +299,15 @@ static nvfp4a_status check_weight_image(const char *fn, int kind, const void *im
 }
 
 // nvfp4a_gemm_ex with the RMSNorm column scales of all n tokens computed first into `colscales` (n floats the caller of this
-// function owns for the duration of the call); used by nvfp4a_b200_gemm_ex_static.  The scales kernel runs after the
-// descriptor has been checked and before the operand checks of gemm_run; it writes nothing but `colscales`.
+// function owns for the duration of the call); used by nvfp4a_b200_gemm_ex_static.  Every argument is validated first (a failed
+// call launches nothing); the scales kernel then runs before the GEMM and writes nothing but `colscales`.
 nvfp4a_status gemm_ex_with_scales(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb,
                                   float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias,
                                   const nvfp4a_epilogue *ex, float *colscales, cudaStream_t stream) {
   EpilogueEx x;
   if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, beta, ldd, &x)) return st;
-  if ((x.mask & kExNorm) && colscales && n > kGemvMaxN && B && B->dtype == NVFP4A_BF16 && forced_route() != 1) {
+  if ((x.mask & kExNorm) && colscales && n > kGemvMaxN && B && B->dtype == NVFP4A_BF16 && forced_route() != 1 && m > 0) {
+    if (nvfp4a_status st = gemm_run(fn, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, x, stream, true)) return st;
     if (nvfp4a_status st = cuda_fail(launch_norm_scales(x, n, colscales, stream), fn)) return st;
     x.colscales = colscales;
   }
@@ -476,6 +481,19 @@ extern "C" nvfp4a_status nvfp4a_gemv_tc_ex(int m, int n, int k, float alpha, con
   return gemv_tc_run("nvfp4a_gemv_tc_ex", m, n, k, alpha, A, B, ldb, beta, C, ldc, D, ldd, bias, x, stream);
 }
 
+// What the fused all-gather needs of D inside the rank's buffer: the push moves 16-byte vectors (GEMV) or TMA boxes (GEMM), so D's
+// base, its column pitch and a shard row must all be multiples of 16 bytes; checked before anything is launched.
+static nvfp4a_status check_tp_layout(const char *fn, const nvfp4a_tensor *D, int ldd, int m, bool swiglu, const unsigned char *local_base, int world) {
+  if (world <= 1 || !D || !D->data) return NVFP4A_OK;
+  if (!dense_t(D)) return NVFP4A_OK;   // (rejected with its own message later)
+  const long long esz = dense_bytes(D->dtype), drows = swiglu ? m / 2 : m;
+  if ((const unsigned char *)D->data < local_base) return fail(NVFP4A_INVALID_VALUE, "%s: D must lie inside buffers[rank]", fn);
+  if (((uintptr_t)D->data & 15) || ((long long)ldd * esz) % 16 || (drows * esz) % 16)
+    return fail(NVFP4A_INVALID_VALUE, "%s: with world > 1, D's base (%p), its column pitch (%lld bytes) and a shard row (%lld bytes) must be multiples of 16 bytes",
+                fn, D->data, (long long)ldd * esz, drows * esz);
+  return NVFP4A_OK;
+}
+
 // nvfp4a_gemv_tc(_ex) of one rank of a tensor-parallel group with the all-gather fused in: D (inside buffers[rank]) is also
 // stored at the same place of every peer's buffer and the ranks meet in a barrier before the stream goes on.
 extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
@@ -495,10 +513,10 @@ extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha
     tp.delta[p] = (long long)((unsigned char *)buffers[p] - tp.local_base);
     tp.flags[p] = (unsigned long long *)flags[p];
   }
-  if (D && D->data && (unsigned char *)D->data < tp.local_base) return fail(NVFP4A_INVALID_VALUE, "%s: D must lie inside buffers[rank]", fn);
   EpilogueEx x;
   if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
   if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemv_tc_ex and nvfp4a_b200_tp_gather", fn);
+  if (nvfp4a_status st = check_tp_layout(fn, D, ldd, m, (x.mask & kExSwiglu) != 0, tp.local_base, world)) return st;
   return gemv_tc_run(fn, m, n, k, alpha, A, B, ldb, 0.f, nullptr, 0, D, ldd, bias, x, stream, world > 1 ? &tp : nullptr);
 }
 
@@ -521,9 +539,9 @@ extern "C" nvfp4a_status nvfp4a_b200_gemm_tc_tp(int m, int n, int k, float alpha
     tp.delta[p] = (long long)((unsigned char *)buffers[p] - tp.local_base);
     tp.flags[p] = (unsigned long long *)flags[p];
   }
-  if (D && D->data && (unsigned char *)D->data < tp.local_base) return fail(NVFP4A_INVALID_VALUE, "%s: D must lie inside buffers[rank]", fn);
   EpilogueEx x;
   if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
   if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemm_tc_ex and nvfp4a_b200_tp_gather", fn);
+  if (nvfp4a_status st = check_tp_layout(fn, D, ldd, m, (x.mask & kExSwiglu) != 0, tp.local_base, world)) return st;
   return gemm_tc_run(fn, m, n, k, alpha, A, B, 0.f, nullptr, 0, D, ldd, bias, workspace, x, stream, world > 1 ? &tp : nullptr);
 }

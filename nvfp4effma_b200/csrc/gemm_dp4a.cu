@@ -10,6 +10,7 @@
 // Tile 128 rows x 128 tokens, 64 values of k per step; 256 threads, each 8 x 8 outputs.  Weights are expanded to int8
 // (2 * e2m1) while they are staged in shared memory; the next step's global loads are in flight during the current step's
 // arithmetic.  The finished tile goes through shared memory to the plain / extended epilogue, one thread per weight row.
+#include <atomic>
 #include "operands.cuh"
 
 namespace nvb {
@@ -186,7 +187,7 @@ bool gemm_dp4a_supports(const GemmArgs &g) {
 }
 
 cudaError_t launch_gemm_dp4a(const GemmArgs &g, cudaStream_t s) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {

@@ -17,6 +17,7 @@
 //               A tile.  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for E4M3, 16 for
 //               UE5M3 scales) and the accumulator is multiplied by 2^Z in the epilogue.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
+#include <atomic>
 #include "operands.cuh"
 #include "sm100.cuh"
 
@@ -32,6 +33,7 @@ struct W4A16Args {
   Epilogue e;
   EpilogueEx x;
   unsigned *status;
+  unsigned tag;  // this launch's tag in the status word
   int d_tma;     // the output goes through the staging tile and TMA stores (SwiGLU: 64 output rows per tile)
 };
 
@@ -89,7 +91,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
   uint32_t *lut = (uint32_t *)(staging + C::kStagingBytes);      // scale code -> BF16 pair (sa * 2^(126 - Z), twice)
   float *colscale = (float *)(lut + 256);                           // RMSNorm column scales of the current token tile
   uint64_t *bars = (uint64_t *)(colscale + BN);
-  uint64_t *full_a = bars, *full_b = bars + kStages, *empty = bars + 2 * kStages, *tmem_full = bars + 3 * kStages, *tmem_empty = tmem_full + 2;
+  uint64_t *full = bars, *empty = bars + kStages, *tmem_full = bars + 2 * kStages, *tmem_empty = tmem_full + 2;
   uint32_t *tmem_slot = (uint32_t *)(tmem_empty + 2);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
@@ -101,7 +103,8 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
   unsigned *const status_word = g.status;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kConvWarps / 2); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    // one `full` barrier per stage: the four conversion warps of the stage's group and the producer's expect-tx arrival
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kConvWarps / 2 + 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -118,51 +121,50 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+  const unsigned tag = g.tag;
+  auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+    if (mbar_try(bar, parity)) return true;   // the common case: no flag read, no clock read
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
-    atomicCAS(status_word, 0u, code);
+    atomicCAS(status_word, 0u, code | tag);
     return false;
   };
 
   if (warp == 0) {
     // ---------------- producer: activation tiles ----------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const int tn = t / tiles_m;
-        for (int ks = 0; ks < nk; ++ks, ++it) {
-          const int s = it % kStages;
-          if (!wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty)) goto done;
-          mbar_arrive_expect_tx(&full_b[s], C::kBBytes);
-          tma_load_2d(smem + (size_t)s * C::kStageBytes + C::kABytes, &tmap_b, ks * 128, tn * BN, &full_b[s]);
-        }
+    // (the whole warp runs the loop, one elected lane issues: see tma_load_2d_elect)
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const int tn = t / tiles_m;
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        const int s = it % kStages;
+        if (!__all_sync(0xFFFFFFFFu, wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty))) goto done;
+        mbar_arrive_expect_tx_elect(&full[s], C::kBBytes);
+        tma_load_2d_elect(smem_u32(smem + (size_t)s * C::kStageBytes + C::kABytes), &tmap_b, ks * 128, tn * BN, smem_u32(&full[s]));
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_f16(128, BN, 1);
-      uint32_t it = 0, tile_i = 0;
-      for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
-        const int acc = tile_i & 1;
-        if (!wait(&tmem_empty[acc], ((tile_i >> 1) & 1) ^ 1, kStWaitTmemEmpty)) goto done;
+    // The whole warp runs the loop and one elected lane issues a stage's four MMAs (K = 16 each: 32 bytes along the row) and the
+    // commit in one statement; from inside a one-lane branch every tcgen05.mma costs ~150 cycles, more than the 128 the tensor
+    // pipe needs for 128 x 256 x 16.
+    constexpr uint32_t idesc = idesc_f16(128, BN, 1);
+    const uint64_t da0 = smem_desc_sw128(smem_u32(smem));
+    uint32_t it = 0, tile_i = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++tile_i) {
+      const int acc = tile_i & 1;
+      if (!__all_sync(0xFFFFFFFFu, wait(&tmem_empty[acc], ((tile_i >> 1) & 1) ^ 1, kStWaitTmemEmpty))) goto done;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        const int s = it % kStages;
+        if (!__all_sync(0xFFFFFFFFu, wait(&full[s], (it / kStages) & 1, kStWaitFullA))) goto done;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int ks = 0; ks < nk; ++ks, ++it) {
-          const int s = it % kStages;
-          if (!wait(&full_a[s], (it / kStages) & 1, kStWaitFullA)) goto done;
-          if (!wait(&full_b[s], (it / kStages) & 1, kStWaitFullB)) goto done;
-          tc_fence_after();
-          const uint32_t sA = smem_u32(smem + (size_t)s * C::kStageBytes);
-          const uint64_t da = smem_desc_sw128(sA), db = smem_desc_sw128(sA + C::kABytes);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) mma_f16(d_tmem, da + 2 * j, db + 2 * j, idesc, (ks | j) != 0);  // K = 16 per instruction: 32 bytes along the row
-          tc_commit(&empty[s]);
-        }
-        tc_commit(&tmem_full[acc]);
+        const uint64_t da = da0 + (uint32_t)s * (uint32_t)(C::kStageBytes >> 4), db = da + (C::kABytes >> 4);
+        mma4_f16_commit_elect(d_tmem, da, db, idesc, (uint32_t)(ks != 0), &empty[s]);
       }
+      tc_commit_elect(&tmem_full[acc]);
     }
   } else if (warp < 6) {
     // ---------------- epilogue ----------------
@@ -442,12 +444,13 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full_a[s]);
+        if (lane == 0) mbar_arrive(&full[s]);
         cur = nxt;
       }
     }
   }
 done:
+  __syncwarp();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -459,7 +462,7 @@ done:
 template <int BN>
 cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const PeerMaps &pm, const W4A16Args &a, cudaStream_t s) {
   using C = Cfg<BN>;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
@@ -496,6 +499,7 @@ cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s) {
   a.A = g.A;
   a.e = g.e; a.x = g.x;
   a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
   const int bn = g.n > 128 ? 256 : 128;
   CUtensorMap tb, td;
   if (!make_tmap_bytes(&tb, g.B.data, (uint64_t)g.k * 2, (uint64_t)g.n, (uint64_t)g.B.ld * 2, bn)) return cudaErrorInvalidValue;

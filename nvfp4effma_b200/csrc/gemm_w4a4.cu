@@ -24,6 +24,7 @@
 // accumulation bound the reference applies to its own tensor-core path (tests/test_util.h:292-302 there).
 // Block scales are consumed as UNSIGNED E4M3: codes with the sign bit set are outside this kernel's contract (the
 // reference's quantizer never emits them).
+#include <atomic>
 #include "operands.cuh"
 #include "sm100.cuh"
 
@@ -40,6 +41,7 @@ struct W4A4Args {
   int ktiles;                  // image: 256-k tiles per row tile
   Epilogue e;
   unsigned *status;
+  unsigned tag;                // this launch's tag in the status word
   int transposed;              // the operands were swapped: TMEM lanes are tokens (B of the call), columns are A's rows
   int d_tma;                   // D is stored by TMA from a shared-memory staging tile (needs 16-byte aligned D and column stride)
 };
@@ -128,13 +130,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // Kernel parameters are copied into registers here: a parameter struct whose members are reached through references
   // is re-read from parameter memory (hundreds of cycles) at every use inside the loops below.
   unsigned *const status_word = g.status;
+  const unsigned tag = g.tag;
   // wait that also ends when another role has raised the abort flag
-  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+  auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
     if (mbar_try(bar, parity)) return true;   // the common case: no flag read, no clock read
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
-    atomicCAS(status_word, 0u, code);
+    atomicCAS(status_word, 0u, code | tag);
     return false;
   };
 
@@ -612,6 +615,14 @@ done:
 
 // ---- host ------------------------------------------------------------------------------------------------------------------
 static __device__ unsigned int g_kernel_status;
+static std::atomic<unsigned> g_launch_seq{0};
+static thread_local unsigned g_last_launch = 0;
+unsigned next_launch_tag() {
+  g_last_launch = (g_launch_seq.fetch_add(1) + 1) & 0xFFFFFu;
+  return g_last_launch << 12;
+}
+static std::atomic<long long> g_tp_wait_limit{2000000000ll};
+long long tp_wait_limit() { return g_tp_wait_limit.load(); }
 unsigned int *kernel_status_device_ptr() {
   unsigned int *p = nullptr;
   cudaGetSymbolAddress((void **)&p, g_kernel_status);
@@ -680,7 +691,7 @@ template <int BN, int ACC, int STAGES, bool PAIR>
 static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tsa, const CUtensorMap &tsb, const CUtensorMap &td,
                               const W4A4Args &a, cudaStream_t s) {
   using Cfg = W4A4Cfg<BN, ACC, STAGES, PAIR>;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
@@ -708,26 +719,29 @@ static cudaError_t launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, cons
   return cudaGetLastError();
 }
 
-static int g_w4a4_bn = 0;  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
+static std::atomic<int> g_w4a4_bn{0};  // 0 = choose by n; tests and tuning may pin 128 or 256 (nvfp4a_b200_set_tile_n)
 void set_w4a4_tile_n(int bn) { g_w4a4_bn = bn; }
 // -1 = automatic; 0 / 1 pin the CTA-pair kernel off / on where it applies (nvfp4a_b200_set_pair).  Automatic currently means
 // off: at 4096^3 the pair form takes 64 us against 58 us (its producer warp, with two rings to feed, is the slower issuer).
-static int g_w4a4_pair = -1;
+static std::atomic<int> g_w4a4_pair{-1};
 void set_w4a4_pair(int mode) { g_w4a4_pair = mode; }
 
-static int g_w4a4_swap = -1;  // 1: tokens on the MMA's M side whenever D can be stored that way; -1: unless that costs a round of tiles; 0: never
+static std::atomic<int> g_w4a4_swap{-1};  // 1: tokens on the MMA's M side whenever D can be stored that way; -1: unless that costs a round of tiles; 0: never
 void set_w4a4_swap(int mode) { g_w4a4_swap = mode; }
 
 bool gemm_w4a4_pair_applies(const GemmArgs &g, bool force);
 cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s);
 
 cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
-  if (g_w4a4_pair != 0 && g_w4a4_swap != 0 && !g_w4a4_bn && gemm_w4a4_pair_applies(g, g_w4a4_pair == 1)) return launch_gemm_w4a4_pair(g, s);
+  const int pin_bn = g_w4a4_bn.load(), pin_pair = g_w4a4_pair.load(), pin_swap = g_w4a4_swap.load();
+  // large problems with a TMA-storable 16-bit D and tiled scales: the CTA-pair kernel (gemm_w4a4_pair.cu)
+  if (pin_pair != 0 && pin_swap != 0 && !pin_bn && gemm_w4a4_pair_applies(g, pin_pair == 1)) return launch_gemm_w4a4_pair(g, s);
   W4A4Args a;
   memset(&a, 0, sizeof a);
   a.k = g.k;
   a.e = g.e;
   a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
   // D through TMA when its base and column stride are 16-byte aligned; otherwise plain stores from registers
   const int esz = dense_bytes(g.e.d_dtype);
@@ -736,23 +750,23 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   // lane's accumulator columns are consecutive elements of D in memory.  Needs a 16-bit D that TMA can store.
   // Automatic: swapped unless the other orientation needs fewer rounds of tiles over the SMs.
   auto rounds = [&](int lanes_rows, int col_rows) {
-    const int bn_ = g_w4a4_bn ? g_w4a4_bn : (col_rows > 128 ? 256 : 128);
+    const int bn_ = pin_bn ? pin_bn : (col_rows > 128 ? 256 : 128);
     const long long tiles = (long long)((lanes_rows + 127) / 128) * ((col_rows + bn_ - 1) / bn_);
     return (tiles + device_sms() - 1) / device_sms() * bn_;   // rounds weighted by the tile's width
   };
-  const bool swap = g_w4a4_swap != 0 && esz == 2 && d_tma_ok && (g_w4a4_swap == 1 || rounds(g.n, g.m) <= rounds(g.m, g.n));
+  const bool swap = pin_swap != 0 && esz == 2 && d_tma_ok && (pin_swap == 1 || rounds(g.n, g.m) <= rounds(g.m, g.n));
   a.transposed = swap;
   const Fp4Operand &X = swap ? g.B.q : g.A, &Y = swap ? g.A : g.B.q;   // X: rows on lanes (128 per tile); Y: rows on columns (BN per tile)
   const int xm = swap ? g.n : g.m, yn = swap ? g.m : g.n;
   a.m = xm; a.n = yn;
-  const int bn = g_w4a4_bn ? g_w4a4_bn : (yn > 128 ? 256 : 128);
+  const int bn = pin_bn ? pin_bn : (yn > 128 ? 256 : 128);
   CUtensorMap ta, tb, tsa, tsb;
   memset(&tsa, 0, sizeof tsa);
   memset(&tsb, 0, sizeof tsb);
   a.a_image = X.image; a.b_image = Y.image;
   auto tiled_ok = [](const Fp4Operand &o) { return o.sld < 0 && ((uintptr_t)o.sc & 15) == 0; };
   // the CTA-pair kernel: 256 x 256 tiles, scales in aligned tiles (or images) on both sides, more than one row tile
-  const bool pair = bn == 256 && g_w4a4_pair == 1 && xm > 128 && (X.image || tiled_ok(X)) && (Y.image || tiled_ok(Y));
+  const bool pair = false;   // pairs run in gemm_w4a4_pair.cu; this kernel's own pair form is no longer instantiated
   if (X.image) {
     const uint64_t tiles = (uint64_t)((xm + 127) / 128) * a.ktiles;
     if (!make_tmap_bytes(&ta, X.data, 128, 128, 128, 128, tiles, kImgTileBytes)) return cudaErrorInvalidValue;
@@ -783,7 +797,6 @@ cudaError_t launch_gemm_w4a4(const GemmArgs &g, cudaStream_t s) {
   } else {
     a.d_tma = d_tma_ok && make_tmap_dense(&td, g.e.d, esz, (uint64_t)g.m, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, 128, esz == 2 ? 16 : 8);
   }
-  if (pair) return launch_cfg<256, 1, 5, true>(ta, tb, tsa, tsb, td, a, s);
   if (bn == 256) return launch_cfg<256, 1, 4, false>(ta, tb, tsa, tsb, td, a, s);
   return launch_cfg<128, 2, 6, false>(ta, tb, tsa, tsb, td, a, s);
 }
@@ -799,6 +812,14 @@ extern "C" nvfp4a_status nvfp4a_b200_kernel_status(unsigned int *status, int res
   cudaError_t e = cudaMemcpy(status, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && reset) e = cudaMemset(p, 0, sizeof(unsigned int));
   return cuda_fail(e, "nvfp4a_b200_kernel_status");
+}
+
+extern "C" unsigned int nvfp4a_b200_last_launch(void) { return nvb::g_last_launch; }
+
+extern "C" int nvfp4a_b200_set_wait_limit(long long cycles) {
+  if (cycles < 1000) return -1;
+  nvb::g_tp_wait_limit = cycles;
+  return 0;
 }
 
 extern "C" int nvfp4a_b200_set_pair(int mode) {

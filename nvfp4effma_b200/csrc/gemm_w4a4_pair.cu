@@ -53,6 +53,7 @@ struct PairArgs {
   int d_dtype;
   float *amax;
   unsigned *status;
+  unsigned tag;              // this launch's tag in the status word
 };
 
 constexpr int kPairThreads = 512, kPairStages = 5, kPairSlots = 4;
@@ -121,12 +122,13 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+  const unsigned tag = g.tag;
+  auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
     if (mbar_try(bar, parity)) return true;   // the common case: no flag read, no clock read
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
-    atomicCAS(status_word, 0u, code);
+    atomicCAS(status_word, 0u, code | tag);
     return false;
   };
 
@@ -371,6 +373,7 @@ cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s) {
   a.d_dtype = g.e.d_dtype;
   a.amax = g.e.amax;
   a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
   CUtensorMap tx, ty, ty64, tsx, tsy, td;
   auto nibble_map = [&](const Fp4Operand &o, int rows, int box_rows, CUtensorMap *tn) {
     if (o.image) return make_tmap_bytes(tn, o.data, 128, 128, 128, box_rows, (uint64_t)((rows + 127) / 128) * a.ktiles, kImgTileBytes);

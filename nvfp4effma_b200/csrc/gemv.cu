@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
       }
       __threadfence_system();
       __syncthreads();
-      tp_barrier_cta(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status);
+      tp_barrier_cta(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status, g.tp.tag, g.tp.wait_cycles);
     }
   }
 }
@@ -236,6 +236,8 @@ cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
   a.x = (const uint16_t *)g.B.data; a.ldx = g.B.ld;
   a.e = g.e; a.ex = g.x; a.tp = g.tp;
   a.tp.status = kernel_status_device_ptr();
+  a.tp.tag = next_launch_tag();
+  a.tp.wait_cycles = tp_wait_limit();
   const int grid = (g.m + 15) / 16;
   if (a.A.image) gemv_kernel<2><<<grid, kGemvWarps * 32, 0, s>>>(a);
   else if (a.A.sld < 0) gemv_kernel<1><<<grid, kGemvWarps * 32, 0, s>>>(a);

@@ -9,6 +9,7 @@
 // CTA in shared memory.  A warp takes a row at a time: lane l reads the 16-byte weight chunks l, l + 32, ... of the row
 // (two blocks each), so a warp load covers 512 contiguous bytes; the n <= 8 dot products of a chunk reuse its decoded
 // weights.  The lanes' sums are added by an xor butterfly; the CTA's 32 x n results then run the plain or extended epilogue.
+#include <atomic>
 #include "operands.cuh"
 
 namespace nvb {
@@ -187,7 +188,7 @@ cudaError_t launch_gemv_blocked(const GemmArgs &g, cudaStream_t s) {
   GemvQArgs a;
   a.m = g.m; a.n = g.n; a.k = g.k;
   a.A = g.A; a.B = g.B; a.e = g.e; a.ex = g.x;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {

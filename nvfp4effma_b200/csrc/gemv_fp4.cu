@@ -26,6 +26,7 @@
 // Semantics: FP32 accumulation in the tensor cores' order, within the FP32 accumulation bound of the exact definition
 // (reference include/nvfp4effma.h:82-92 there), as the reference's own tensor-core GEMV (src/tensors/gemv_tc.cuh there).
 // Block scales are consumed as unsigned E4M3.
+#include <atomic>
 #include "operands.cuh"
 #include "sm100.cuh"
 
@@ -45,6 +46,7 @@ struct GemvFp4Args {
   Epilogue e;
   EpilogueEx ex;
   unsigned *status;
+  unsigned tag;        // this launch's tag in the status word
   int stages;          // ring depth (2..6), chosen by the host from the shared memory left beside the pieces
   int piece_bytes;     // shared memory of the activation pieces: chunks per CTA x piece rows x 128
 };
@@ -141,11 +143,12 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto wait = [abort_flag, status_word](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+  const unsigned tag = g.tag;
+  auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
-    atomicCAS(status_word, 0u, code);
+    atomicCAS(status_word, 0u, code | tag);
     return false;
   };
 
@@ -392,7 +395,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
 }  // namespace
 
-static int g_gemv_splits = 0;  // 0 = automatic
+static std::atomic<int> g_gemv_splits{0};  // 0 = automatic
 void set_gemv_fp4_splits(int s) { g_gemv_splits = s; }
 
 // splits: power of two, at most 8 and nk; every CTA's k range is at most kMaxChunks chunks (its pieces' shared memory).
@@ -404,8 +407,7 @@ static int choose_splits(int m, int k) {
   const int need = (nk + kMaxChunks - 1) / kMaxChunks;
   int s = 1;
   while (s < need) s *= 2;
-  if (g_gemv_splits) {
-    const int f = g_gemv_splits;
+  if (const int f = g_gemv_splits.load()) {
     return (f >= s && f <= 8 && f <= nk && !(f & (f - 1))) ? f : 0;
   }
   if (s > 4 || s > nk) return 0;
@@ -429,6 +431,7 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   a.x = (const uint16_t *)g.B.data; a.ldx = g.B.ld;
   a.e = g.e; a.ex = g.x;
   a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
   a.ktiles = (g.k + kImgK - 1) / kImgK;
   a.a_image = g.A.image;
   CUtensorMap ta, ts;
@@ -445,7 +448,7 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   const int splits = choose_splits(g.m, g.k);
   if (splits <= 0) return cudaErrorInvalidValue;
   void (*kern)(CUtensorMap, CUtensorMap, GemvFp4Args) = g.n == 1 ? gemv_fp4_kernel<1> : gemv_fp4_kernel<2>;
-  static bool attr_set[64][2] = {};
+  static std::atomic<bool> attr_set[64][2];   // zero-initialised; set once per device and kernel
   int dev = 0;
   cudaGetDevice(&dev);
   const int nk = g.k >> 8, nloc_max = (nk + splits - 1) / splits;

@@ -302,6 +302,22 @@ __device__ __forceinline__ void mma4_commit_elect(uint32_t d_tmem, uint64_t a_de
                                                   uint32_t sfb_step, uint32_t accumulate, uint64_t *bar) {
   NVB_MMA4_BODY("1", "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%19];");
 }
+// The same for kind::f16 (K = 16 per instruction: four MMAs cover the 64 values of k of a 128-byte-row stage).
+__device__ __forceinline__ void mma4_f16_commit_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint64_t *bar) {
+  asm volatile("{\n\t.reg .pred p, q, t;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 t, %3, %3;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %3, t;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %3, t;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %10, %3, t;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_desc + 2), "l"(b_desc + 2), "l"(a_desc + 4), "l"(b_desc + 4),
+                 "l"(a_desc + 6), "l"(b_desc + 6), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar_addr) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_addr) : "memory");
+}
 __device__ __forceinline__ void tc_commit_elect(uint64_t *bar) {
   asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
                "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
@@ -331,6 +347,12 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
 // Block scales stored as 512-byte tiles (the swizzled layout), as a tensor of 8-byte words: `rows` rows of row_bytes bytes `stride`
 // bytes apart; a box is 2 KiB of one row (the four tiles of 256 values of k), zero-filled past the end of the row.
 bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride);
+// Tag of a launch for the status word: (library-wide launch sequence number mod 2^20) << 12.  A kernel that gives up a wait records
+// code | tag, so the word names the kind of wait (low 12 bits: 0x1xx W4A4 GEMM, 0x2xx FP4 GEMV, 0x3xx W4A16 GEMM, 0x4xx tensor-parallel
+// barrier, 0x5xx ceiling measurement) and the launch (nvfp4a_b200_last_launch gives the calling thread's latest sequence number).
+unsigned next_launch_tag();
+// SM clock cycles a tensor-parallel barrier waits for its peers before it gives up (nvfp4a_b200_set_wait_limit; default 2e9, about a second)
+long long tp_wait_limit();
 // kernel status word: 0 = healthy; kernels that gave up a wait write a non-zero code (see nvfp4a_b200_kernel_status)
 unsigned int *kernel_status_device_ptr();
 

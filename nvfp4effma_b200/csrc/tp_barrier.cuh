@@ -16,6 +16,8 @@ struct TpPush {
   long long delta[kMaxRanks];
   unsigned long long *flags[kMaxRanks];
   unsigned *status;
+  unsigned tag;                // this launch's tag in the status word
+  long long wait_cycles;       // SM clock cycles the barrier waits for its peers
   unsigned char *local_base;   // host side: this rank's buffer (peer p's is local_base + delta[p])
 };
 
@@ -29,9 +31,11 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 }
 
 // Called by all threads of ONE CTA per rank after the rank's stores to its peers are complete (and fenced): bumps the
-// rank's epoch, writes it into slot `rank` of every rank's flag array and waits (bounded: about a second of SM clock, then
-// code 0x401 in *status) until every slot of its own array has reached the epoch.
-__device__ __forceinline__ void tp_barrier_cta(unsigned long long *const *flags, int world, int rank, unsigned *status) {
+// rank's epoch, writes it into slot `rank` of every rank's flag array and waits until every slot of its own array has reached the
+// epoch -- bounded: after wait_cycles of SM clock (by default about a second) it records code 0x401 in *status and returns.  A peer
+// that is more than that behind (first-call module loads, a stalled host) therefore shows up as 0x401, and the buffers are then
+// incomplete: callers poll the status word at a convenient point (nvfp4a_b200_kernel_status).
+__device__ __forceinline__ void tp_barrier_cta(unsigned long long *const *flags, int world, int rank, unsigned *status, unsigned tag, long long wait_cycles) {
   __shared__ unsigned long long epoch_s;
   unsigned long long *mine = flags[rank];
   if (threadIdx.x == 0) {
@@ -46,8 +50,8 @@ __device__ __forceinline__ void tp_barrier_cta(unsigned long long *const *flags,
     st_release_sys(flags[p] + rank, epoch);
     const long long start = clock64();
     while (ld_acquire_sys(mine + p) < epoch) {
-      if (clock64() - start > 2000000000ll) {
-        atomicCAS(status, 0u, 0x401u);
+      if (clock64() - start > wait_cycles) {
+        atomicCAS(status, 0u, 0x401u | tag);
         break;
       }
     }

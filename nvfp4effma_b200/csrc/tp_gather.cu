@@ -22,6 +22,8 @@ struct TpGatherArgs {
   int rows;                                // T
   long long row_pitch_bytes, col_offset_bytes, shard_bytes;  // this rank's columns: [col_offset, col_offset + shard_bytes) of every row
   unsigned *status;
+  unsigned tag;
+  long long wait_cycles;
   int copy, barrier;
 };
 
@@ -41,7 +43,7 @@ __global__ void __launch_bounds__(1024) tp_gather_kernel(const TpGatherArgs a) {
   }
   if (!a.barrier) return;
   __syncthreads();
-  tp_barrier_cta(a.flags, a.world, a.rank, a.status);
+  tp_barrier_cta(a.flags, a.world, a.rank, a.status, a.tag, a.wait_cycles);
 }
 
 }  // namespace nvb
@@ -73,6 +75,8 @@ extern "C" nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const
   a.world = world; a.rank = rank; a.rows = rows;
   a.row_pitch_bytes = row_pitch_bytes; a.col_offset_bytes = col_offset_bytes; a.shard_bytes = shard_bytes;
   a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
+  a.wait_cycles = tp_wait_limit();
   const long long bytes = (long long)rows * shard_bytes * (world - 1);
   if (world == 1) return NVFP4A_OK;
   if (bytes <= (1 << 20)) {   // one CTA copies and joins the barrier

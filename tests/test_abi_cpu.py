@@ -95,3 +95,30 @@ def test_quantize_and_epilogue_argument_checks():
     assert L.check(L.OK) is None
     with pytest.raises(ValueError):
         L.check(L.lib.nvfp4a_swizzle_scales(None, None, 4, 16, 64, 1, None))
+
+
+def test_tensor_parallel_entries_reject_layouts_the_push_cannot_move():
+    """The fused all-gather moves 16-byte vectors / TMA boxes: with world > 1, D's base, its column pitch and a shard row must be
+    multiples of 16 bytes, and D must lie inside the rank's buffer -- INVALID_VALUE before any device is touched."""
+    A, B = _fake(L.NVFP4, with_scales=False), _fake(L.BF16, with_scales=False, addr=0x2000)
+    bufs = (ctypes.c_void_p * 2)(0x100000, 0x200000)
+    flags = (ctypes.c_void_p * 2)(0x300000, 0x300100)
+    ws = ctypes.c_void_p(0x400000)
+
+    def gemv(d_addr, m, ldd, world=2):
+        D = L.Tensor(d_addr, L.BF16, None, 0, None, None, 0, 0)
+        return L.lib.nvfp4a_b200_gemv_tc_tp(m, 1, 256, 1.0, A, B, 256, D, ldd, None, None, bufs, flags, world, 0, None)
+
+    def gemm(d_addr, m, ldd, world=2):
+        D = L.Tensor(d_addr, L.BF16, None, 0, None, None, 0, 0)
+        return L.lib.nvfp4a_b200_gemm_tc_tp(m, 64, 256, 1.0, A, B, D, ldd, None, None, ws, bufs, flags, world, 0, None)
+
+    for call in (gemv, gemm):
+        assert call(0x100002, 128, 256) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # base
+        assert call(0x100000, 128, 260) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # pitch: 520 bytes
+        assert call(0x100000, 132, 256) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # shard row: 264 bytes
+        assert call(0x0FFFF0, 128, 256) == L.INVALID_VALUE and b"inside" in L.lib.nvfp4a_last_error()       # below the buffer
+    bad_flags = (ctypes.c_void_p * 2)(0x300000, 0x300104)
+    D = L.Tensor(0x100000, L.BF16, None, 0, None, None, 0, 0)
+    assert L.lib.nvfp4a_b200_gemv_tc_tp(128, 1, 256, 1.0, A, B, 256, D, 256, None, None, bufs, bad_flags, 2, 0, None) == L.INVALID_VALUE
+    assert L.lib.nvfp4a_b200_set_wait_limit(10) == -1 and L.lib.nvfp4a_b200_set_wait_limit(2000000000) == 0

@@ -118,3 +118,71 @@ def test_extended_epilogue(tc, bt):
             glu = bool(mask & 2)
             run_case(m, n, k, bt, L.FP32 if v % 2 else L.BF16, mask, (not glu) and v % 3 == 1, (not glu) and v % 4 == 2, tc)
             v += 1
+
+
+@pytest.mark.parametrize("which", ["gate_up", "down"])
+def test_llama_mlp_gemms_at_full_size_on_a_token_slab(which):
+    """The fused transformer-MLP calls at their full size, 2048 tokens, through nvfp4a_gemm_tc_ex on images: gate / up
+    28672 x 4096 with the deferred RMSNorm column scale, bias, SwiGLU and amax, and down 4096 x 14336 with bias, the second
+    output times w2 and the sums of squares.  The whole problem runs (224 x 8 tiles of weight rows and tokens, the column
+    scales of all 2048 tokens staged in the workspace); a slab of 64 tokens is checked the way the small cases are: the
+    accumulators of the same entry without the descriptor, the epilogue emulated on the host."""
+    glu = which == "gate_up"
+    m, n, k = (28672, 2048, 4096) if glu else (4096, 2048, 14336)
+    mask = 3 if glu else 4
+    rng = np.random.default_rng(31 + glu)
+    mo = m // 2 if glu else m
+    npart, lsq = 256, m // 16
+    A = rand_fp4(rng, m, k, glob=None)
+    dA = DevFp4(A)
+    dB = dev(rand_dense(rng, L.BF16, n * k, 2.0))
+    bias = rand_dense(rng, L.BF16, m, 4.0)
+    w2 = rand_dense(rng, L.FP32, m, 1.5)
+    parts = (rng.integers(1, 4096, npart * n) / 64.0).astype(np.float32)
+    d_bias, d_w2, d_parts = dev(bias), dev(w2), dev(parts)
+    dD, damax = torch.zeros(mo * n, dtype=torch.int16, device="cuda"), dev(np.zeros(1, np.float32))
+    d2 = torch.zeros(m * n if not glu else 1, dtype=torch.int16, device="cuda")
+    sq = torch.full((lsq * n,), -1.0, dtype=torch.float32, device="cuda")
+    ex = L.Epilogue()
+    if glu:
+        ex.norm_parts, ex.norm_nparts, ex.norm_ld, ex.norm_inv_n, ex.norm_eps, ex.swiglu = d_parts.data_ptr(), npart, npart, 1.0 / 4096.0, 1e-6, 1
+    else:
+        ex.d2, ex.d2_dtype, ex.ldd2, ex.w2, ex.w2_dtype, ex.sq, ex.ld_sq = d2.data_ptr(), L.BF16, m, d_w2.data_ptr(), L.FP32, sq.data_ptr(), lsq
+    tA = dA.tensor()
+    img = torch.zeros(L.lib.nvfp4a_tc_image_bytes(L.TC_A16, L.NVFP4, m, k), dtype=torch.uint8, device="cuda")
+    L.check(L.lib.nvfp4a_tc_image(L.TC_A16, ctypes.byref(tA), k, m, k, ptr(img), stream()))
+    tA.data = img.data_ptr()
+    tB, tbias = tensor(dB, L.BF16), tensor(d_bias, L.BF16)   # contiguous BF16 [n][k] is its own activation image
+    ws = torch.zeros(L.lib.nvfp4a_tc_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    alpha = 0.75
+    tD = tensor(dD, L.BF16, amax=damax)
+    L.check(L.lib.nvfp4a_gemm_tc_ex(m, n, k, alpha, ctypes.byref(tA), ctypes.byref(tB), 0.0, None, 0, ctypes.byref(tD), mo, ctypes.byref(tbias),
+                                    ctypes.byref(ex), ptr(ws), stream()))
+    assert L.lib.nvfp4a_b200_last_route() == 5
+    dR = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    tR = tensor(dR, L.FP32)
+    L.check(L.lib.nvfp4a_gemm_tc(m, n, k, 1.0, ctypes.byref(tA), ctypes.byref(tB), 0.0, None, 0, ctypes.byref(tR), m, None, ptr(ws), stream()))
+    torch.cuda.synchronize()
+    st = ctypes.c_uint(0)
+    L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 1))
+    assert st.value == 0 and not bool(ws.any())
+    for j0 in (0, 1977):   # the first tokens, and a slab that ends in the last, partly filled token tile
+        nj = min(64, n - j0)
+        acc = host(dR.view(n, m)[j0:j0 + nj])
+        r = O.epilogue_ex(m, nj, acc, alpha=alpha, bias=bias, bias_dtype=L.BF16, mask=mask, norm_parts=parts[j0 * npart:(j0 + nj) * npart] if glu else None,
+                          norm_nparts=npart, norm_ld=npart, norm_inv_n=1.0 / 4096.0, norm_eps=1e-6, D_dtype=L.BF16, ldd=mo, w2=None if glu else w2,
+                          w2_dtype=L.FP32, d2_dtype=L.BF16, ldd2=m, ld_sq=lsq)
+        got = host(dD.view(n, mo)[j0:j0 + nj]).view(np.uint16)
+        if glu:
+            y, h = O.to_f32(got, L.BF16).astype(np.float64), r["swiglu64"]
+            g = r["v"].reshape(nj, m // 16, 16)[:, :, :8].reshape(nj, mo).astype(np.float64)
+            assert np.all(np.abs(y - h) <= np.abs(h) * (4e-7 * (2.0 + np.abs(g)) + out_rel(L.BF16)) + 1e-30), (which, j0)
+        else:
+            assert np.array_equal(got, r["D"].reshape(nj, mo)), (which, j0)
+            assert np.array_equal(host(d2.view(n, m)[j0:j0 + nj]).view(np.uint16), r["d2"].reshape(nj, m)), (which, j0, "d2")
+            assert np.array_equal(host(sq.view(n, lsq)[j0:j0 + nj]).view(np.uint32), r["sq"].reshape(nj, lsq).view(np.uint32)), (which, j0, "sq")
+        # amax covers every output: at least the slab's largest value before rounding, and a value some output attains
+        vmax = float(np.abs(r["swiglu64"] if glu else r["v"].astype(np.float64)).max())
+        assert float(host(damax)[0]) >= vmax * (1 - 2.0 ** -7)
+    out = O.to_f32(host(dD).view(np.uint16), L.BF16)
+    assert abs(float(host(damax)[0]) - float(np.abs(out).max())) <= 2.0 ** -7 * float(host(damax)[0])

@@ -188,6 +188,24 @@ def test_cuda_core_route_is_bit_exact_in_the_tiled_order(exact_route):
     assert not bad, f"{len(bad)} cases differ: {bad[:5]}"
 
 
+def test_cuda_core_route_decodes_signed_block_scales_like_the_reference(exact_route):
+    """Block-scale codes with the sign bit set are legal E4M3 for the reference (src/nvfp4effma.cuh:56-60 there); the tensor cores
+    read scales as unsigned, so such tensors belong on the CUDA-core route, which must decode them exactly: D and amax equal the
+    oracle's bit for bit with negative scales on both operands, linear and swizzled."""
+    for i, (fa, fb) in enumerate([(0, 0), (SW, SW), (SW | AM, PR)]):
+        c = Case(200, 150, 256, L.NVFP4, OUTS[i % 3], -1, L.FP32, 1.25, 0.0, fa=fa, fb=fb)
+        h = build_case(c, 1500 + i)
+        rng = np.random.default_rng(1500 + i)
+        for t in (h["A"], h["B"]):
+            flip = rng.integers(0, 3, t.scales.size) == 0
+            t.scales[flip & (t.scales != 0)] |= 0x80
+        assert (h["A"].scales & 0x80).any() and (h["B"].scales & 0x80).any()
+        exp = oracle_case(c, h)
+        got, amax = run_gemm(c, h)
+        assert L.lib.nvfp4a_b200_last_route() == 1
+        assert np.array_equal(got, exp["D"]) and amax == exp["amax"], c
+
+
 def test_default_routes_within_the_accumulation_bound():
     """nvfp4a_gemm as routed by default (tcgen05 / GEMV / CUDA cores) against the float64 reference within the bound."""
     fmt_sizes = [(257, 129, 256), (200, 64, 128), (300, 300, 320), (150, 192, 256)]
@@ -466,3 +484,52 @@ def test_w4a8_dp4a_gemm_is_bit_exact_in_the_tiled_order():
             assert L.lib.nvfp4a_b200_last_route() == 7, c
             assert np.array_equal(got.view(np.uint8), exp["D"].view(np.uint8)), c
             assert amax == exp["amax"], c
+
+
+def test_gemm_dual_forward_dgrad_and_wgrad():
+    """nvfp4a_gemm_dual picks, per operand, the half whose blocks run along k (reference include/nvfp4effma.h:97-103):
+    forward Y = X W^T (trans 0, 0), dgrad dX = dY W (A = W with trans_a = 1: the column half of the [k][m] weight),
+    wgrad dW = dY^T X (both column halves).  Each must equal nvfp4a_gemm on the chosen halves bit for bit (the call only
+    forwards) and lie within the bound of the exact definition; a missing half is INVALID_VALUE."""
+    T, I, Ou = 256, 384, 192
+    rng = np.random.default_rng(77)
+
+    def dual(x):
+        rows, cols = x.shape
+        row = O.Fp4(rows, cols, flags=O.GLOBAL_AMAX, glob=0.0)
+        col = O.Fp4(cols, rows, flags=O.GLOBAL_AMAX, glob=0.0)
+        O.quantize(x, row, tile=16, compute_amax=True)
+        O.quantize(x, col, transposed=True, tile=16, compute_amax=True)
+        dr, dc = DevFp4(row), DevFp4(col)
+        return row, col, dr, dc, L.DualTensor(dr.tensor(), dc.tensor(), cols, rows)
+
+    W = dual(rng.standard_normal((Ou, I)).astype(np.float32))
+    X = dual(rng.standard_normal((T, I)).astype(np.float32))
+    dY = dual(rng.standard_normal((T, Ou)).astype(np.float32))
+    cases = [("forward", Ou, T, I, W, 0, X, 0), ("dgrad", I, T, Ou, W, 1, dY, 0), ("wgrad", I, Ou, T, X, 1, dY, 1)]
+    for name, m, n, k, A, ta, B, tb in cases:
+        hA, hB = A[1 if ta else 0], B[1 if tb else 0]
+        dA, dB = A[3 if ta else 2], B[3 if tb else 2]
+        outs = []
+        for use_dual in (True, False):
+            dD, damax = torch.zeros(m * n, dtype=torch.float32, device="cuda"), dev(np.zeros(1, np.float32))
+            tD = tensor(dD, L.FP32, amax=damax)
+            if use_dual:
+                st = L.lib.nvfp4a_gemm_dual(m, n, k, 1.0, ctypes.byref(A[4]), ta, ctypes.byref(B[4]), tb, 0.0, None, 0, ctypes.byref(tD), m, None, stream())
+            else:
+                tA, tB = dA.tensor(), dB.tensor()
+                st = L.lib.nvfp4a_gemm(m, n, k, 1.0, ctypes.byref(tA), hA.ld, ctypes.byref(tB), hB.ld, 0.0, None, 0, ctypes.byref(tD), m, None, stream())
+            assert st == 0, (name, L.last_error())
+            torch.cuda.synchronize()
+            outs.append((host(dD).copy(), float(host(damax)[0])))
+        assert np.array_equal(outs[0][0], outs[1][0]) and outs[0][1] == outs[1][1], name
+        exp = O.gemm(m, n, k, hA, hB, D_dtype=L.FP32, want_ref=True)
+        assert np.all(np.abs(outs[0][0].reshape(n, m).astype(np.float64) - exp["ref64"]) <= exp["bound"]), name
+    # 16 x 16 tiles: the column half of W decodes to the transpose of its row half, so dgrad really multiplies by W
+    assert np.array_equal(O.dequantize(W[1])[0], O.dequantize(W[0])[0].T)
+    lone = L.DualTensor(W[2].tensor(), L.Tensor(), I, 0)
+    dD = torch.zeros(I * T, dtype=torch.float32, device="cuda")
+    tD = tensor(dD, L.FP32)
+    st = L.lib.nvfp4a_gemm_dual(I, T, Ou, 1.0, ctypes.byref(lone), 1, ctypes.byref(dY[4]), 0, 0.0, None, 0, ctypes.byref(tD), I, None, stream())
+    assert st == L.INVALID_VALUE and "column" in L.last_error()
+    assert kernel_status() == 0

@@ -50,6 +50,42 @@ def test_decoder_stack_runs_decode_and_prefill():
         assert h.shape == (T, 256) and bool(torch.isfinite(h.float()).all()) and float(h.float().abs().max()) > 0
 
 
+def test_a_barrier_whose_peer_never_arrives_gives_up_and_reports_it():
+    """The bounded wait of the ranks' barrier, made to run out on ONE GPU without hanging anything: a group of two whose second
+    rank does not exist -- both "ranks'" buffers and flag arrays are ordinary local allocations and nobody ever posts the peer's
+    flag.  With the wait limit set to 2e5 cycles the kernel copies its shard, waits a tenth of a millisecond, records 0x401 with the
+    launch's sequence number in the status word and returns; the word reads back, resets, and a normal call then works."""
+    import ctypes
+    from nvfp4effma_b200 import _lib as L
+    rows, pitch, shard = 4, 512, 256
+    bufs = [torch.zeros(rows * pitch, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int64, device="cuda") for _ in range(2)]
+    bufs[0].view(rows, pitch)[:, :shard] = 7
+    st = ctypes.c_uint(0)
+    L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 1))
+    assert L.lib.nvfp4a_b200_set_wait_limit(200000) == 0
+    try:
+        pb = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+        pf = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        L.check(L.lib.nvfp4a_b200_tp_gather(pb, pf, 2, 0, rows, pitch, 0, shard, stream))
+        seq = L.lib.nvfp4a_b200_last_launch()
+        L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 1))        # synchronises: the kernel has returned
+        assert st.value & 0xFFF == 0x401 and st.value >> 12 == seq and seq > 0
+        assert bool((bufs[1].view(rows, pitch)[:, :shard] == 7).all())           # the shard did reach the "peer"
+        assert int(flags[1][0]) == 1 and int(flags[0][1]) == 0                   # our epoch was posted; the peer's never came
+        L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 0))
+        assert st.value == 0                                                     # the read above cleared the word
+    finally:
+        L.lib.nvfp4a_b200_set_wait_limit(2000000000)
+    import nvfp4effma_b200 as nf
+    w = nf.quantize(rand((128, 256), seed=7))
+    y = nf.linear(rand((16, 256), torch.bfloat16, seed=8), w, act="exact")
+    torch.cuda.synchronize()
+    L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 1))
+    assert st.value == 0 and bool(torch.isfinite(y.float()).all())
+
+
 RANK_SCRIPT = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["NVB_ROOT"])
