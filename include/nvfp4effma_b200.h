@@ -53,6 +53,10 @@ int nvfp4a_b200_set_wait_limit(long long cycles);
  * against come from this call. */
 nvfp4a_status nvfp4a_b200_mma_ceiling(int bn, int pair, int iters, int commit_each, unsigned long long *cycles, cudaStream_t stream);
 
+/* Test aid (no counterpart in the reference): 0 keeps nvfp4a_quantize_ex on its two-launch path (an amax kernel, then the encode kernel)
+ * where it would otherwise run the one-read cooperative kernel; 1 (default) restores the choice.  Results are identical bit for bit. */
+int nvfp4a_b200_set_quant_fused(int on);
+
 /* Pins the token-tile width of the W4A4 tcgen05 GEMM: 0 = by problem size, 128 (two accumulators in tensor memory, the
  * epilogue overlaps the next tile) or 256 (one accumulator, less shared-memory traffic per flop).  Tuning / test aid, no
  * counterpart in the reference.  Returns 0, or -1 for another value. */

@@ -84,6 +84,7 @@ _PROTOS = {
     "nvfp4a_b200_static_scratch_tokens": (_i, []),
     "nvfp4a_b200_mma_ceiling": (_i, [_i, _i, _i, _i, _v, _s]),
     "nvfp4a_b200_last_launch": (C.c_uint, []),
+    "nvfp4a_b200_set_quant_fused": (_i, [_i]),
     "nvfp4a_b200_set_wait_limit": (_i, [C.c_longlong]),
 }
 EXPORTS = tuple(_PROTOS)

@@ -7,6 +7,8 @@
 // sized in multiples of the SM count, and -- when the global amax has to be computed first -- the second pass walking
 // the matrix backwards so that it starts on the bytes the first pass left in the 126 MB L2.
 #include <stdio.h>
+#include <stdlib.h>
+#include <atomic>
 #include <type_traits>
 #include "common.cuh"
 
@@ -293,6 +295,230 @@ __global__ void __launch_bounds__(256, 3) quant_rows_kernel(const uint8_t *__res
   if (stat) warp_amax_commit(stat, mx);
 }
 
+// ---- one read: amax and encode in ONE cooperative kernel ------------------------------------------------------------------------
+// The global amax must be known before the first block scale, so the matrix is visited twice; this kernel keeps part of it on the
+// chip between the visits instead of paying a second full trip to HBM.  One CTA per SM (cooperative launch: all CTAs are resident,
+// so the grid barrier between the visits cannot starve), each with a contiguous share of the matrix in units of 64 blocks of one
+// row (2 KiB of 16-bit values), dealt to its 16 warps in turn.  Visit 1 takes the amax, four units per warp in flight.  A warp
+// keeps its last four units in registers and the six before them in shared memory (10 x 2 KiB x 16 warps = 320 KiB per SM, 47 MB
+// over the chip: a third of an 8192 x 8192 BF16 matrix).  After the barrier every step of a warp encodes one on-chip unit and one
+// unit read again from memory (in descending order), whose load was issued a step earlier.
+// Measured on 8192 x 8192: HBM traffic 159 MB against 287 MB for the two launches, the same 55 us -- the encode arithmetic (about
+// 170 instructions per block of 16) at 16 warps per SM, not memory, is what bounds the second visit.
+// Per-CTA maxima meet in a device array (no atomics on floats, no memset launch): every CTA reads all of them after the barrier.
+// The barrier's wait is bounded like every wait of this library; on expiry the status word gets 0x601 and the kernel goes on
+// (with whatever maxima have arrived) so that it always terminates.
+constexpr int kQfSmemBytes = 96 * 2048;            // 96 units of 2 KiB stay in shared memory per CTA
+constexpr int kQfMaxGrid = 1024;
+static __device__ unsigned long long g_qf_arrivals;   // arrivals of every launch so far on this device (each launch adds its grid size, which never changes)
+static __device__ float g_qf_max[kQfMaxGrid];      // per-CTA maxima of the current launch
+
+// max |x| of a block of 16-bit values taken on the packed words (bit patterns of non-negative BF16 / FP16 values order like the values)
+template <int T>
+__device__ __forceinline__ float packed_block_max(const PackedBlock<T> &a) {
+  uint32_t pm = 0;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) pm = packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(pm, a.w[q].x), a.w[q].y), a.w[q].z), a.w[q].w);
+  if (T == NVFP4A_BF16) return fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xFFFF0000u));
+  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pm));
+  return fmaxf(f.x, f.y);
+}
+// quant_block16 with the block's maximum already known
+// (the factor 1 / (scale * S_dec) depends on the scale code only: it comes from a 256-entry table the CTA fills once)
+template <bool UE>
+__device__ __forceinline__ uint2 quant_block16_given_max(float v[16], float bmax, float enc6, const float *inv_of_code, uint32_t &code) {
+  code = UE ? f32_to_ue5m3_sw(fminf(__fmul_rn(bmax, enc6), kFltMax)) : e4m3_encode(fminf(__fmul_rn(bmax, enc6), kFltMax));
+  const float inv = inv_of_code[code];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) v[k] = __fmul_rn(v[k], inv);
+  return make_uint2(e2m1_pack8(v), e2m1_pack8(v + 8));
+}
+// the two blocks (lane and lane + 32 of a 64-block unit) a lane owns, encoded and stored: nibbles, and the scale bytes as words
+// shared by four lanes (the same code for the linear and the swizzled layout)
+template <int T, bool UE>
+__device__ __forceinline__ void emit_two_blocks(const PackedBlock<T> a0, const PackedBlock<T> a1, int r, int c0, int c1, bool live0, bool live1,
+                                             float enc6, const float *inv_of_code, uint8_t *data, int ldq, uint8_t *sc, const ScalePos sp, bool words, int lane) {
+  float v[16];
+  uint32_t code0, code1;
+  unpack_block<T>(a0, v);
+  const uint2 q0 = quant_block16_given_max<UE>(v, packed_block_max<T>(a0), enc6, inv_of_code, code0);
+  unpack_block<T>(a1, v);
+  const uint2 q1 = quant_block16_given_max<UE>(v, packed_block_max<T>(a1), enc6, inv_of_code, code1);
+  uint8_t *drow = data + (size_t)r * ldq;
+  if (live0) __stcs((uint2 *)(drow + 8 * c0), q0);
+  if (live1) __stcs((uint2 *)(drow + 8 * c1), q1);
+  if (words) {
+    uint32_t w0 = live0 ? code0 << (8 * (lane & 3)) : 0u, w1 = live1 ? code1 << (8 * (lane & 3)) : 0u;
+    w0 |= __shfl_xor_sync(0xFFFFFFFFu, w0, 1); w1 |= __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
+    w0 |= __shfl_xor_sync(0xFFFFFFFFu, w0, 2); w1 |= __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
+    if ((lane & 3) == 0) {
+      const size_t rowpos = sp.row(r);
+      if (live0) *(uint32_t *)(sc + rowpos + sp.col(c0)) = w0;
+      if (live1) *(uint32_t *)(sc + rowpos + sp.col(c1)) = w1;
+    }
+  } else {
+    if (live0) sc[sp.at(r, c0)] = (uint8_t)code0;
+    if (live1) sc[sp.at(r, c1)] = (uint8_t)code1;
+  }
+}
+
+template <int T, bool UE, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+quant_fused_kernel(const uint8_t *__restrict__ src, int lds, int rows, int bpr, QOut o, float *gout, float *stat, unsigned *status, unsigned tag) {
+  static_assert(T != NVFP4A_FP32, "16-bit sources");
+  extern __shared__ uint4 qf_keep[];   // [warp][unit][4 words][32 lanes]
+  constexpr int kQfWarps = WARPS, kQfRegUnits = WARPS == 16 ? 4 : 0, kQfSmemUnits = 96 / WARPS, kFlight = WARPS == 16 ? 4 : 2;
+  __shared__ float warp_max[kQfWarps];
+  __shared__ float gmax_s;
+  __shared__ float inv_of_code[256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int upr = (bpr + 63) >> 6;
+  const long long U = (long long)rows * upr;   // (below 2^31: the host checks)
+  const unsigned u_begin = (unsigned)(U * blockIdx.x / gridDim.x), u_end = (unsigned)(U * (blockIdx.x + 1) / gridDim.x);
+  const int n_cta = (int)(u_end - u_begin);
+  const int n_w = n_cta > warp ? (n_cta - warp + kQfWarps - 1) / kQfWarps : 0;   // this warp's units: u_begin + warp + 16 j
+  // of a warp's units the last n_rg stay in registers, the n_sm before them in shared memory; the first n_glob are read again
+  const int n_ret = n_w < kQfRegUnits + kQfSmemUnits ? n_w : kQfRegUnits + kQfSmemUnits;
+  const int n_rg = n_ret < kQfRegUnits ? n_ret : kQfRegUnits, n_sm = n_ret - n_rg, n_glob = n_w - n_ret;
+  const size_t row_bytes = (size_t)lds * 2;
+  // every load tells L2 to drop the line early: asking it to keep lines (evict_last) slowed the first visit from 22 to 28 us and
+  // bought no hits for the second
+  const uint64_t drop_pol = l2_policy_evict_first();
+  uint4 *const my_smem = qf_keep + (size_t)warp * kQfSmemUnits * 128;
+  struct Unit { int r, c0; };
+  auto unit_of = [&](int j) {
+    const unsigned u = u_begin + warp + (unsigned)(kQfWarps * j), r = u / (unsigned)upr;
+    return Unit{(int)r, (int)(u - r * (unsigned)upr) * 64 + lane};
+  };
+  auto load_unit = [&](int j, uint64_t pol, PackedBlock<T> &a0, PackedBlock<T> &a1) {
+    const Unit t = unit_of(j);
+    const uint8_t *p = src + (size_t)t.r * row_bytes + (size_t)t.c0 * 32;
+    a0 = load_block<T>(p, t.c0 < bpr, pol);
+    a1 = load_block<T>(p + 32 * 32, t.c0 + 32 < bpr, pol);
+  };
+  auto absmax_of = [&](uint32_t pm, const PackedBlock<T> &a) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) pm = packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(packed_absmax<T>(pm, a.w[q].x), a.w[q].y), a.w[q].z), a.w[q].w);
+    return pm;
+  };
+
+  // ---- visit 1: amax; the last units stay on chip ----
+  uint32_t pm = 0;
+  int j = 0;
+  for (; j + kFlight <= n_glob; j += kFlight) {   // several units per warp in flight; nothing of them is kept
+    PackedBlock<T> x[2 * kFlight];
+#pragma unroll
+    for (int q = 0; q < kFlight; ++q) load_unit(j + q, drop_pol, x[2 * q], x[2 * q + 1]);
+#pragma unroll
+    for (int q = 0; q < 2 * kFlight; ++q) pm = absmax_of(pm, x[q]);
+  }
+  for (; j < n_glob + n_sm; ++j) {    // the rest of those, then the units that stay in shared memory
+    PackedBlock<T> a0, a1;
+    load_unit(j, drop_pol, a0, a1);
+    pm = absmax_of(absmax_of(pm, a0), a1);
+    if (j >= n_glob) {
+      uint4 *d = my_smem + (j - n_glob) * 128 + lane;
+      d[0] = a0.w[0]; d[32] = a0.w[1]; d[64] = a1.w[0]; d[96] = a1.w[1];
+    }
+  }
+  // the last units stay in registers (named, not an array: they must not end up in local memory); all four loads fly together
+  PackedBlock<T> rk0_0, rk1_0, rk0_1, rk1_1, rk0_2, rk1_2, rk0_3, rk1_3;
+  rk0_0.w[0] = rk0_0.w[1] = make_uint4(0, 0, 0, 0);
+  rk1_0 = rk0_1 = rk1_1 = rk0_2 = rk1_2 = rk0_3 = rk1_3 = rk0_0;
+  if (kQfRegUnits) {
+    if (n_rg > 0) load_unit(j, drop_pol, rk0_0, rk1_0);
+    if (n_rg > 1) load_unit(j + 1, drop_pol, rk0_1, rk1_1);
+    if (n_rg > 2) load_unit(j + 2, drop_pol, rk0_2, rk1_2);
+    if (n_rg > 3) load_unit(j + 3, drop_pol, rk0_3, rk1_3);
+    pm = absmax_of(absmax_of(absmax_of(absmax_of(pm, rk0_0), rk1_0), rk0_1), rk1_1);
+    pm = absmax_of(absmax_of(absmax_of(absmax_of(pm, rk0_2), rk1_2), rk0_3), rk1_3);
+  }
+  float m = T == NVFP4A_BF16 ? fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xFFFF0000u))
+                             : fmaxf(__half2float(__ushort_as_half((unsigned short)(pm & 0xFFFFu))), __half2float(__ushort_as_half((unsigned short)(pm >> 16))));
+#pragma unroll
+  for (int of = 16; of; of >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, of));
+  if (lane == 0) warp_max[warp] = m;
+  __syncthreads();
+
+  // ---- grid barrier (bounded) ----
+  // One 64-bit arrival counter that only grows: every launch of this kernel on a device has the same grid (one CTA per SM), so the
+  // arrival that returns `old` belongs to the round that is complete at (old / grid + 1) * grid.  Three dependent trips to L2 in all:
+  // the arrival (which publishes this CTA's maximum), the poll that sees the last arrival, the read of all CTAs' maxima by ONE warp
+  // per CTA (a line that thousands of warps read at once is served one request at a time).
+  if (warp == 0) {
+    float cm = lane < kQfWarps ? warp_max[lane] : 0.f;
+#pragma unroll
+    for (int of = 16; of; of >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xFFFFFFFFu, cm, of));
+    if (lane == 0) {
+      g_qf_max[blockIdx.x] = cm;
+      unsigned long long old, now;
+      asm volatile("atom.add.acq_rel.gpu.global.u64 %0, [%1], 1;" : "=l"(old) : "l"(&g_qf_arrivals) : "memory");
+      const unsigned long long target = (old / gridDim.x + 1) * gridDim.x;
+      const long long start = clock64();
+      for (;;) {
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(&g_qf_arrivals) : "memory");
+        if (now >= target) break;
+        if (clock64() - start > 2000000000ll) { atomicCAS(status, 0u, 0x601u | tag); break; }
+      }
+    }
+    __syncwarp();
+    float all = 0.f;
+    for (unsigned i = lane; i < gridDim.x; i += 32) all = fmaxf(all, __ldcg(&g_qf_max[i]));
+#pragma unroll
+    for (int of = 16; of; of >>= 1) all = fmaxf(all, __shfl_xor_sync(0xFFFFFFFFu, all, of));
+    if (lane == 0) gmax_s = all;
+  }
+  __syncthreads();
+  const float gmax = gmax_s;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *gout = gmax;
+    if (stat && gmax > 0.f) atomicMax((int *)stat, __float_as_int(gmax));
+  }
+
+  // ---- visit 2: encode, on-chip units first, then back through L2 ----
+  const QGlobal G = make_global(gmax, o.smax, true);
+  const float enc6 = __fmul_rn(G.s_enc, 1.f / 6.f), s_dec = G.s_dec;
+  if (threadIdx.x < 256) inv_of_code[threadIdx.x] = fminf(__frcp_rn(__fmul_rn(scale_to_f32(threadIdx.x, UE), s_dec)), kFltMax);
+  __syncthreads();
+  const ScalePos sp{o.sld};
+  const bool words = (bpr & 3) == 0 && (o.sld < 0 || ((o.sld & 3) == 0 && ((uintptr_t)o.sc & 3) == 0));
+  uint8_t *const data = o.data, *const sc = o.sc;
+  const int ldq = o.ld >> 1;
+  auto emit = [&](int j, const PackedBlock<T> &x0, const PackedBlock<T> &x1) {
+    const Unit t = unit_of(j);
+    emit_two_blocks<T, UE>(x0, x1, t.r, t.c0, t.c0 + 32, t.c0 < bpr, t.c0 + 32 < bpr, enc6, inv_of_code, data, ldq, sc, sp, words, lane);
+  };
+  // Interleaved: every step encodes one on-chip unit (registers first, then shared memory) and one re-read unit whose load was
+  // issued a step earlier, so the arithmetic of the on-chip units hides the latency of the re-reads.  The encoder is a long
+  // stretch of code: it appears at two places only (one loop), so that it stays in the instruction cache.
+  PackedBlock<T> n0, n1;
+  int jg = n_glob - 1;
+  if (jg >= 0) load_unit(jg, drop_pol, n0, n1);
+  for (int i = 0; i < n_ret || jg >= 0; ++i) {
+    if (i < n_ret) {
+      PackedBlock<T> x0, x1;
+      int j;
+      if (kQfRegUnits && i < n_rg) {   // (i is the same for the whole warp)
+        x0 = i == 0 ? rk0_0 : i == 1 ? rk0_1 : i == 2 ? rk0_2 : rk0_3;
+        x1 = i == 0 ? rk1_0 : i == 1 ? rk1_1 : i == 2 ? rk1_2 : rk1_3;
+        j = n_glob + n_sm + i;
+      } else {
+        const uint4 *d = my_smem + (i - n_rg) * 128 + lane;
+        x0.w[0] = d[0]; x0.w[1] = d[32]; x1.w[0] = d[64]; x1.w[1] = d[96];
+        j = n_glob + i - n_rg;
+      }
+      emit(j, x0, x1);
+    }
+    if (jg >= 0) {
+      const PackedBlock<T> c0 = n0, c1 = n1;
+      if (jg >= 1) load_unit(jg - 1, drop_pol, n0, n1);
+      emit(jg, c0, c1);
+      --jg;
+    }
+  }
+  __syncthreads();
+}
+
 // ---- pass 2, general path ----------------------------------------------------------------------------------------------
 // 16 consecutive lanes own one 16 x 16 tile of the OUTPUT matrix (lane i its row 16 t + i): rowwise or columnwise
 // (COL: output row = source column), 1 x 16 blocks or 16 x 16 tiles, 4over6, per-row globals, either scale type.
@@ -524,9 +750,50 @@ static QOut make_qout(const nvfp4a_tensor *t, int ld, int sld) {
   return o;
 }
 
+unsigned int *kernel_status_device_ptr();
+unsigned next_launch_tag();
+static std::atomic<int> g_quant_fused{1};
+static bool quant_fused_enabled() { return g_quant_fused.load() != 0; }
+
+template <int T, bool UE, int WARPS>
+static cudaError_t launch_quant_fused_w(const uint8_t *src, int lds, int rows, int bpr, QOut o, const nvfp4a_tensor *dst, cudaStream_t stream) {
+  static std::atomic<int> ready[64];   // per device: 0 unknown, 1 usable, -1 no cooperative launch
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int st = ready[dev & 63].load();
+  if (st == 0) {
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    int per_sm = 0;
+    if (coop && cudaFuncSetAttribute(quant_fused_kernel<T, UE, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQfSmemBytes) == cudaSuccess)
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_fused_kernel<T, UE, WARPS>, WARPS * 32, kQfSmemBytes);
+    st = (coop && per_sm >= 1) ? 1 : -1;
+    ready[dev & 63] = st;
+    (void)cudaGetLastError();
+  }
+  if (st < 0 || device_sms() > kQfMaxGrid) return cudaErrorNotSupported;
+  if (cudaError_t e = cudaFuncSetAttribute(quant_fused_kernel<T, UE, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQfSmemBytes)) return e;
+  float *gout = (float *)dst->global_scale, *stat = dst->amax;
+  unsigned *status = kernel_status_device_ptr();
+  unsigned tag = next_launch_tag();
+  void *args[] = {(void *)&src, (void *)&lds, (void *)&rows, (void *)&bpr, (void *)&o, (void *)&gout, (void *)&stat, (void *)&status, (void *)&tag};
+  return cudaLaunchCooperativeKernel((const void *)quant_fused_kernel<T, UE, WARPS>, dim3(device_sms()), dim3(WARPS * 32), args, kQfSmemBytes, stream);
+}
+template <int T, bool UE>
+static cudaError_t launch_quant_fused(const uint8_t *src, int lds, int rows, int bpr, QOut o, const nvfp4a_tensor *dst, cudaStream_t stream) {
+  if ((long long)rows * ((bpr + 63) / 64) >= (1ll << 31)) return cudaErrorNotSupported;
+  return launch_quant_fused_w<T, UE, 16>(src, lds, rows, bpr, o, dst, stream);
+}
+
 }  // namespace nvb
 
 using namespace nvb;
+
+
+extern "C" int nvfp4a_b200_set_quant_fused(int on) {
+  nvb::g_quant_fused = on ? 1 : 0;
+  return 0;
+}
 
 extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, int rows, int cols, const nvfp4a_tensor *rowwise,
                                             int ld_row, const nvfp4a_tensor *columnwise, int ld_col, const nvfp4a_quant_config *cfg,
@@ -565,6 +832,20 @@ extern "C" nvfp4a_status nvfp4a_quantize_ex(const nvfp4a_tensor *src, int lds, i
   const uint8_t *s = (const uint8_t *)src->data;
   const int bpr = cols / 16;
   const long long blocks = (long long)rows * bpr;
+  // One-read path: the common recipe (rowwise 1 x 16 blocks, one amax for the tensor, no 4over6, 16-bit source) on a matrix large
+  // enough to occupy every SM runs as ONE cooperative kernel that reads most of the source once (quant_fused_kernel).
+  if (c.compute_amax && rowwise && !columnwise && c.tile_rows == 1 && c.four_over_six == NVFP4A_4OVER6_OFF &&
+      !(rowwise->flags & NVFP4A_GLOBAL_PER_ROW) && src->dtype != NVFP4A_FP32 && (bpr & 3) == 0 && (long long)rows * cols >= (8ll << 20) &&
+      quant_fused_enabled()) {
+    const QOut o = make_qout(rowwise, ld_row, sld[0]);
+    cudaError_t e = cudaSuccess;
+    by_dense(src->dtype, [&](auto tc) {
+      constexpr int T = decltype(tc)::value;
+      if constexpr (T != NVFP4A_FP32) e = o.ue ? launch_quant_fused<T, true>(s, lds, rows, bpr, o, rowwise, stream) : launch_quant_fused<T, false>(s, lds, rows, bpr, o, rowwise, stream);
+    });
+    if (e != cudaErrorNotSupported) return cuda_fail(e, "nvfp4a_quantize_ex: kernel launch");
+    // (a device without cooperative launch takes the two-pass path below)
+  }
   if (c.compute_amax) {
     float *ar = rowwise ? (float *)rowwise->global_scale : nullptr, *ac = columnwise ? (float *)columnwise->global_scale : nullptr;
     const bool row_per_row = rowwise && (rowwise->flags & NVFP4A_GLOBAL_PER_ROW);

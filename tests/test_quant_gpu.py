@@ -203,3 +203,38 @@ def test_full_size_8192_square_bf16_swizzled_amax_computed():
     assert float(host(d_g)[0]) == amax == float(host(d_a)[0])
     assert np.array_equal(host(d_d), h.data)
     assert np.array_equal(host(d_s), h.scales)
+
+
+@pytest.mark.parametrize("dtype,flags,lds_pad,rows,cols", [(L.BF16, AM | SW, 0, 3001, 4160), (L.FP16, AM, 64, 2100, 4096), (L.BF16, AM | UE, 0, 8190, 1088)])
+def test_one_read_kernel_equals_the_two_launch_path(dtype, flags, lds_pad, rows, cols):
+    """Large matrices with the common recipe run as one cooperative kernel that keeps part of the matrix on the chip between the
+    amax visit and the encode visit; nvfp4a_b200_set_quant_fused(0) pins the amax kernel + encode kernel pair instead.  Both must
+    write the same bytes (rows that do not divide over the SMs, a ragged last 64-block unit per row, padded source pitch, FP16,
+    UE5M3 scales) -- and repeated calls must agree (the grid barrier's counter carries over from launch to launch)."""
+    rng = np.random.default_rng(rows + cols)
+    lds = cols + lds_pad
+    x = rng.standard_normal((rows, lds), dtype=np.float32) * 3.0
+    x[rng.random((rows, lds)) < 0.002] *= 100.0
+    d_x = dev(O.from_f32(x, dtype))
+    sbytes = O.scale_bytes(bool(flags & SW), 0 if flags & SW else cols // 16, rows, cols)
+    outs = []
+    try:
+        for fused in (1, 0, 1):
+            assert L.lib.nvfp4a_b200_set_quant_fused(fused) == 0
+            d_d = torch.full((rows * cols // 2,), 0xEE, dtype=torch.uint8, device="cuda")
+            d_s = torch.full((sbytes,), 0xEE, dtype=torch.uint8, device="cuda")
+            d_g, d_a = dev(np.zeros(1, np.float32)), dev(np.zeros(1, np.float32))
+            S, R = tensor(d_x, dtype), tensor(d_d, L.NVFP4, d_s, 0, d_g, d_a, flags, 0)
+            cfg = L.QuantConfig(1, 0, 1)
+            L.check(L.lib.nvfp4a_quantize_ex(ctypes.byref(S), lds, rows, cols, ctypes.byref(R), cols, None, 0, ctypes.byref(cfg), stream()))
+            torch.cuda.synchronize()
+            outs.append((host(d_d), host(d_s), float(host(d_g)[0]), float(host(d_a)[0])))
+    finally:
+        L.lib.nvfp4a_b200_set_quant_fused(1)
+    st = ctypes.c_uint(0)
+    L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 1))
+    assert st.value == 0
+    for other in outs[1:]:
+        assert np.array_equal(outs[0][0], other[0]) and np.array_equal(outs[0][1], other[1]) and outs[0][2:] == other[2:]
+    xr = O.to_f32(O.from_f32(x, dtype), dtype).reshape(rows, lds)[:, :cols]
+    assert outs[0][2] == float(np.abs(xr).max()) == outs[0][3]
