@@ -43,6 +43,12 @@ unsigned int nvfp4a_b200_last_launch(void);
  * value below 1000. */
 int nvfp4a_b200_set_wait_limit(long long cycles);
 
+/* Tuning aid (no counterpart in the reference): kernels that support it are launched with programmatic stream serialization, so
+ * that their set-up (barriers, tensor-memory allocation, descriptor prefetch -- nothing that touches global memory) runs while the
+ * stream's previous kernel drains; they wait for that kernel's completion before their first global access, so stream order is
+ * kept as without it.  on = 0 turns the attribute off for launches made after the call.  Process-wide; on by default.  Returns 0. */
+int nvfp4a_b200_set_pdl(int on);
+
 /* Measured ceiling of the block-scaled FP4 tensor-core instruction (no counterpart in the reference, which has no sm_100 kernel):
  * every SM's MMA thread issues 4 * iters tcgen05.mma kind::mxf4nvf4 of 128 x bn x 64 (pair != 0: cta_group::2, 256 x bn x 64 per SM
  * pair) back to back on one resident operand stage -- no loads, no epilogue; commit_each bit 0: one tcgen05.commit per four, bit 1: the twelve

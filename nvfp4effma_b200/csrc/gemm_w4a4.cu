@@ -623,6 +623,8 @@ unsigned next_launch_tag() {
 }
 static std::atomic<long long> g_tp_wait_limit{2000000000ll};
 long long tp_wait_limit() { return g_tp_wait_limit.load(); }
+static std::atomic<int> g_pdl{1};
+bool pdl_enabled() { return g_pdl.load() != 0; }
 unsigned int *kernel_status_device_ptr() {
   unsigned int *p = nullptr;
   cudaGetSymbolAddress((void **)&p, g_kernel_status);
@@ -681,6 +683,18 @@ bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, ui
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_tmap_image_pair(CUtensorMap *map, const void *base, uint32_t rows, uint64_t ktiles, uint64_t tiles128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {128, rows, ktiles, tiles128};
+  cuuint64_t strides[3] = {128, (cuuint64_t)kImgTileBytes, (cuuint64_t)kImgTileBytes * ktiles};
+  cuuint32_t box[4] = {128, rows, 1, 2};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            rows == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 bool gemm_w4a4_supports(const GemmArgs &g) {
@@ -819,6 +833,11 @@ extern "C" unsigned int nvfp4a_b200_last_launch(void) { return nvb::g_last_launc
 extern "C" int nvfp4a_b200_set_wait_limit(long long cycles) {
   if (cycles < 1000) return -1;
   nvb::g_tp_wait_limit = cycles;
+  return 0;
+}
+
+extern "C" int nvfp4a_b200_set_pdl(int on) {
+  nvb::g_pdl = on ? 1 : 0;
   return 0;
 }
 

@@ -102,6 +102,8 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   const int total = my_tiles * nk;
   unsigned *const status_word = g.status;
 
+  // The set-up touches no global memory: under programmatic dependent launch it runs while the stream's previous kernel drains.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full[s], 9); mbar_init(&empty[s], 1); }
     for (int q = 0; q < SD; ++q) { mbar_init(&sfs_full[q], 1); mbar_init(&sfs_empty[q], 4); }
@@ -121,6 +123,7 @@ gemm_w4a4_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // from here on the previous kernel has completed and its writes are visible
 
   const unsigned tag = g.tag;
   auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
@@ -407,10 +410,12 @@ cudaError_t launch_gemm_w4a4_pair(const GemmArgs &g, cudaStream_t s) {
   cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = kPairSmem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, gemm_w4a4_pair_kernel, tx, ty, ty64, tsx, tsy, td, a);
 }
 

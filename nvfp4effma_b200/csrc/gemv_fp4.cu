@@ -13,7 +13,8 @@
 //     sum_i a_i x_i = 2^(eb - 157) * sum_d 4^d * (sum_i a_i * piece_d(i)).
 // The 16 pieces of a token are 16 rows of the MMA's M dimension (block scales 1.0), 256 weight rows are its N dimension,
 // and the inner sums are what the tensor cores compute: accumulator lane d, column r holds piece d against weight row r.
-// Two warps read the 16 (or 32) lanes and add the pieces with their powers of four in FP32.  Pieces are built once per CTA
+// Two warps read the 16 (or 32) lanes, join piece d with piece d + 8 and leave the sums in shared memory, where each of 256
+// threads adds its weight row's eight values with their powers of four in FP32.  Pieces are built once per CTA
 // in shared memory (8 warps, while the first weight tiles are in flight) in the 128-byte-swizzled K-major layout the MMA
 // reads.  The MMA's M is 128: the rows past the pieces read whatever follows them in shared memory and produce
 // accumulator lanes nobody looks at (every FP4 bit pattern is a finite number).
@@ -22,6 +23,12 @@
 // contiguous range of 256-k chunks.  Partial results meet through distributed shared memory: rank 0 adds the partials of
 // ranks 1, 2, ... in rank order -- deterministic, no atomics, no global scratch -- and runs the plain or extended epilogue,
 // one thread per weight row.
+//
+// Timeline of a launch (8192 x 8192, 128 CTAs, about 10 us between the previous kernel's end and this one's): the set-up
+// (barriers, tensor memory) touches no global memory and runs under programmatic dependent launch while the previous kernel
+// drains; the ring's first fill is requested by five warps at once right after the block-wide barrier, because a copy
+// instruction costs its warp 150-300 ns to issue whatever it moves (an image stage is therefore two rank-4 tensor copies: 32
+// KiB of nibbles, 4 KiB of scales); the epilogue's operands are fetched only after the pieces are built.
 //
 // Semantics: FP32 accumulation in the tensor cores' order, within the FP32 accumulation bound of the exact definition
 // (reference include/nvfp4effma.h:82-92 there), as the reference's own tensor-core GEMV (src/tensors/gemv_tc.cuh there).
@@ -88,7 +95,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint32_t *wmax = tmem_slot + 2;                          // [8 warps][NTOK] largest |x| bit pattern
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gm = g.m, gn = g.n, ktiles = g.ktiles;
+  const int gm = g.m, gn = g.n;
   const int tiles128 = (gm + 127) >> 7;
   const int tm = blockIdx.y;                               // 256-row tile
   const bool a_image = g.a_image;
@@ -99,7 +106,47 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   unsigned *const status_word = g.status;
   const bool second = tm * 2 + 1 < tiles128;               // the tile's second 128 rows exist
 
-  // the decomposition warps fetch their activations before anything else: the loads fly during the set-up below
+  // One stage of the weight ring.  A copy instruction costs the issuing warp 150-200 cycles per active lane whatever it moves,
+  // so a stage is as few copies as its layout allows, issued by as many lanes of ONE instruction: an image's nibbles (32 KiB, both
+  // 128-row halves) and block scales (4 KiB) are two rank-4 tensor copies in lanes 0 and 1.
+  auto request_stage = [&](int it) {
+    const int s = it % kStages, c = c0 + it;
+    uint8_t *sW = stages + (size_t)s * stage_bytes, *sSf = sW + kDataBytes;
+    if (lane == 0) mbar_arrive_expect_tx(&full[s], kDataBytes + (linear ? (uint32_t)kRawSfBytes : ((second || a_image) ? 4096u : 2048u)));
+    __syncwarp();
+    if (a_image) {
+      if (lane < 2) tma_load_4d(lane ? sSf : sW, lane ? &tmap_s : &tmap_a, 0, 0, c, 2 * tm, &full[s]);
+    } else if (lane < 2) {
+      if (lane == 0) {
+        tma_load_2d(sW, &tmap_a, c * 128, tm * 256, &full[s]);
+      } else if (linear) {
+        tma_load_2d(sW + kStageBytes, &tmap_s, c * 4, tm * 256, &full[s]);   // 16 bytes (4 words) of 256 rows; rows past m read zeros
+      }
+    } else if (lane < 4 && !linear) {
+      const int h = lane - 2;
+      if (h == 0 || second) bulk_load(sSf + h * 2048, sa_base + (size_t)(2 * tm + h) * ((size_t)((-sa_ld) >> 2) * 512) + (size_t)c * 2048, 2048, &full[s]);
+    }
+  };
+
+  const int early = nloc < kStages ? nloc : kStages;   // the ring's first fill needs no wait
+
+  // The set-up touches no global memory, so it may run while the stream's previous kernel finishes (programmatic dependent
+  // launch); nothing before the block-wide barrier waits for memory either: the first weights are requested right after it.
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    if (a_image || linear) prefetch_tensormap(&tmap_s);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(pieces_ready, kDecompThreads / 32);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x < 128) ((uint32_t *)unit_sf)[threadIdx.x] = 0x38383838u;  // E4M3 1.0
+  fence_proxy_async_smem();
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  pdl_wait();
+  // the decomposition warps ask for their activations first: the loads fly while the barrier below gathers the CTA
   const int t2 = threadIdx.x - 64, nvec = nloc * 32;  // vectors of 8 consecutive k; at most 2 per thread and token
   uint4 xq[NTOK][2];
   if (warp >= 2) {
@@ -112,32 +159,6 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
   }
 
-  // rank 0 runs the epilogue, one thread per weight row: its operands are fetched now, far ahead of their use
-  const int erow = t2, ei = tm * 256 + erow;
-  const bool erow_ok = warp >= 2 && rank == 0 && ei < gm;
-  float e_rowp = 0.f, e_bias = 0.f, e_c[NTOK];
-#pragma unroll
-  for (int t = 0; t < NTOK; ++t) e_c[t] = 0.f;
-  if (erow_ok) {
-    e_rowp = epi_row_part(g.e, ei);
-    if (g.e.bias) e_bias = load_dense(g.e.bias_dtype, g.e.bias, ei);
-    if (g.e.beta != 0.f)
-#pragma unroll
-      for (int t = 0; t < NTOK; ++t)
-        if (t < gn) e_c[t] = load_dense(g.e.c_dtype, g.e.c, (size_t)t * g.e.ldc + ei);
-  }
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_ready[s], 1); }
-    mbar_init(acc_full, 1);
-    mbar_init(pieces_ready, kDecompThreads / 32);
-    *abort_flag = 0;
-    fence_barrier_init();
-    prefetch_tensormap(&tmap_a);
-  }
-  if (threadIdx.x < 128) ((uint32_t *)unit_sf)[threadIdx.x] = 0x38383838u;  // E4M3 1.0
-  fence_proxy_async_smem();
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -145,6 +166,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   const unsigned tag = g.tag;
   auto wait = [abort_flag, status_word, tag](uint64_t *bar, uint32_t parity, unsigned code) -> bool {
+    if (mbar_try(bar, parity)) return true;   // the common case: no flag read, no clock read
     if (*abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     *abort_flag = 1;
@@ -152,63 +174,52 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     return false;
   };
 
+  // rank 0 runs the epilogue, one thread per weight row; its operands are fetched once the pieces are built, far ahead of their use
+  const int erow = t2, ei = tm * 256 + erow;
+  const bool erow_ok = warp >= 2 && rank == 0 && ei < gm;
+  float e_rowp = 0.f, e_bias = 0.f, e_c[NTOK];
+#pragma unroll
+  for (int t = 0; t < NTOK; ++t) e_c[t] = 0.f;
+
+  // The ring's first fill, one stage per warp: a copy instruction is slow to issue (see request_stage), and the decomposition
+  // warps among these have nothing to do until their activations arrive.
+  if (warp < early) request_stage(warp);
+
   if (warp == 0) {
-    // ---------------- producer ----------------
-    // A copy instruction costs the issuing warp 150-200 cycles whatever it moves, and the ring's first stages are all
-    // requested before anything else can happen: lanes 0 and 1 issue the stage's two tensor copies in one instruction,
-    // lanes 2 and 3 the bulk copies of the scale tiles in another.  All lanes wait on `empty` together.
-    for (int it = 0; it < nloc; ++it) {
-      const int s = it % kStages, c = c0 + it;
+    // ---------------- producer: after the first fill, each stage as its slot comes free ----------------
+    for (int it = early; it < nloc; ++it) {
+      const int s = it % kStages;
       const bool okw = wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty);
       if (!__all_sync(0xFFFFFFFFu, okw)) break;
-      uint8_t *sW = stages + (size_t)s * stage_bytes, *sSf = sW + kDataBytes;
-      if (lane == 0) mbar_arrive_expect_tx(&full[s], kDataBytes + (linear ? (uint32_t)kRawSfBytes : (second ? 4096u : 2048u)));
-      __syncwarp();
-      if (lane < 2) {
-        if (a_image) {
-          // a tile index past the image reads zeros
-          const int z = lane == 0 ? (2 * tm) * ktiles + c : (second ? (2 * tm + 1) * ktiles + c : 0x7FFFFFF);
-          tma_load_3d(sW + lane * 16384, &tmap_a, 0, 0, z, &full[s]);
-        } else if (lane == 0) {
-          tma_load_2d(sW, &tmap_a, c * 128, tm * 256, &full[s]);
-        } else if (linear) {
-          tma_load_2d(sW + kStageBytes, &tmap_s, c * 4, tm * 256, &full[s]);   // 16 bytes (4 words) of 256 rows; rows past m read zeros
-        }
-      } else if (lane < 4 && !linear) {
-        const int h = lane - 2;
-        if (h == 0 || second) {
-          const uint8_t *src = a_image ? sa_base + ((size_t)(2 * tm + h) * ktiles + c) * kImgTileBytes + kImgDataBytes
-                                       : sa_base + (size_t)(2 * tm + h) * ((size_t)((-sa_ld) >> 2) * 512) + (size_t)c * 2048;
-          bulk_load(sSf + h * 2048, src, 2048, &full[s]);
-        }
-      }
+      request_stage(it);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer: D[piece][weight row] += pieces (A, M = 128) x weights (B, N = 256) ----------------
-    if (lane == 0 && nloc > 0) {
+    // The whole warp runs the loop and one elected lane issues: from inside a one-lane branch every tcgen05 instruction costs the
+    // warp about 150 cycles, and a chunk needs twelve of them (eight scale-tile copies, four MMAs).
+    if (nloc > 0) {
       constexpr uint32_t idesc = idesc_mxf4nvf4(128, kRows);
       const uint32_t sfa_tmem = tmem_base + 256;
-      tmem_cp_32x128b_warpx4(sfa_tmem, smem_desc_sf(smem_u32(unit_sf)));
-      if (wait(pieces_ready, 0, kStWaitPieces)) {
+      tmem_cp_32x128b_warpx4_elect(sfa_tmem, smem_desc_sf(smem_u32(unit_sf)));
+      if (__all_sync(0xFFFFFFFFu, wait(pieces_ready, 0, kStWaitPieces))) {
         tc_fence_after();
         bool ok = true;
+        const uint64_t da0 = smem_desc_sw128(smem_u32(pieces));
         for (int it = 0; it < nloc; ++it) {
           const int s = it % kStages;
-          ok = linear ? wait(&sf_ready[s], (it / kStages) & 1, kStWaitRetile) : wait(&full[s], (it / kStages) & 1, kStWaitFull);
+          ok = __all_sync(0xFFFFFFFFu, linear ? wait(&sf_ready[s], (it / kStages) & 1, kStWaitRetile) : wait(&full[s], (it / kStages) & 1, kStWaitFull));
           if (!ok) break;
           tc_fence_after();
           const uint32_t sW = smem_u32(stages + (size_t)s * stage_bytes), sSf = sW + kDataBytes;
           const uint32_t sfb_tmem = tmem_base + 272 + 32 * s;
-          const uint64_t da = smem_desc_sw128(smem_u32(pieces) + it * (PR * 128)), db = smem_desc_sw128(sW);
+          const uint64_t da = da0 + (uint32_t)(it * (PR * 128 >> 4)), db = smem_desc_sw128(sW);
+          const uint64_t sf0 = smem_desc_sf(sSf), sf1 = smem_desc_sf(sSf + 2048);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            tmem_cp_32x128b_warpx4(sfb_tmem + 8 * j, smem_desc_sf(sSf + j * 512));
-            tmem_cp_32x128b_warpx4(sfb_tmem + 8 * j + 4, smem_desc_sf(sSf + 2048 + j * 512));
-            mma_mxf4nvf4(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_tmem, sfb_tmem + 8 * j, (it | j) != 0);
-          }
-          tc_commit(&empty[s]);
+          for (int j = 0; j < 4; ++j)   // descriptors advance in 16-byte units: 32 bytes along the operand rows, 512 bytes per scale tile
+            cp2_mma_mxf4nvf4_elect(sfb_tmem + 8 * j, sf0 + 32 * j, sf1 + 32 * j, tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_tmem, (uint32_t)((it | j) != 0));
+          tc_commit_elect(&empty[s]);
         }
-        if (ok) tc_commit(acc_full);
+        if (ok) tc_commit_elect(acc_full);
       }
     }
   } else {
@@ -266,44 +277,42 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(pieces_ready);
+    if (erow_ok) {
+      e_rowp = epi_row_part(g.e, ei);
+      if (g.e.bias) e_bias = load_dense(g.e.bias_dtype, g.e.bias, ei);
+      if (g.e.beta != 0.f)
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t)
+          if (t < gn) e_c[t] = load_dense(g.e.c_dtype, g.e.c, (size_t)t * g.e.ldc + ei);
+    }
 
     if ((warp & 3) == 0) {
-      // ---------------- warps 4 and 8 (tensor-memory lanes 0..31): 128 weight rows each -> res[token][row] ----------------
+      // ---------------- warps 4 and 8 (tensor-memory lanes 0..31): accumulator -> shared memory, 128 weight rows each ----------------
+      // A thread of the 16 x 256-bit load holds pieces d and d + 8 (d = lane / 4) of sixteen weight rows; it joins the two and
+      // leaves them in red[token][weight row][9] (the stage ring is free by now: every MMA has completed), from where all 256
+      // threads sum their row's eight values.
       const int half = warp >> 3;  // 0: columns 0..127, 1: columns 128..255
       if (nloc > 0 && wait(acc_full, 0, kStWaitAcc)) {
         tc_fence_after();
-        const int dlo = lane >> 2;                 // this thread's pieces: dlo and dlo + 8
+        const int dlo = lane >> 2;
         const float flo = pow2f(2 * dlo), fhi = pow2f(2 * dlo + 16);
 #pragma unroll
-        for (int t = 0; t < NTOK; ++t) {
-          const int ex = ebs[t] - 157, e1 = max(ex, -100);
-          const float s1 = pow2f(e1), s2 = pow2f(ex - e1);
+        for (int t = 0; t < NTOK; ++t)
 #pragma unroll
           for (int q = 0; q < 2; ++q) {            // 64 columns per load
             uint32_t r[32];
             tmem_ld_16x256b_x8(tmem_base + ((uint32_t)(16 * t) << 16) + half * 128 + q * 64, r);
             tmem_ld_wait();
+            float *red = (float *)stages + ((size_t)t * 256 + half * 128 + q * 64 + 2 * (lane & 3)) * 9 + dlo;
 #pragma unroll
             for (int gq = 0; gq < 8; ++gq) {
-              float v0 = __fmaf_rn(__uint_as_float(r[4 * gq + 2]), fhi, __fmul_rn(__uint_as_float(r[4 * gq]), flo));
-              float v1 = __fmaf_rn(__uint_as_float(r[4 * gq + 3]), fhi, __fmul_rn(__uint_as_float(r[4 * gq + 1]), flo));
-#pragma unroll
-              for (int o = 4; o < 32; o <<= 1) {
-                v0 = __fadd_rn(v0, __shfl_xor_sync(0xFFFFFFFFu, v0, o));
-                v1 = __fadd_rn(v1, __shfl_xor_sync(0xFFFFFFFFu, v1, o));
-              }
-              if (lane < 4) {
-                const int col = half * 128 + q * 64 + gq * 8 + 2 * lane;
-                const bool bad = ebs[t] == 255;  // Inf or NaN among the activations
-                float *dst = &res[(rank * NTOK + t) * 256 + col];
-                st_peer_f32(dst, 0, bad ? __int_as_float(0x7FC00000) : __fmul_rn(__fmul_rn(v0, s1), s2));
-                st_peer_f32(dst + 1, 0, bad ? __int_as_float(0x7FC00000) : __fmul_rn(__fmul_rn(v1, s1), s2));
-              }
+              red[(gq * 8) * 9] = __fmaf_rn(__uint_as_float(r[4 * gq + 2]), fhi, __fmul_rn(__uint_as_float(r[4 * gq]), flo));
+              red[(gq * 8 + 1) * 9] = __fmaf_rn(__uint_as_float(r[4 * gq + 3]), fhi, __fmul_rn(__uint_as_float(r[4 * gq + 1]), flo));
             }
           }
-        }
       }
-    } else if (linear && warp >= 5) {
+    }
+    if (linear && (warp & 3) != 0 && warp >= 5) {
       // ---------------- warps 5, 6, 7, 9: linear block scales [256 rows][16 bytes] -> the eight 512-byte tiles of the stage ----------------
       const int w = warp == 9 ? 3 : warp - 5;
       for (int it = w; it < nloc; it += 4) {
@@ -324,6 +333,22 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sf_ready[s]);
+      }
+    }
+    {
+      // ---------------- all eight warps: each thread sums the sixteen pieces of its weight row and hands the result to rank 0 ----------------
+      // (the order of the additions is that of a butterfly over the piece pairs)
+      named_barrier(3, kDecompThreads);
+      if (nloc > 0 && !*abort_flag) {
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+          const float *v = (const float *)stages + ((size_t)t * 256 + t2) * 9;
+          const float sum = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[1]), __fadd_rn(v[2], v[3])), __fadd_rn(__fadd_rn(v[4], v[5]), __fadd_rn(v[6], v[7])));
+          const int ex = ebs[t] - 157, e1 = max(ex, -100);
+          const float s1 = pow2f(e1), s2 = pow2f(ex - e1);
+          const bool bad = ebs[t] == 255;  // Inf or NaN among the activations
+          st_peer_f32(&res[(rank * NTOK + t) * 256 + t2], 0, bad ? __int_as_float(0x7FC00000) : __fmul_rn(__fmul_rn(sum, s1), s2));
+        }
       }
     }
   }
@@ -437,7 +462,8 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   CUtensorMap ta, ts;
   memset(&ts, 0, sizeof ts);
   if (g.A.image) {
-    if (!make_tmap_bytes(&ta, g.A.data, 128, 128, 128, 128, (uint64_t)((g.m + 127) / 128) * a.ktiles, kImgTileBytes)) return cudaErrorInvalidValue;
+    if (!make_tmap_image_pair(&ta, g.A.data, 128, (uint64_t)a.ktiles, (uint64_t)((g.m + 127) / 128))) return cudaErrorInvalidValue;
+    if (!make_tmap_image_pair(&ts, (const uint8_t *)g.A.data + kImgDataBytes, 16, (uint64_t)a.ktiles, (uint64_t)((g.m + 127) / 128))) return cudaErrorInvalidValue;
     a.sa = g.A.data;
   } else {
     if (!make_tmap_bytes(&ta, g.A.data, (uint64_t)g.k / 2, (uint64_t)g.m, (uint64_t)g.A.ld / 2, kRows)) return cudaErrorInvalidValue;
@@ -469,10 +495,12 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel's set-up overlaps the previous kernel's tail
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, ta, ts, a);
 }
 

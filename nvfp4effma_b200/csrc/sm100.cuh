@@ -62,6 +62,14 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.cp / mma operand reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream still
+// runs, once every CTA of the predecessor has executed pdl_launch_dependents() (or exited).  It must execute pdl_wait()
+// before it touches any memory the predecessor reads or writes: the wait returns when the predecessor has completed and its
+// writes are visible.  Both are no-ops in a launch without the attribute or without a predecessor.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- thread-block clusters: rank, barrier, loads from a peer CTA's shared memory ---------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -96,6 +104,10 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, int x, int y, int z, int w, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
 }
 // CTA pair: the copy lands in this CTA's shared memory, its bytes are counted on the barrier at `own_bar`'s address in the
 // pair's even CTA (rank 0 of a cluster of two), whose MMA thread waits for both CTAs' operands on that one barrier.
@@ -302,6 +314,21 @@ __device__ __forceinline__ void mma4_commit_elect(uint32_t d_tmem, uint64_t a_de
                                                   uint32_t sfb_step, uint32_t accumulate, uint64_t *bar) {
   NVB_MMA4_BODY("1", "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%19];");
 }
+// One 64-value k group of the FP4 GEMV in one statement (elected lane of a converged warp): the two 512-byte scale tiles of the
+// group's 256 weight rows copied into tensor memory (tcgen05.cp), then the MMA that reads them.
+__device__ __forceinline__ void cp2_mma_mxf4nvf4_elect(uint32_t sfb_tmem, uint64_t sf_desc0, uint64_t sf_desc1, uint32_t d_tmem, uint64_t a_desc,
+                                                       uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %8, 0;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t"
+               "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%2], %3;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%4], %5, %6, %7, [%9], [%0], p;\n\t}"
+               ::"r"(sfb_tmem), "l"(sf_desc0), "r"(sfb_tmem + 4), "l"(sf_desc1), "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc),
+                 "r"(accumulate), "r"(sfa_tmem) : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xFFFFFFFF;\n\t@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}"
+               ::"r"(taddr), "l"(sdesc) : "memory");
+}
 // The same for kind::f16 (K = 16 per instruction: four MMAs cover the 64 values of k of a 128-byte-row stage).
 __device__ __forceinline__ void mma4_f16_commit_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate, uint64_t *bar) {
   asm volatile("{\n\t.reg .pred p, q, t;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 t, %3, %3;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
@@ -347,12 +374,18 @@ bool make_tmap_dense(CUtensorMap *map, const void *base, int elem_bytes, uint64_
 // Block scales stored as 512-byte tiles (the swizzled layout), as a tensor of 8-byte words: `rows` rows of row_bytes bytes `stride`
 // bytes apart; a box is 2 KiB of one row (the four tiles of 256 values of k), zero-filled past the end of the row.
 bool make_tmap_scales(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t stride);
+// A tensor-core image as a rank-4 tensor of bytes [128-row tile][k tile][row of 128 bytes]: `rows` = 128 with the 128-byte swizzle
+// for the nibbles (base = the image), 16 without swizzle for a tile's 2 KiB of block scales (base = the image + 16 KiB).  One
+// box is that part of two vertically adjacent tiles (the two halves of 256 weight rows); a tile past the image reads zeros.
+bool make_tmap_image_pair(CUtensorMap *map, const void *base, uint32_t rows, uint64_t ktiles, uint64_t tiles128);
 // Tag of a launch for the status word: (library-wide launch sequence number mod 2^20) << 12.  A kernel that gives up a wait records
 // code | tag, so the word names the kind of wait (low 12 bits: 0x1xx W4A4 GEMM, 0x2xx FP4 GEMV, 0x3xx W4A16 GEMM, 0x4xx tensor-parallel
 // barrier, 0x5xx ceiling measurement) and the launch (nvfp4a_b200_last_launch gives the calling thread's latest sequence number).
 unsigned next_launch_tag();
 // SM clock cycles a tensor-parallel barrier waits for its peers before it gives up (nvfp4a_b200_set_wait_limit; default 2e9, about a second)
 long long tp_wait_limit();
+// whether launches ask for programmatic stream serialization (nvfp4a_b200_set_pdl; on by default)
+bool pdl_enabled();
 // kernel status word: 0 = healthy; kernels that gave up a wait write a non-zero code (see nvfp4a_b200_kernel_status)
 unsigned int *kernel_status_device_ptr();
 
