@@ -93,6 +93,8 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint32_t *tmem_slot = (uint32_t *)(pieces_ready + 1);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
   uint32_t *wmax = tmem_slot + 2;                          // [8 warps][NTOK] largest |x| bit pattern
+  volatile int *inexact = (volatile int *)(wmax + 8 * NTOK);   // some activation of this CTA does not fit the digit planes
+  int *consumed = (int *)(wmax + 8 * NTOK + 1);                // warps done with a stage (the CUDA-core consumer)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gm = g.m, gn = g.n;
@@ -140,6 +142,8 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     mbar_init(acc_full, 1);
     mbar_init(pieces_ready, kDecompThreads / 32);
     *abort_flag = 0;
+    *inexact = 0;
+    *consumed = 0;
     fence_barrier_init();
   }
   if (threadIdx.x < 128) ((uint32_t *)unit_sf)[threadIdx.x] = 0x38383838u;  // E4M3 1.0
@@ -201,7 +205,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       constexpr uint32_t idesc = idesc_mxf4nvf4(128, kRows);
       const uint32_t sfa_tmem = tmem_base + 256;
       tmem_cp_32x128b_warpx4_elect(sfa_tmem, smem_desc_sf(smem_u32(unit_sf)));
-      if (__all_sync(0xFFFFFFFFu, wait(pieces_ready, 0, kStWaitPieces))) {
+      if (__all_sync(0xFFFFFFFFu, wait(pieces_ready, 0, kStWaitPieces)) && !*inexact) {   // (the CUDA cores consume the ring otherwise)
         tc_fence_after();
         bool ok = true;
         const uint64_t da0 = smem_desc_sw128(smem_u32(pieces));
@@ -226,6 +230,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ---------------- 8 warps: activations -> FP4 pieces in shared memory ----------------
     const int w2 = warp - 2;
     int ebs[NTOK];  // biased exponent the token's pieces refer to
+    uint32_t lost = 0;
 #pragma unroll
     for (int t = 0; t < NTOK; ++t) {
       uint32_t a = 0;
@@ -247,6 +252,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int w = 0; w < 8; ++w) a = max(a, wmax[w * NTOK + t]);
       const int eb = max((int)(a >> 7), 1);
       ebs[t] = eb;
+      if (eb == 255) lost = 1;   // Inf or NaN: IEEE arithmetic on the CUDA cores gives each output its own Inf or NaN
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int v = t2 + u * kDecompThreads;
@@ -260,6 +266,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t mant = (h & 0x7Fu) | (e ? 0x80u : 0u);
           const int sh = (int)max(e, 1u) - eb + 24;  // <= 24
           X[i] = sh >= 0 ? mant << sh : (sh > -8 ? mant >> (-sh) : 0u);
+          if (sh < 0) lost |= mant & ((1u << min(-sh, 8)) - 1u);   // bits of this element below the last digit plane
           sgn |= (h >> 15) << (4 * i + 3);
         }
         const int chunk = v >> 5, b = (v & 31) * 4;
@@ -274,9 +281,12 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
       }
     }
+    if (lost) *inexact = 1;
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) mbar_arrive(pieces_ready);
+    named_barrier(3, kDecompThreads);   // every warp's verdict is in
+    const bool exact = *inexact == 0;
     if (erow_ok) {
       e_rowp = epi_row_part(g.e, ei);
       if (g.e.bias) e_bias = load_dense(g.e.bias_dtype, g.e.bias, ei);
@@ -286,7 +296,67 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (t < gn) e_c[t] = load_dense(g.e.c_dtype, g.e.c, (size_t)t * g.e.ldc + ei);
     }
 
-    if ((warp & 3) == 0) {
+    if (!exact) {
+      // ---------------- the exact route for activations the digit planes cannot hold ----------------
+      // Some element lies more than 2^24 below its token's largest, so its low bits (or all of it) would be dropped -- far below
+      // the FP32 accumulation bound unless the large elements meet zero weights.  Then the tensor cores sit this CTA out: the
+      // eight warps consume the ring themselves, one thread per weight row, decoding nibbles and block scales from the stages
+      // and accumulating in FP32 against the activations (kept as FP32 in the pieces' memory).  Several times slower; rare.
+      float *xs = (float *)pieces;   // [token][k of this CTA]
+#pragma unroll
+      for (int t = 0; t < NTOK; ++t)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int v = t2 + u * kDecompThreads;
+          if (v >= nvec) break;
+          const uint32_t w[4] = {xq[t][u].x, xq[t][u].y, xq[t][u].z, xq[t][u].w};
+          float *dst = xs + (size_t)t * nloc * 256 + (size_t)v * 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dst[2 * i] = __uint_as_float(w[i] << 16);
+            dst[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+          }
+        }
+      named_barrier(3, kDecompThreads);
+      float acc[NTOK];
+#pragma unroll
+      for (int t = 0; t < NTOK; ++t) acc[t] = 0.f;
+      const int r = t2;
+      bool ok = true;
+      for (int it = 0; it < nloc && ok; ++it) {
+        const int s = it % kStages;
+        ok = wait(&full[s], (it / kStages) & 1, kStWaitFull);
+        if (!ok) break;
+        const uint8_t *st = stages + (size_t)s * stage_bytes;
+        const uint8_t *rowp = st + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint8_t *sfp = linear ? st + kStageBytes + r * 16 : st + kDataBytes + (r >> 7) * 2048 + (r & 31) * 16 + ((r & 127) >> 5) * 4;
+#pragma unroll 2
+        for (int u16 = 0; u16 < 8; ++u16) {
+          const uint4 q = *(const uint4 *)(rowp + ((u16 ^ (r & 7)) << 4));
+          const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const int jj = 2 * u16 + b;   // block of 16 values within the chunk
+            const float sc = __fmul_rn(e4m3_to_f32((linear ? sfp[jj] : sfp[(jj >> 2) * 512 + (jj & 3)]) & 0x7Fu), 0.5f);
+#pragma unroll
+            for (int t = 0; t < NTOK; ++t) {
+              const float *xv = xs + (size_t)t * nloc * 256 + (size_t)it * 256 + jj * 16;
+              float part = 0.f;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                part = __fmaf_rn((float)e2m1_x2((wd[2 * b + (i >> 3)] >> (4 * (i & 7))) & 0xFu), xv[i], part);
+              acc[t] = __fmaf_rn(sc, part, acc[t]);
+            }
+          }
+        }
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0 && atomicAdd(consumed, 1) == 8 * (it + 1) - 1) mbar_arrive(&empty[s]);   // the eighth warp hands the stage back
+      }
+      if (ok)
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) st_peer_f32(&res[(rank * NTOK + t) * 256 + r], 0, acc[t]);
+    } else if ((warp & 3) == 0) {
       // ---------------- warps 4 and 8 (tensor-memory lanes 0..31): accumulator -> shared memory, 128 weight rows each ----------------
       // A thread of the 16 x 256-bit load holds pieces d and d + 8 (d = lane / 4) of sixteen weight rows; it joins the two and
       // leaves them in red[token][weight row][9] (the stage ring is free by now: every MMA has completed), from where all 256
@@ -312,7 +382,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
       }
     }
-    if (linear && (warp & 3) != 0 && warp >= 5) {
+    if (exact && linear && (warp & 3) != 0 && warp >= 5) {
       // ---------------- warps 5, 6, 7, 9: linear block scales [256 rows][16 bytes] -> the eight 512-byte tiles of the stage ----------------
       const int w = warp == 9 ? 3 : warp - 5;
       for (int it = w; it < nloc; it += 4) {
@@ -335,7 +405,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (lane == 0) mbar_arrive(&sf_ready[s]);
       }
     }
-    {
+    if (exact) {
       // ---------------- all eight warps: each thread sums the sixteen pieces of its weight row and hands the result to rank 0 ----------------
       // (the order of the additions is that of a butterfly over the piece pairs)
       named_barrier(3, kDecompThreads);

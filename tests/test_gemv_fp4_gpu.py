@@ -70,9 +70,10 @@ def test_automatic_route_by_size():
     check_bound(c, h, got, amax, exp)
 
 
-@pytest.mark.parametrize("spread", [0, 12, 23])
+@pytest.mark.parametrize("spread", [0, 12, 23, 31, 60, 120])
 def test_activations_with_a_wide_dynamic_range(pin, spread):
-    """|x| spread over 2^-spread .. 1 (and exact zeros): up to 2^-24 of the largest element the digit planes hold every bit."""
+    """|x| spread over 2^-spread .. 1 (and exact zeros): up to 2^-24 of the largest element the digit planes hold every bit;
+    a CTA that meets anything smaller computes its share on the CUDA cores instead."""
     pin(2)
     m, n, k = 384, 2, 2048
     c = Case(m, n, k, L.BF16, L.FP32, L.FP32, -1, 1.0, 0.0, fa=SW)
@@ -85,6 +86,35 @@ def test_activations_with_a_wide_dynamic_range(pin, spread):
     got, amax = run_gemm(c, h)
     assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
     check_bound(c, h, got, amax, exp)
+
+
+@pytest.mark.parametrize("linear", [False, True])
+def test_large_activations_that_meet_zero_weights(pin, linear):
+    """A few activations of magnitude 1 at positions where every weight is zero, all others near 2^-40: the result consists of
+    the small terms alone, so bits dropped relative to the LARGEST activation would show (the FP32 accumulation bound is
+    relative to sum |a_i x_i|).  Both tokens; swizzled and linear block scales; one token left narrow."""
+    from util import rand_fp4
+    pin(2)
+    m, n, k = 640, 2, 4096
+    c = Case(m, n, k, L.BF16, L.FP32, L.FP32, -1, 1.0, 0.0, fa=0 if linear else SW)
+    h = build_case(c, 990)
+    rng = np.random.default_rng(991)
+    if linear:
+        h["A"] = rand_fp4(rng, m, k, ld=h["lda"], ld_scale=k // 16, glob=0.375)
+    big = rng.choice(k, 9, replace=False)
+    a = h["A"].data.reshape(m, h["lda"] // 2)
+    for kk in big:                                    # zero nibble kk of every weight row
+        a[:, kk // 2] &= 0xF0 if kk % 2 == 0 else 0x0F
+    x = (rng.standard_normal(h["ldb"] * n) * 2.0 ** -40).astype(np.float32)
+    x[big] = rng.choice([-1.0, 1.0, 1.5], big.size)   # token 0 only; token 1 stays within a few binades
+    x[h["ldb"]:] *= 2.0 ** 40
+    h["B"] = O.Dense(L.BF16, O.from_f32(x, L.BF16), h["ldb"])
+    exp = oracle_case(c, h, want_ref=True)
+    got, amax = run_gemm(c, h)
+    assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
+    check_bound(c, h, got, amax, exp)
+    assert np.abs(exp["ref64"][0]).max() < 1e-6       # token 0's outputs really are made of the small terms
+    assert kernel_status() == 0
 
 
 def test_extended_epilogue(pin):
