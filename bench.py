@@ -41,9 +41,34 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
+def source_hash(files):
+    """SHA-256 (first 16 hex digits) over the named kernel sources: what a DRAM-traffic figure captured under ncu belongs to."""
+    import hashlib
+    h = hashlib.sha256()
+    for f in sorted(files):
+        with open(os.path.join(ROOT, "nvfp4effma_b200", "csrc", f), "rb") as fh:
+            h.update(f.encode() + b"\0" + fh.read())
+    return h.hexdigest()[:16]
+
+
 def load_traffic():
+    """profiles/traffic.json: per kernel {"bytes": DRAM read + write bytes per launch (one ncu capture), "sources": the kernel's
+    source files, "hash": source_hash(sources) at the capture}.  A figure whose sources have changed since is stale: the
+    roofline then carries null, and `traffic_stamp` in the JSON line says which entries were current."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
-    return json.load(open(p)) if os.path.exists(p) else {}
+    if not os.path.exists(p):
+        return {}, {}
+    out, stamp = {}, {}
+    for key, e in json.load(open(p)).items():
+        if not isinstance(e, dict):
+            e = {"bytes": e}
+        try:
+            current = source_hash(e["sources"]) == e["hash"]
+        except (OSError, KeyError, TypeError):
+            current = False
+        out[key] = e.get("bytes") if current else None
+        stamp[key] = {"hash": e.get("hash"), "current": current}
+    return out, stamp
 
 
 class ClockSampler:
@@ -86,31 +111,73 @@ class ClockSampler:
 
 
 # ---- the reference arm: CPU block-sum emulation -----------------------------------------------------------------------------
+CPU_COLS = 256   # output columns of one host sample of the 4096^3 GEMM (1/16 of the workload)
+_cpu_operands = {}
+
+
 def cpu_gemm_sample(cols, threads):
     """One bounded sample of the W4A4 4096^3 GEMM on the host: `cols` output columns x all 4096 rows, k = 4096, through the
-    oracle (the reference's host emulation restated).  Returns seconds."""
+    oracle (the reference's host emulation restated).  The operands are built once, outside the timed call.  Returns seconds."""
     import numpy as np
     import oracle as O
-    rng = np.random.default_rng(2)
-    A = O.Fp4(M, K, glob=np.array([0.01], np.float32))
-    B = O.Fp4(cols, K, glob=np.array([0.01], np.float32))
-    for t in (A, B):
-        t.data[:] = rng.integers(0, 256, t.data.size, dtype=np.uint8)
-        t.scales[:] = rng.integers(0x20, 0x50, t.scales.size).astype(np.uint8)
+    if cols not in _cpu_operands:
+        rng = np.random.default_rng(2)
+        A = O.Fp4(M, K, glob=np.array([0.01], np.float32))
+        B = O.Fp4(cols, K, glob=np.array([0.01], np.float32))
+        for t in (A, B):
+            t.data[:] = rng.integers(0, 256, t.data.size, dtype=np.uint8)
+            t.scales[:] = rng.integers(0x20, 0x50, t.scales.size).astype(np.uint8)
+        _cpu_operands[cols] = (A, B)
+    A, B = _cpu_operands[cols]
     t0 = time.perf_counter()
     O.gemm(M, cols, K, A, B, D_dtype=O.BF16, nthreads=threads)
     return time.perf_counter() - t0
+
+
+def cpu_gemv_baseline(threads):
+    """The GEMV workload (8192 x 8192 NVFP4 weights, one BF16 activation vector) in full through the oracle, in the order of
+    the reference's GEMV kernel.  Returns (GB/s of weight bytes, seconds)."""
+    import numpy as np
+    import oracle as O
+    rng = np.random.default_rng(3)
+    A = O.Fp4(GEMV_M, GEMV_K, glob=np.array([0.01], np.float32))
+    A.data[:] = rng.integers(0, 256, A.data.size, dtype=np.uint8)
+    A.scales[:] = rng.integers(0x20, 0x50, A.scales.size).astype(np.uint8)
+    x = O.Dense(O.BF16, O.from_f32(rng.standard_normal(GEMV_K).astype(np.float32), O.BF16), GEMV_K)
+    t0 = time.perf_counter()
+    O.gemm(GEMV_M, 1, GEMV_K, A, x, D_dtype=O.BF16, order=1, nthreads=threads)
+    t = time.perf_counter() - t0
+    return (GEMV_M * GEMV_K // 2 + GEMV_M * GEMV_K // 16) / t / 1e9, t
+
+
+def cpu_quant_baseline(threads):
+    """The quantization workload (8192 x 8192, swizzled scales, amax computed) in full through the oracle.  Returns (GB/s of
+    the algorithmic bytes, seconds)."""
+    import numpy as np
+    import oracle as O
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((QUANT_R, QUANT_C)).astype(np.float32)
+    dst = O.Fp4(QUANT_R, QUANT_C, flags=O.SWIZZLED | O.GLOBAL_AMAX, glob=0.0)
+    t0 = time.perf_counter()
+    O.quantize(x, dst, compute_amax=True, nthreads=threads)
+    t = time.perf_counter() - t0
+    return (QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16) / t / 1e9, t
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    cols = 32
-    for _ in range(min(args.warmup, 1)):
+    cols = CPU_COLS
+    cpu_gemm_sample(cols, threads)   # builds the operands, warms the pages
+    t_one = cpu_gemm_sample(cols, threads)
+    while cols > 32 and t_one * args.steps > 150.0:   # keep the whole run within a few minutes whatever --steps asks
+        cols //= 2
         cpu_gemm_sample(cols, threads)
+        t_one = cpu_gemm_sample(cols, threads)
     ts = [cpu_gemm_sample(cols, threads) for _ in range(args.steps)]
-    t = sum(ts) / len(ts)
+    ts.sort()
+    t = ts[len(ts) // 2]
     tflops = 2.0 * M * cols * K / t / 1e12
     sample = f"{cols} of {N} output columns x {M} rows x k {K} per step (exact block sums), scaled linearly"
     line = {"impl": "reference", "metric": "w4a4_gemm_4096_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
@@ -148,6 +215,38 @@ def time_steps(fn, steps, warmup, stream, dist, world):
     return ms
 
 
+def time_groups(fn, steps, warmup, groups, dist, world):
+    """The headline timing: `warmup` direct calls, then fn(0..steps-1) captured into one CUDA graph (no host time between the
+    kernels), one untimed replay, then `groups` replays, each a group of exactly `steps` steps timed by its own pair of CUDA
+    events.  Returns the groups' times in ms (max over ranks per group) and the launches issued on this rank."""
+    import torch
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(steps):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(groups):
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    if world > 1:
+        t = torch.tensor(ts, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ts = [float(v) for v in t]
+    return ts, warmup + steps * (groups + 1)
+
+
 def time_graph(fn, calls, replays, warmup, dist, world):
     """Kernels of a few microseconds: `calls` launches of fn(i) captured into one CUDA graph (the host's ctypes overhead per
     call would otherwise exceed the kernel), replayed `replays` times after `warmup` direct calls; CUDA events around each
@@ -181,6 +280,60 @@ def time_graph(fn, calls, replays, warmup, dist, world):
     return ms, warmup + calls * (replays + 2)
 
 
+def fp4_mma_ceiling(L, dev):
+    """TFLOP/s of the bare FP4 MMA stream (CTA pairs, N = 256): one launch of 4 x 4096 MMAs per SM, timed by events."""
+    import torch
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    cyc = torch.zeros(2 * sms, dtype=torch.int64, device=dev)
+    iters, flags = 4096, 16 | 1   # issued by an elected lane of a converged warp, one commit per four MMAs as a GEMM's main loop
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    best = None
+    for i in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        L.check(L.lib.nvfp4a_b200_mma_ceiling(256, 1, iters, flags, ctypes.c_void_p(cyc.data_ptr()), stream))
+        e1.record()
+        torch.cuda.synchronize()
+        if i:
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+    flops = (sms // 2 * 2) * 4 * iters * 2.0 * 128 * 256 * 64
+    return flops / (best * 1e-3) / 1e12
+
+
+def reference_cuda_core(L, W, A, B, D, dev):
+    """Context only: the reference library's own nvfp4a_gemm (its CUDA-core DP4A kernel, NVFP4A_DP4A=1) on the same 4096^3
+    operands, when the library built from the reference's sources travelled with the repository."""
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libnvfp4effma_ref.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/libnvfp4effma_ref.so was not built"}
+    os.environ["NVFP4A_DP4A"] = "1"
+    ref = ctypes.CDLL(so)
+    ref.nvfp4a_gemm.restype, ref.nvfp4a_gemm.argtypes = L.lib.nvfp4a_gemm.restype, L.lib.nvfp4a_gemm.argtypes
+    tD = W.tensor(D, L.BF16)
+
+    def call():
+        st = ref.nvfp4a_gemm(M, N, K, 1.0, ctypes.byref(A), K, ctypes.byref(B), K, 0.0, None, 0, ctypes.byref(tD), M, None, W.stream_ptr())
+        if st != 0:
+            raise RuntimeError(f"reference nvfp4a_gemm returned {st}")
+
+    try:
+        call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+    except (RuntimeError, OSError) as exc:
+        return {"unavailable": str(exc)}
+    ms = e0.elapsed_time(e1) / 3
+    return {"entry": "the reference library's nvfp4a_gemm, NVFP4A_DP4A=1 (its exact DP4A CUDA-core kernel), built for sm_100 from its own sources",
+            "ms_per_call": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "calls": 3}
+
+
 def hbm_entry(name, bytes_per_call, ms, world, peaks, traffic, key, workload, l2, **more):
     gbs = bytes_per_call / (ms * 1e-3) / 1e9
     d = {"metric": name, "value": gbs * world, "unit": "GB/s", "us_per_call": ms * 1e3,
@@ -203,11 +356,13 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.current_stream()
     peaks = load_peaks()
-    traffic = load_traffic()
+    traffic, traffic_stamp = load_traffic()
     launches = 0
     only = args.only
     if args.pair != -1:
         assert L.lib.nvfp4a_b200_set_pair(args.pair) == 0
+    if args.no_pdl:
+        L.lib.nvfp4a_b200_set_pdl(0)
 
     # ---- GEMM W4A4 4096^3: rotating sets (inputs 18.9 MB + D 33.6 MB each; 3 sets > 126 MB of L2) ----
     nsets = 3
@@ -229,16 +384,25 @@ def run_ours(args, rank, world, local_rank):
         t_wait = time.perf_counter()
         while not sampler.rows and time.perf_counter() - t_wait < 3.0:   # nvidia-smi needs a moment before its first sample
             time.sleep(0.05)
-    ms = time_steps(gemm_step, args.steps, args.warmup, stream, dist, world)
-    launches += args.steps + args.warmup
+    groups = 5
+    group_ms, n = time_groups(gemm_step, args.steps, args.warmup, groups, dist, world)
+    launches += n
+    ms = sorted(group_ms)[groups // 2]   # the median group of exactly --steps steps
     ms_step = ms / args.steps
     tflops = 2.0 * M * N * K * world / (ms_step * 1e-3) / 1e12
     peak_fp4 = 4.0 * peaks["bf16_tflops"]
     per_gpu = tflops / world
+    ceiling = fp4_mma_ceiling(L, dev)   # what the FP4 MMA instruction itself sustains on this GPU, measured now
+    launches += 3
     roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak_fp4, "unit": "TFLOP/s", "frac": per_gpu / peak_fp4,
                 "traffic": traffic.get("w4a4_gemm_4096_dram_bytes"),
-                "peak_note": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']:.0f} TF/s): no fp4 figure is measured; "
-                             f"of nominal 9000 TF/s: {per_gpu / NOMINAL_FP4_TFLOPS:.3f}"}
+                "peak_note": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']:.0f} TF/s): no fp4 figure is in the measured peaks",
+                "fp4_mma_ceiling_tflops": ceiling, "frac_of_fp4_mma_ceiling": per_gpu / ceiling if ceiling else None,
+                "frac_of_nominal_9000": per_gpu / NOMINAL_FP4_TFLOPS,
+                "ceiling_note": "tcgen05.mma kind::mxf4nvf4 cta_group::2 256 x 256 x 64 issued back to back on every SM, no loads, "
+                                "no epilogue (nvfp4a_b200_mma_ceiling), timed by CUDA events in this run"}
+    timing = {"method": f"CUDA graph of --steps GEMMs; {groups} replays, each timed by its own events; headline = median group",
+              "group_ms": group_ms, "min_ms_per_step": min(group_ms) / args.steps, "max_ms_per_step": max(group_ms) / args.steps}
 
     # ---- e2e: host operands, copies inside the timed region ----
     A, B, D, tA, tB = sets[0]
@@ -261,9 +425,12 @@ def run_ours(args, rank, world, local_rank):
     launches += e2e_steps + 3
     e2e = {"value": 2.0 * M * N * K * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": ms_e2e}
+    extra = {}
+    if rank == 0 and world == 1 and only == "all" and not args.no_cpu:
+        extra["reference_cuda_core_b200"] = reference_cuda_core(L, W, tA, tB, D, dev)
+        launches += 4 if "ms_per_call" in extra["reference_cuda_core_b200"] else 0
     del sets, hA, hB, hD
 
-    extra = {}
     # ---- GEMV 8192^2 batch 1 (W4A16): 8 distinct weights = 302 MB > L2; the image entry is what TCWeight decodes through ----
     if only in ("all", "gemv"):
         nw = 8
@@ -302,7 +469,7 @@ def run_ours(args, rank, world, local_rank):
         qbytes = QUANT_R * QUANT_C * 2 + QUANT_R * QUANT_C // 2 + QUANT_R * QUANT_C // 16
         ms_q, n1 = time_graph(lambda i: W.quantize_amax_swizzled(xs[i % nx], out), 24, 7, 5, dist, world)
         ms_qg, n2 = time_graph(lambda i: W.quantize_given_amax(xs[i % nx], out), 24, 7, 5, dist, world)
-        launches += 3 * n1 + n2   # amax computed: memset + amax kernel + encode kernel per call
+        launches += n1 + n2   # amax computed: one cooperative kernel per call (amax, grid barrier, encode)
         extra["quant_8192"] = hbm_entry("quantize_bf16_nvfp4_8192x8192_gbs", qbytes, ms_q, world, peaks, traffic, "quant_8192_dram_bytes",
                                         "quantize_ex_8192x8192_bf16_swizzled_amax_computed", "3 rotating inputs (403 MB) > L2",
                                         timing="CUDA graph of 24 calls, median of 7 replays",
@@ -314,11 +481,11 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- fused transformer-MLP GEMMs (W4A16, extended epilogue) at 2048 tokens ----
     if not args.no_mlp and only in ("all", "mlp"):
-        extra["mlp_w4a16"] = bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks)
+        extra["mlp_w4a16"] = bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks, traffic)
         launches += extra["mlp_w4a16"].pop("_launches")
     # ---- tensor-parallel decoder linear stack ----
     if not args.no_tp and only in ("all", "tp"):
-        extra["tp_llama8b_linears"] = bench_tp(args, dev, rank, world, dist, stream, peaks)
+        extra["tp_llama8b_linears"] = bench_tp(args, dev, rank, world, dist, stream, peaks, L)
         launches += extra["tp_llama8b_linears"].pop("_launches")
 
     clocks = sampler.stop() if rank == 0 else None
@@ -332,16 +499,25 @@ def run_ours(args, rank, world, local_rank):
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu and only == "all":
         threads = os.cpu_count() or 1
-        cols = 32
-        cpu_gemm_sample(4, threads)
+        cols = CPU_COLS
+        cpu_gemm_sample(cols, threads)   # builds the operands, warms the pages
+        ts = []
         t0 = time.perf_counter()
-        reps = 0
-        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
-            cpu_gemm_sample(cols, threads)
-            reps += 1
-        t = (time.perf_counter() - t0) / reps
+        while len(ts) < 3 or (time.perf_counter() - t0 < 12.0 and len(ts) < 40):
+            ts.append(cpu_gemm_sample(cols, threads))
+        ts.sort()
+        t = ts[len(ts) // 2]
         cpu = {"value": 2.0 * M * cols * K / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-               "sample": f"{reps} x ({cols} of {N} output columns x {M} rows x k {K}) through the oracle's exact block sums, incl. operand set-up"}
+               "sample": f"median of {len(ts)} x ({cols} of {N} output columns x {M} rows x k {K}) through the oracle's exact block sums; "
+                         "operands built outside the timed call"}
+        if "gemv_8192_b1" in extra:
+            gbs, sec = cpu_gemv_baseline(threads)
+            extra["gemv_8192_b1"]["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "seconds": sec,
+                                                     "sample": "the whole workload once (8192 x 8192 x 1) through the oracle, in the order of the reference's GEMV kernel"}
+        if "quant_8192" in extra:
+            gbs, sec = cpu_quant_baseline(threads)
+            extra["quant_8192"]["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "seconds": sec,
+                                                   "sample": "the whole workload once (8192 x 8192 FP32 -> NVFP4, amax computed, swizzled scales) through the oracle"}
 
     if rank == 0:
         line = {"metric": "w4a4_gemm_4096_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -350,13 +526,20 @@ def run_ours(args, rank, world, local_rank):
                 "config": {"workload": "w4a4_gemm_m4096_n4096_k4096", "entry": "nvfp4a_gemm",
                            "scales": "E4M3 1x16 in the cuBLASLt GEMM-swizzled layout, FP32 decode-factor globals",
                            "l2": f"{nsets} rotating operand/output sets (157 MB) > L2", "per_rank": "independent GEMMs, no collective"},
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "kernel_status": status, "extra": extra}
+                "roofline": roofline, "timing": timing, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+                "kernel_status": status, "traffic_stamp": traffic_stamp, "extra": extra}
+        tp = extra.get("tp_llama8b_linears", {})
+        if "tp_efficiency" in tp:
+            line["tp_efficiency"] = tp["tp_efficiency"]
         print(json.dumps(line), flush=True)
+        parity_failed = tp.get("parity", "bit-exact") != "bit-exact"
     if world > 1:
         dist.destroy_process_group()
+    if rank == 0 and parity_failed:
+        sys.exit("bench: the sharded linear stack differs from the unsharded one (see extra.tp_llama8b_linears.parity)")
 
 
-def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks):
+def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks, traffic):
     """gate / up (RMSNorm column scale + SwiGLU + bias + amax) and down (second output + sums of squares) of a Llama-3-8B MLP
     through nvfp4a_gemm_tc_ex: NVFP4 weights, 2048 BF16 tokens."""
     import torch
@@ -427,11 +610,12 @@ def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks):
             "gate_up_w4a8": {"entry": "nvfp4a_gemm_ex, INT8 activations", "kernel": "DP4A tiled GEMM (exact block sums, CUDA cores)", "ms": ms_gu8,
                              "tflops": tf(f_gu, ms_gu8)},
             "roofline": {"bound": "tensor", "achieved": tf(f_gu + f_dn, ms_gu + ms_dn), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": tf(f_gu + f_dn, ms_gu + ms_dn) / peaks["bf16_tflops"], "traffic": None},
+                         "frac": tf(f_gu + f_dn, ms_gu + ms_dn) / peaks["bf16_tflops"], "traffic": traffic.get("mlp_w4a16_dram_bytes"),
+                         "traffic_note": "one gate / up launch plus one down launch"},
             "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1 + 5}
 
 
-def bench_tp(args, dev, rank, world, dist, stream, peaks):
+def bench_tp(args, dev, rank, world, dist, stream, peaks, L):
     """Llama-3-8B-shaped linear stack, weights sharded by output rows over the ranks, NCCL all-gather per layer: decode
     (1 and 8 tokens, the whole step in one CUDA graph when the collectives capture) and prefill (4096 tokens)."""
     import torch
@@ -467,6 +651,8 @@ def bench_tp(args, dev, rank, world, dist, stream, peaks):
                     "cuda_graph": graph is not None}
         out["_launches"] += 4 * layers * (steps + 6)
 
+    if world > 1:
+        out["parity"] = tp_parity(stack, dev, dist, L)
     decode(1, "decode_1")
     decode(8, "decode_8")
     if world > 1 and stack.collective == "peer":   # the same step with NCCL all-gathers, for comparison
@@ -484,7 +670,65 @@ def bench_tp(args, dev, rank, world, dist, stream, peaks):
         out["prefill_4096"] = {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "tflops_all_ranks": tfl,
                                "frac_of_bf16_peak_all_ranks": tfl / (peaks["bf16_tflops"] * world)}
         out["_launches"] += 8 * layers * (steps + 2)
+    if world > 1:
+        # strong scaling of this stack: the same layers unsharded on one GPU (every rank times its own copy; the slowest counts)
+        del stack
+        torch.cuda.empty_cache()
+        solo = TPDecoderLinears(layers=layers, group=None, seed=4, device=dev, replicate=True)
+        h1 = torch.randn((1, 4096), generator=torch.Generator(device=dev).manual_seed(41), device=dev).bfloat16()
+        for _ in range(2):
+            solo(h1)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            solo(h1)
+        gr.replay()
+        t1_decode = time_steps(lambda i: gr.replay(), 20, 3, stream, dist, world) / 20
+        eff = {"definition": "t_1 / (N * t_N): one GPU running the whole unsharded stack against N GPUs running their shards",
+               "decode_1": {"t1_ms": t1_decode, "tN_ms": out["decode_1"]["ms_per_step"], "efficiency": t1_decode / (world * out["decode_1"]["ms_per_step"])}}
+        out["_launches"] += 4 * layers * 26
+        if "prefill_4096" in out:
+            hp = torch.randn((4096, 4096), generator=torch.Generator(device=dev).manual_seed(44), device=dev).bfloat16()
+            solo(hp)
+            t1_prefill = time_steps(lambda i: solo(hp), 3, 1, stream, dist, world) / 3
+            eff["prefill_4096"] = {"t1_ms": t1_prefill, "tN_ms": out["prefill_4096"]["ms_per_step"],
+                                   "efficiency": t1_prefill / (world * out["prefill_4096"]["ms_per_step"])}
+            out["_launches"] += 8 * layers * 5
+        out["tp_efficiency"] = eff
     return out
+
+
+def tp_parity(stack, dev, dist, L):
+    """Sharded against unsharded, bit for bit, on the first two layers of the benchmark's own stack (full Llama-3-8B shapes):
+    1, 8 and 64 tokens through the peer-memory all-gather (with the fused prefill GEMM at 64 tokens) and through NCCL.  The
+    decode GEMVs are pinned to one kernel for the comparison: left to itself the library gives a 28672-row unsharded layer to
+    the FP4 tensor-core GEMV and its shards to the mma.sync GEMV, which add in different orders (both within the accumulation
+    bound, not bit-identical to each other).  Returns "bit-exact" or a description of the first difference."""
+    import torch
+    from nvfp4effma_b200.tp import TPDecoderLinears
+    solo = TPDecoderLinears(layers=2, group=None, seed=4, device=dev, replicate=True)
+    bad = []
+    L.lib.nvfp4a_b200_set_route(2)
+    try:
+        for T in (1, 8, 64):
+            h = torch.randn((T, 4096), generator=torch.Generator(device=dev).manual_seed(70 + T), device=dev).bfloat16()
+            want = solo(h, layers=2)
+            modes = ["peer", "nccl"] if stack.collective == "peer" else [stack.collective]
+            for mode in modes:
+                stack.set_collective(mode)
+                got = stack(h, layers=2).clone()
+                if not torch.equal(got, want):
+                    bad.append(f"{mode} T={T}: {int((got != want).sum())} of {got.numel()} values differ")
+            stack.set_collective(modes[0])
+    finally:
+        L.lib.nvfp4a_b200_set_route(0)
+    flag = torch.tensor([len(bad)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    del solo
+    torch.cuda.empty_cache()
+    if int(flag[0]) == 0:
+        return "bit-exact"
+    return "MISMATCH: " + ("; ".join(bad) if bad else "on another rank")
 
 
 def main():
@@ -500,6 +744,7 @@ def main():
     ap.add_argument("--tp-layers", type=int, default=32)
     ap.add_argument("--pair", type=int, default=-1, choices=[-1, 0, 1],
                     help="W4A4 GEMM: -1 automatic, 0 single-CTA tiles only, 1 CTA pairs wherever they apply (tuning aid)")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization (tuning aid)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "gemv", "quant", "mlp", "tp"],
                     help="run one workload only (for profiling captures); the JSON line then lacks the others")
     args = ap.parse_args()

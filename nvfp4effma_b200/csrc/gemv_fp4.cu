@@ -191,12 +191,17 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   if (warp == 0) {
     // ---------------- producer: after the first fill, each stage as its slot comes free ----------------
+    int requested = early;
     for (int it = early; it < nloc; ++it) {
       const int s = it % kStages;
       const bool okw = wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty);
       if (!__all_sync(0xFFFFFFFFu, okw)) break;
       request_stage(it);
+      requested = it + 1;
     }
+    // No copy may be in flight when the CTA leaves.  On the normal path every fill has long been consumed and these waits return
+    // at once; after a wait somewhere gave up they hold the CTA (bounded) until the last requested fill of every stage has landed.
+    for (int it = requested - 1; it >= 0 && it >= requested - kStages; --it) mbar_wait(&full[it % kStages], (it / kStages) & 1);
   } else if (warp == 1) {
     // ---------------- MMA issuer: D[piece][weight row] += pieces (A, M = 128) x weights (B, N = 256) ----------------
     // The whole warp runs the loop and one elected lane issues: from inside a one-lane branch every tcgen05 instruction costs the
@@ -384,9 +389,12 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     if (exact && linear && (warp & 3) != 0 && warp >= 5) {
       // ---------------- warps 5, 6, 7, 9: linear block scales [256 rows][16 bytes] -> the eight 512-byte tiles of the stage ----------------
+      // A stage belongs to one warp for the whole launch: a wait on the parity of fill f is only meaningful to a thread that
+      // has seen fill f - 1 complete (on a barrier still in its first phase, a wait for the second fill's parity returns at once).
       const int w = warp == 9 ? 3 : warp - 5;
-      for (int it = w; it < nloc; it += 4) {
+      for (int it = 0; it < nloc; ++it) {
         const int s = it % kStages;
+        if ((s & 3) != w) continue;
         if (!wait(&full[s], (it / kStages) & 1, kStWaitRetile)) break;
         uint8_t *st = stages + (size_t)s * stage_bytes;
         const uint8_t *raw = st + kStageBytes;

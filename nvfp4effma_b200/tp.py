@@ -260,10 +260,11 @@ class TPDecoderLinears:
     def weight_bytes_local(self) -> int:
         return sum(m.image.numel() for layer in self.layers for m in layer)
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, layers: int | None = None) -> torch.Tensor:
+        """``layers``: run only the first that many decoder layers (parity checks against an unsharded stack)."""
         if self.collective == "peer" and h.shape[0] > self.max_tokens:
             raise ValueError(f"{h.shape[0]} tokens exceed the peer buffers ({self.max_tokens})")
-        for qkv, o, gate_up, down in self.layers:   # consecutive layers alternate between the two peer buffers
+        for qkv, o, gate_up, down in self.layers[:layers]:   # consecutive layers alternate between the two peer buffers
             a = qkv(h, 0)[:, :self.hidden]
             h = down(gate_up(o(a, 1), 0), 1)
         return h

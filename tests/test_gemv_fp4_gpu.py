@@ -117,6 +117,46 @@ def test_large_activations_that_meet_zero_weights(pin, linear):
     assert kernel_status() == 0
 
 
+def test_linear_scales_back_to_back_at_the_benchmark_size():
+    """8192 x 8192 weights with linear block scales, automatic split, 300 launches back to back in one CUDA graph (as a decode
+    step issues them): every launch gives the bytes of the first, and those are within the bound of the oracle.  The stages of
+    the weight ring land in any order here; a warp that re-tiles scales must not take a stage's second fill for its first."""
+    from util import rand_fp4
+    m, n, k = 8192, 1, 8192
+    c = Case(m, n, k, L.BF16, L.BF16, -1, -1, 1.0, 0.0)
+    h = build_case(c, 995)
+    rng = np.random.default_rng(996)
+    h["A"] = rand_fp4(rng, m, k, ld=h["lda"], ld_scale=k // 16, glob=0.375)
+    exp = oracle_case(c, h, want_ref=True)
+    got, amax = run_gemm(c, h)
+    assert L.lib.nvfp4a_b200_last_route() == FP4_GEMV
+    check_bound(c, h, got, amax, exp)
+    dA = DevFp4(h["A"])
+    tA, x = dA.tensor(), dev(h["B"].raw)
+    tx = tensor(x, L.BF16)
+    outs = [torch.zeros(h["ldd"], dtype=torch.int16, device="cuda") for _ in range(50)]
+    touts = [tensor(o, L.BF16) for o in outs]
+
+    def launch(i):
+        st = L.lib.nvfp4a_gemm(m, n, k, 1.0, ctypes.byref(tA), h["lda"], ctypes.byref(tx), h["ldb"], 0.0, None, 0, ctypes.byref(touts[i]), h["ldd"],
+                               None, stream())
+        assert st == 0, L.lib.nvfp4a_last_error()
+
+    launch(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(50):
+            launch(i)
+    for _ in range(6):
+        g.replay()
+    torch.cuda.synchronize()
+    assert kernel_status() == 0
+    first = outs[0][:m].cpu()
+    assert np.array_equal(first.numpy().view(np.uint16), got.reshape(-1)[:m])
+    assert all(torch.equal(o[:m].cpu(), first) for o in outs[1:])
+
+
 def test_extended_epilogue(pin):
     pin(2)
     v = 0
