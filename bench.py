@@ -712,13 +712,14 @@ def tp_parity(stack, dev, dist, L):
     try:
         for T in (1, 8, 64):
             h = torch.randn((T, 4096), generator=torch.Generator(device=dev).manual_seed(70 + T), device=dev).bfloat16()
-            want = solo(h, layers=2)
+            want = solo(h, layers=2, collect=True)
             modes = ["peer", "nccl"] if stack.collective == "peer" else [stack.collective]
             for mode in modes:
                 stack.set_collective(mode)
-                got = stack(h, layers=2).clone()
-                if not torch.equal(got, want):
-                    bad.append(f"{mode} T={T}: {int((got != want).sum())} of {got.numel()} values differ")
+                got = stack(h, layers=2, collect=True)
+                for li, (g, w) in enumerate(zip(got, want)):
+                    if not torch.equal(g, w):
+                        bad.append(f"{mode} T={T} layer {li}: {int((g != w).sum())} of {g.numel()} values differ")
             stack.set_collective(modes[0])
     finally:
         L.lib.nvfp4a_b200_set_route(0)

@@ -141,7 +141,8 @@ static BOperand make_b(const nvfp4a_tensor *B, int ldb, int ldsb, int k, bool im
 // nvfp4a_gemm / nvfp4a_gemm_ex
 static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B, int ldb,
                               float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias,
-                              const EpilogueEx &ex, cudaStream_t stream, bool validate_only = false) {
+                              const EpilogueEx &ex, cudaStream_t stream, bool validate_only = false, int a_groups = 1, GemmArgs *args_out = nullptr) {
+  // a_groups > 1 (nvfp4a_gemm_grouped): A holds a_groups stacked weights of m rows; nothing is launched, the arguments go to args_out
   if (!A || !B || !D || !A->data || !B->data || !D->data) return fail(NVFP4A_INVALID_VALUE, "%s: A, B or D (or its data pointer) is NULL", fn);
   if (m < 0 || n < 0 || k < 0) return fail(NVFP4A_INVALID_VALUE, "%s: negative size (m = %d, n = %d, k = %d)", fn, m, n, k);
   if (A->dtype != NVFP4A_NVFP4) return fail(NVFP4A_NOT_SUPPORTED, "%s: A must be NVFP4 (dtype %d)", fn, (int)A->dtype);
@@ -164,7 +165,7 @@ static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, 
     if (!aligned(t->block_scale, al) || t->ld_scale % 4 || (t->ld_scale && t->ld_scale < k / 16))
       return fail(NVFP4A_INVALID_VALUE, "%s: block scales of %s must be %u-byte aligned, ld_scale a multiple of 4 and >= k / 16 (ld_scale = %d)",
                   fn, which ? "B" : "A", al, t->ld_scale);
-    if (nvfp4a_status st = check_scales(fn, which ? "B" : "A", t, which ? n : m, k, which ? &ldsb : &ldsa)) return st;
+    if (nvfp4a_status st = check_scales(fn, which ? "B" : "A", t, which ? n : m * a_groups, k, which ? &ldsb : &ldsa)) return st;
   }
   if (nvfp4a_status st = check_epilogue_operands(fn, m, beta, C, ldc, D, ldd, bias, ex.mask)) return st;
   if (nvfp4a_status st = check_device()) return st;
@@ -181,7 +182,8 @@ static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, 
   g.B = make_b(B, ldb, ldsb, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
-  if (validate_only) return NVFP4A_OK;
+  if (args_out) *args_out = g;
+  if (validate_only || args_out) return NVFP4A_OK;
   return dispatch(fn, g, stream);
 }
 
@@ -361,10 +363,24 @@ extern "C" nvfp4a_status nvfp4a_gemm_dual(int m, int n, int k, float alpha, cons
   return nvfp4a_gemm(m, n, k, alpha, a, trans_a ? A->ld_col : A->ld_row, b, trans_b ? B->ld_col : B->ld_row, beta, C, ldc, D, ldd, bias, stream);
 }
 
-extern "C" nvfp4a_status nvfp4a_gemm_grouped(int, int, int, int, float, const nvfp4a_tensor *, int, const nvfp4a_tensor *, int, float,
-                                             const nvfp4a_tensor *, int, const nvfp4a_tensor *, int, const nvfp4a_tensor *, const int *, cudaStream_t) {
+extern "C" nvfp4a_status nvfp4a_gemm_grouped(int groups, int m, int k, int rows, float alpha, const nvfp4a_tensor *A, int lda, const nvfp4a_tensor *B,
+                                             int ldb, float beta, const nvfp4a_tensor *C, int ldc, const nvfp4a_tensor *D, int ldd,
+                                             const nvfp4a_tensor *bias, const int *seg, cudaStream_t stream) {
   clear_error();
-  return fail(NVFP4A_NOT_SUPPORTED, "nvfp4a_gemm_grouped: the grouped (mixture-of-experts) GEMM is not part of this build");
+  const char *fn = "nvfp4a_gemm_grouped";
+  if (groups < 0 || rows < 0) return fail(NVFP4A_INVALID_VALUE, "%s: negative groups = %d or rows = %d", fn, groups, rows);
+  if (groups > 0 && m > 0 && (long long)groups * m > 0x7FFFFFFFll) return fail(NVFP4A_INVALID_VALUE, "%s: groups * m = %d * %d exceeds 2^31 - 1", fn, groups, m);
+  if (groups == 0) return NVFP4A_OK;
+  if (rows > 0 && m > 0 && !seg) return fail(NVFP4A_INVALID_VALUE, "%s: seg is NULL", fn);
+  GemmArgs g;
+  memset(&g, 0, sizeof g);
+  const EpilogueEx none = {};
+  // the checks of nvfp4a_gemm with A taken as [groups * m][k]; an empty problem returns before anything is filled in
+  if (nvfp4a_status st = gemm_run(fn, m, rows, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, none, stream, false, groups, &g)) return st;
+  if (m == 0 || rows == 0) return NVFP4A_OK;
+  // Every group runs the CUDA-core kernel in the reference's tiled order: the bytes of nvfp4a_gemm's tiled kernel for that group.
+  g_last_route = 1;
+  return cuda_fail(launch_gemm_grouped(g, seg, groups, stream), "nvfp4a_gemm_grouped: kernel launch");
 }
 
 extern "C" size_t nvfp4a_tc_image_bytes(int operand, nvfp4a_dtype dtype, int rows, int k) {

@@ -12,7 +12,11 @@ namespace nvb {
 
 constexpr int GR = 16, GC = 16, GK = 64;  // rows, columns, k per staging step
 
-__global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g) {
+// GROUPED (nvfp4a_gemm_grouped, reference include/nvfp4effma.h:104-116): A is the stack of `groups` weights of g.m rows each,
+// group q owns the columns (rows of B, D, C) [seg[q], seg[q + 1]); blockIdx.x counts 16-column tiles over the groups in order, each
+// group's last tile partial, and the CTA finds its group by walking seg (device memory: the row counts never visit the host).
+template <bool GROUPED>
+__global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g, const int *__restrict__ seg, int groups) {
   __shared__ __align__(16) int8_t a_i8[GR][GK];
   __shared__ float a_sc[GR][GK / 16];
   __shared__ __align__(16) int8_t b_i8[GC][GK];
@@ -22,7 +26,21 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g) {
   __shared__ float colscale[GC];
 
   const int tid = threadIdx.x, ri = tid & 15, cj = tid >> 4;
-  const int i0 = blockIdx.y * GR, j0 = blockIdx.x * GC;
+  int j0 = blockIdx.x * GC, ro = 0;   // ro: first row of this group's weight in the stacked A (and in its per-row globals, bias)
+  if (GROUPED) {
+    int t = blockIdx.x, q = 0, lo = 0, hi = 0;
+    for (; q < groups; ++q) {
+      lo = seg[q]; hi = seg[q + 1];
+      const int tiles = (hi - lo + GC - 1) / GC;
+      if (t < tiles) break;
+      t -= tiles;
+    }
+    if (q == groups || hi > g.n) return;   // past the last group's tiles (the grid is sized for the worst case), or seg beyond `rows`
+    j0 = lo + t * GC;
+    g.n = hi;
+    ro = q * g.m;
+  }
+  const int i0 = blockIdx.y * GR;
   const int i = i0 + ri, j = j0 + cj;
   const int bt = g.B.dtype;
   const bool fp4b = bt == NVFP4A_NVFP4, q8b = bt == NVFP4A_INT8, blocked = fp4b || q8b;
@@ -47,7 +65,7 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g) {
         const int row = i0 + rr;
         uint2 w = make_uint2(0, 0);
         float sc = 0.f;
-        if (row < g.m && kin) { w = g.A.block(row, kb); sc = scale_to_f32(g.A.scale_code(row, kb), ue_a); }
+        if (row < g.m && kin) { w = g.A.block(ro + row, kb); sc = scale_to_f32(g.A.scale_code(ro + row, kb), ue_a); }
 #pragma unroll
         for (int e = 0; e < 16; ++e) a_i8[rr][16 * bb + e] = (int8_t)e2m1_x2(((e < 8 ? w.x : w.y) >> (4 * (e & 7))) & 15u);
         a_sc[rr][bb] = sc;
@@ -103,7 +121,13 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g) {
   if (live) {
     float colp = epi_col_part(e, j);
     if (g.x.mask & kExNorm) colp = __fmul_rn(colp, colscale[cj]);
-    v = epi_value(e, i, j, acc, epi_scale(e, epi_row_part(e, i), colp));
+    if (GROUPED) {
+      v = __fmul_rn(acc, epi_scale(e, epi_row_part(e, ro + i), colp));
+      if (e.bias) v = __fadd_rn(v, load_dense(e.bias_dtype, e.bias, ro + i));
+      if (e.beta != 0.f) v = __fmaf_rn(e.beta, load_dense(e.c_dtype, e.c, (size_t)j * e.ldc + i), v);
+    } else {
+      v = epi_value(e, i, j, acc, epi_scale(e, epi_row_part(e, i), colp));
+    }
   }
   if (!(g.x.mask & (kExSwiglu | kExOut2))) {
     if (live) { store_dense(e.d_dtype, e.d, (size_t)j * e.ldd + i, v); amax = fabsf(v); }
@@ -138,7 +162,15 @@ cudaError_t launch_gemm_generic(const GemmArgs &g, cudaStream_t s) {
   // grid.y is limited to 65535 slices of 16 rows (m up to ~1M), grid.x unbounded in practice
   const dim3 grid((g.n + GC - 1) / GC, (g.m + GR - 1) / GR);
   if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-  gemm_generic_kernel<<<grid, 256, 0, s>>>(g);
+  gemm_generic_kernel<false><<<grid, 256, 0, s>>>(g, nullptr, 0);
+  return cudaGetLastError();
+}
+
+// g.m = rows of ONE group's weight, g.n = the bound `rows` on seg[groups]; every group may end in a partial tile
+cudaError_t launch_gemm_grouped(const GemmArgs &g, const int *seg, int groups, cudaStream_t s) {
+  const dim3 grid((g.n + GC - 1) / GC + groups, (g.m + GR - 1) / GR);
+  if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+  gemm_generic_kernel<true><<<grid, 256, 0, s>>>(g, seg, groups);
   return cudaGetLastError();
 }
 

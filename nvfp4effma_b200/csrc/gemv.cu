@@ -131,8 +131,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
   };
 
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int st = warp; st < nsteps; st += kGemvWarps) {
-    const GemvStep cur = load_step(st);
+  auto consume = [&](const GemvStep &cur) {
     const uint32_t S0[2] = {lut[cur.sc0 & 0xFF], lut[(cur.sc0 >> 8) & 0xFF]}, S1[2] = {lut[cur.sc1 & 0xFF], lut[(cur.sc1 >> 8) & 0xFF]};
     const uint32_t ww0[4] = {cur.w0.x, cur.w0.y, cur.w0.z, cur.w0.w}, ww1[4] = {cur.w1.x, cur.w1.y, cur.w1.z, cur.w1.w};
 #pragma unroll
@@ -146,7 +145,21 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
       mma_bf16_16816(acc, bf16x2_mul(decode_pair<2>(a), sa), bf16x2_mul(decode_pair<2>(b), sb), bf16x2_mul(decode_pair<3>(a), sa),
                      bf16x2_mul(decode_pair<3>(b), sb), x26, x37);
     }
+  };
+  // Four of the warp's steps are requested before the first is consumed: a 16-row slice is short (k = 4096 is four steps per
+  // warp), so without this every warp would have one step's 1 KiB in flight and wait out a full memory latency per step.
+  // The steps are consumed in their order, so the sums are those of a plain loop.
+  int st = warp;
+  for (; st + 3 * kGemvWarps < nsteps; st += 4 * kGemvWarps) {
+    const GemvStep s0 = load_step(st), s1 = load_step(st + kGemvWarps), s2 = load_step(st + 2 * kGemvWarps), s3 = load_step(st + 3 * kGemvWarps);
+    consume(s0); consume(s1); consume(s2); consume(s3);
   }
+  if (st + kGemvWarps < nsteps) {
+    const GemvStep s0 = load_step(st), s1 = load_step(st + kGemvWarps);
+    consume(s0); consume(s1);
+    st += 2 * kGemvWarps;
+  }
+  for (; st < nsteps; st += kGemvWarps) consume(load_step(st));
   // partial sums of this warp: c0, c1 -> (row gq, columns 2 q, 2 q + 1); c2, c3 -> row gq + 8
   part[warp][gq][2 * q] = acc[0]; part[warp][gq][2 * q + 1] = acc[1];
   part[warp][gq + 8][2 * q] = acc[2]; part[warp][gq + 8][2 * q + 1] = acc[3];

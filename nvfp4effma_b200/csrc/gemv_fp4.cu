@@ -94,7 +94,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
   uint32_t *wmax = tmem_slot + 2;                          // [8 warps][NTOK] largest |x| bit pattern
   volatile int *inexact = (volatile int *)(wmax + 8 * NTOK);   // some activation of this CTA does not fit the digit planes
-  int *consumed = (int *)(wmax + 8 * NTOK + 1);                // warps done with a stage (the CUDA-core consumer)
+  int *consumed = (int *)(wmax + 8 * NTOK + 1);                // [stage] warps done with the stage (the CUDA-core consumer)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gm = g.m, gn = g.n;
@@ -143,7 +143,7 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     mbar_init(pieces_ready, kDecompThreads / 32);
     *abort_flag = 0;
     *inexact = 0;
-    *consumed = 0;
+    for (int s = 0; s < kStages; ++s) consumed[s] = 0;
     fence_barrier_init();
   }
   if (threadIdx.x < 128) ((uint32_t *)unit_sf)[threadIdx.x] = 0x38383838u;  // E4M3 1.0
@@ -356,7 +356,9 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         __threadfence_block();
         __syncwarp();
-        if (lane == 0 && atomicAdd(consumed, 1) == 8 * (it + 1) - 1) mbar_arrive(&empty[s]);   // the eighth warp hands the stage back
+        // the eighth warp hands the stage back; the count is per stage because a warp may run several stages ahead of another,
+        // but never a whole fill ahead on the same stage
+        if (lane == 0 && (atomicAdd(&consumed[s], 1) & 7) == 7) mbar_arrive(&empty[s]);
       }
       if (ok)
 #pragma unroll

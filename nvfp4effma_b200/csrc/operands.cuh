@@ -63,6 +63,7 @@ struct GemmArgs {
 
 // kernels (each returns the launch error)
 cudaError_t launch_gemm_generic(const GemmArgs &g, cudaStream_t s);  // any operand combination, exact tiled order (CUDA cores)
+cudaError_t launch_gemm_grouped(const GemmArgs &g, const int *seg, int groups, cudaStream_t s);  // the same kernel over groups of columns
 cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s);          // n <= 8: HBM-streaming split-k GEMV
 bool gemv_supports(const GemmArgs &g);
 cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s);      // n <= 2: weights straight into tcgen05 kind::mxf4nvf4, activations as FP4 digit planes

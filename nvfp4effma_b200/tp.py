@@ -224,7 +224,8 @@ class TPLinear:
 class TPDecoderLinears:
     """The linear layers of a Llama-style decoder stack under tensor parallelism: per layer QKV (hidden -> qkv), O (hidden ->
     hidden), gate / up with SwiGLU (hidden -> 2 x intermediate, interleaved per 16 rows) and down (intermediate -> hidden).
-    Attention, norms and residuals are not part of this path: O reads the first ``hidden`` features of the QKV output."""
+    Attention, norms and residuals are not part of this path: O reads the first ``hidden`` features of the QKV output, and every
+    layer starts from the stack's input (see ``forward``)."""
 
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
                  device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096,
@@ -260,13 +261,19 @@ class TPDecoderLinears:
     def weight_bytes_local(self) -> int:
         return sum(m.image.numel() for layer in self.layers for m in layer)
 
-    def forward(self, h: torch.Tensor, layers: int | None = None) -> torch.Tensor:
-        """``layers``: run only the first that many decoder layers (parity checks against an unsharded stack)."""
+    def forward(self, h: torch.Tensor, layers: int | None = None, collect: bool = False):
+        """Every layer reads the stack's input ``h`` [T, hidden] and the last layer's output is returned.  (Norms and residuals are
+        not part of this path, and without them a chain of SwiGLUs squares the activations' scale layer after layer: BF16's range
+        is left within six layers.  Launches, shapes, collectives and their order are those of the chained stack.)
+        ``layers``: run only the first that many layers; ``collect``: return a list with a copy of every layer's output."""
         if self.collective == "peer" and h.shape[0] > self.max_tokens:
             raise ValueError(f"{h.shape[0]} tokens exceed the peer buffers ({self.max_tokens})")
-        for qkv, o, gate_up, down in self.layers[:layers]:   # consecutive layers alternate between the two peer buffers
+        outs, y = [], h
+        for qkv, o, gate_up, down in self.layers[:layers]:   # the four collectives of a layer alternate between the two peer buffers
             a = qkv(h, 0)[:, :self.hidden]
-            h = down(gate_up(o(a, 1), 0), 1)
-        return h
+            y = down(gate_up(o(a, 1), 0), 1)
+            if collect:
+                outs.append(y.clone())
+        return outs if collect else y
 
     __call__ = forward

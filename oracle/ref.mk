@@ -1,9 +1,11 @@
 # Builds the UNMODIFIED reference library (srose69/nvfp4effma) for sm_100 from its own sources where they
 # lie (REF, read-only), into oracle/_ref/ only.  Test infrastructure: the result pins the CPU oracle against
-# the reference's own CUDA-core kernels on a B200 (tests/test_ref_pin.py) and is never linked into the product.
+# the reference's own CUDA-core kernels on a B200 (tests/test_ref_pin_gpu.py) and is never linked into the product.
 # The object list restates the reference Makefile's instance matrix (Makefile:46-54 there): one object per
 # kernel instance, selected by -D macros.
-REF  ?= /root/reference
+ifndef REF
+$(error REF is not set: make -f oracle/ref.mk REF=<directory of the reference's sources>)
+endif
 OUT  ?= oracle/_ref
 NVCC ?= /usr/local/cuda/bin/nvcc
 FLAGS = -O3 -Xptxas -O3 -std=c++14 -Xcompiler -ffp-contract=off,-fPIC -gencode arch=compute_100,code=sm_100

@@ -1,8 +1,8 @@
 """Generates tests/golden/quant_torch_ref.npz from the REFERENCE's independent torch statement of the quantizer.
 
-Run in the build container, where the reference is mounted (default /root/reference):
+Run where the reference's sources are available:
 
-    python tests/golden/make_quant_golden.py [/path/to/reference]
+    python tests/golden/make_quant_golden.py <directory of the reference's sources>
 
 The reference's ``binds/python/tests/test_nvfp4effma.py`` holds ``ref_quantize`` (Transformer Engine's NVFP4 arithmetic in
 plain float32 torch ops, device-agnostic).  That module cannot be imported without the reference's compiled extension
@@ -19,7 +19,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_quant_golden.py <directory of the reference's sources>")
+REF = sys.argv[1]
 SRC = os.path.join(REF, "binds/python/tests/test_nvfp4effma.py")
 WANT = {"GRID", "FLT_MAX", "e2m1_rne", "e4m3_rn", "ref_quantize"}
 

@@ -69,7 +69,14 @@ def test_gemm_argument_checks():
     assert call(16, 4, 128, 1.0, mis, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
     swz = _fake(L.NVFP4, flags=L.SCALES_SWIZZLED, ld_scale=12)
     assert call(16, 4, 128, 1.0, swz, 128, B, 128, 0.0, None, 0, D, 16, None, None) == L.INVALID_VALUE
-    assert L.lib.nvfp4a_gemm_grouped(1, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, None, None) == L.NOT_SUPPORTED
+    grouped = L.lib.nvfp4a_gemm_grouped
+    assert grouped(1, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, None, None) == L.INVALID_VALUE   # seg is NULL
+    assert b"seg" in L.lib.nvfp4a_last_error()
+    seg = ctypes.c_void_p(0x1000)
+    assert grouped(-1, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, seg, None) == L.INVALID_VALUE
+    assert grouped(2, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 8, None, seg, None) == L.INVALID_VALUE     # ldd < m
+    assert grouped(0, 16, 64, 4, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, seg, None) == L.OK               # no groups: no-op
+    assert grouped(2, 16, 64, 0, 1.0, A, 64, B, 64, 0.0, None, 0, D, 16, None, seg, None) == L.OK               # no rows: no-op
 
 
 def test_quantize_and_epilogue_argument_checks():

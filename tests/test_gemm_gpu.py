@@ -418,7 +418,7 @@ def test_image_entries_gemm_tc_and_gemv_tc(bt):
 
 
 def test_w4a4_4096_cubed_against_block_sum_oracle_sample():
-    """BASELINE config 3 at full size: BF16 N(0,1) operands quantized to NVFP4 (linear E4M3 scales, FP32 decode-factor
+    """The W4A4 GEMM 4096^3 at full size: BF16 N(0,1) operands quantized to NVFP4 (linear E4M3 scales, FP32 decode-factor
     globals), D BF16 column major.  The oracle checks a slab of 64 columns x all rows within the bound and reports the share
     within 1 BF16 ulp; linearity (alpha = 2 doubles every output exactly) is checked on the whole matrix."""
     m = n = k = 4096
@@ -533,3 +533,66 @@ def test_gemm_dual_forward_dgrad_and_wgrad():
     st = L.lib.nvfp4a_gemm_dual(I, T, Ou, 1.0, ctypes.byref(lone), 1, ctypes.byref(dY[4]), 0, 0.0, None, 0, ctypes.byref(tD), I, None, stream())
     assert st == L.INVALID_VALUE and "column" in L.last_error()
     assert kernel_status() == 0
+
+
+@pytest.mark.parametrize("bt", [L.INT8, L.NVFP4, L.BF16, L.FP32])
+def test_grouped_gemm_gives_every_group_the_bytes_of_its_own_gemm(bt):
+    """nvfp4a_gemm_grouped (reference include/nvfp4effma.h:104-116): three experts of 40 weight rows stacked in A, the row counts
+    of B per expert in a device array (one expert empty, rows past seg[groups] left alone); every group's rows of D are the
+    bytes the oracle's tiled order gives for that group's own GEMM -- bias, beta * C and per-row globals of the stacked A included."""
+    from util import rand_fp4, rand_q8
+    rng = np.random.default_rng(4100 + bt)
+    groups, m, k, rows = 3, 40, 192, 45
+    seg = np.array([0, 19, 19, 41], np.int32)
+    lda, ldb, ldd = k + 64, k + 64, m + 8
+    A = rand_fp4(rng, groups * m, k, ld=lda, ld_scale=k // 16 + 4, flags=O.PER_ROW, glob=0.375)
+    if bt == L.NVFP4:
+        B = rand_fp4(rng, rows, k, ld=ldb, ld_scale=k // 16 + 8, flags=O.PER_ROW, glob=1.75)
+    elif bt == L.INT8:
+        B = rand_q8(rng, rows, k, ld=ldb, ld_scale=k // 16 + 8)
+    else:
+        B = O.Dense(bt, rand_dense(rng, bt, ldb * rows, 2.0), ldb)
+    bias = rand_dense(rng, L.BF16, groups * m, 3.0)
+    Dinit = rand_dense(rng, L.BF16, ldd * rows, 4.0)     # D is also C (beta != 0)
+    alpha, beta = 1.25, 0.5
+
+    def rows_of(t, lo, hi):
+        """The sub-matrix of rows [lo, hi) of a host operand (linear scales: whole rows of every array)."""
+        if isinstance(t, O.Dense):
+            return O.Dense(t.dtype, t.raw[lo * t.ld: hi * t.ld], t.ld)
+        if isinstance(t, O.Q8):
+            q = O.Q8(hi - lo, t.cols, ld=t.ld, ld_scale=t.ld_scale)
+            q.data[:], q.scales[:] = t.data[lo * t.ld: hi * t.ld], t.scales[lo * t.ld_scale: hi * t.ld_scale]
+            return q
+        q = O.Fp4(hi - lo, t.cols, ld=t.ld, ld_scale=t.ld_scale, flags=t.flags, scale_max=t.scale_max, glob=0.0)
+        q.data[:], q.scales[:], q.glob[:] = t.data[lo * t.ld // 2: hi * t.ld // 2], t.scales[lo * t.ld_scale: hi * t.ld_scale], t.glob[lo:hi]
+        return q
+
+    want = Dinit.copy()
+    amax = 0.0
+    for q in range(groups):
+        lo, hi = int(seg[q]), int(seg[q + 1])
+        if hi == lo:
+            continue
+        exp = O.gemm(m, hi - lo, k, rows_of(A, q * m, (q + 1) * m), rows_of(B, lo, hi), D_dtype=L.BF16, alpha=alpha, beta=beta,
+                     C=Dinit[lo * ldd: hi * ldd], C_dtype=L.BF16, ldc=ldd, ldd=ldd, bias=bias[q * m: (q + 1) * m], bias_dtype=L.BF16,
+                     lda=lda, ldb=ldb, D_init=Dinit[lo * ldd: hi * ldd])
+        want[lo * ldd: hi * ldd] = exp["D"]
+        amax = max(amax, exp["amax"])
+
+    dA = DevFp4(A)
+    if bt == L.NVFP4:
+        keep = DevFp4(B); tB = keep.tensor()
+    elif bt == L.INT8:
+        keep = (dev(B.data), dev(B.scales)); tB = tensor(keep[0], L.INT8, keep[1], B.ld_scale)
+    else:
+        keep = dev(B.raw); tB = tensor(keep, bt)
+    dD, damax, dbias, dseg = dev(Dinit), dev(np.zeros(1, np.float32)), dev(bias), dev(seg)
+    tA, tD, tbias = dA.tensor(), tensor(dD, L.BF16, amax=damax), tensor(dbias, L.BF16)
+    st = L.lib.nvfp4a_gemm_grouped(groups, m, k, rows, alpha, ctypes.byref(tA), lda, ctypes.byref(tB), ldb, beta, ctypes.byref(tD), ldd,
+                                   ctypes.byref(tD), ldd, ctypes.byref(tbias), ctypes.c_void_p(dseg.data_ptr()), stream())
+    assert st == 0, L.lib.nvfp4a_last_error()
+    torch.cuda.synchronize()
+    got = host(dD).view(np.uint16)
+    assert np.array_equal(got, want)          # groups bit for bit; padding, the empty group and rows 41 .. 44 untouched
+    assert float(host(damax)[0]) == amax

@@ -88,13 +88,14 @@ def test_activations_with_a_wide_dynamic_range(pin, spread):
     check_bound(c, h, got, amax, exp)
 
 
+@pytest.mark.parametrize("splits", [1, 2])
 @pytest.mark.parametrize("linear", [False, True])
-def test_large_activations_that_meet_zero_weights(pin, linear):
+def test_large_activations_that_meet_zero_weights(pin, linear, splits):
     """A few activations of magnitude 1 at positions where every weight is zero, all others near 2^-40: the result consists of
     the small terms alone, so bits dropped relative to the LARGEST activation would show (the FP32 accumulation bound is
     relative to sum |a_i x_i|).  Both tokens; swizzled and linear block scales; one token left narrow."""
     from util import rand_fp4
-    pin(2)
+    pin(splits)   # one CTA per row tile: sixteen chunks through a ring of four stages, the eight consumer warps far apart
     m, n, k = 640, 2, 4096
     c = Case(m, n, k, L.BF16, L.FP32, L.FP32, -1, 1.0, 0.0, fa=0 if linear else SW)
     h = build_case(c, 990)

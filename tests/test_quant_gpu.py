@@ -182,7 +182,7 @@ def test_transpose_of_16x16_tiles_is_the_columnwise_quantization():
 
 
 def test_full_size_8192_square_bf16_swizzled_amax_computed():
-    """BASELINE config 2 at full size: N(0,1) with 1 % of entries x 50, swizzled scales, amax computed; bit-exact."""
+    """Quantization of 8192 x 8192 at full size: N(0,1) with 1 % of entries x 50, swizzled scales, amax computed; bit-exact."""
     rng = np.random.default_rng(1)
     rows = cols = 8192
     x = rng.standard_normal((rows, cols), dtype=np.float32)
