@@ -10,7 +10,14 @@
 //     whose 8 columns are the n <= 8 activation vectors.  The order of k inside a step is permuted the same way for A
 //     and B, which a dot product allows;
 //   * the warps' partial sums are added in warp order through shared memory (deterministic, no atomics), then the plain
-//     or extended epilogue runs on the slice.
+//     or extended epilogue runs on the slice;
+//   * a long reduction (k >= 8192) is cut into 2 or 4 contiguous sections of steps, each with its own partial sums per warp,
+//     added at the end in (section, warp) order.  The sections are the unit of a second level of parallelism: when the
+//     matrix has few rows (a decode shard of a few hundred rows fills neither the SMs nor the memory pipeline with one CTA
+//     walking all of k per 16-row slice) a cluster of as many CTAs takes one section each, the peers store their partial
+//     sums into the first CTA's shared memory (DSMEM) and leave; otherwise one CTA walks the sections in turn.  The
+//     arithmetic is the same either way, so a row's sum depends on k alone, not on how many rows the matrix (or a
+//     tensor-parallel shard of it) has.
 // Accumulation is FP32 in the tensor cores' order: results agree with the reference's exact definition
 // (include/nvfp4effma.h:82-92 there) within the FP32 accumulation bound, as its own tensor-core GEMV does
 // (src/tensors/gemv_tc.cuh there).  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for
@@ -22,7 +29,7 @@
 
 namespace nvb {
 
-constexpr int kGemvWarps = 8;
+constexpr int kGemvWarps = 8, kGemvMaxSplit = 4;
 
 struct GemvArgs {
   int m, n, k;
@@ -31,6 +38,8 @@ struct GemvArgs {
   Epilogue e;
   EpilogueEx ex;
   TpPush tp;
+  int sections;                 // sections of k (1, 2 or 4; chosen from k alone)
+  int ksplit;                   // CTAs per 16-row slice (cluster size along x): 1, or `sections`
 };
 
 __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
@@ -65,14 +74,15 @@ struct GemvStep {
 
 // LAYOUT 0: plain operand, linear scales; 1: plain operand, swizzled scales; 2: image
 template <int LAYOUT>
-__global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g) {
+__global__ void __launch_bounds__(kGemvWarps * 32, 3) gemv_kernel(const GemvArgs g) {
   __shared__ uint32_t lut[256];                       // scale code -> BF16 pair (sa * 2^(126 - Z), twice)
-  __shared__ float part[kGemvWarps][16][8];
+  __shared__ float part[kGemvMaxSplit * kGemvWarps][16][8];   // [CTA of the cluster x warp]; the first CTA's copy collects all
   __shared__ float vtile[8][16];
   __shared__ float colscale[8];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
-  const int i0 = blockIdx.x * 16;
+  const int ksplit = g.ksplit, krank = ksplit > 1 ? (int)sm100::cluster_ctarank() : 0;
+  const int i0 = (blockIdx.x / ksplit) * 16;
   const int gm = g.m, gn = g.n, gk = g.k;
   const bool ue = g.A.ue != 0;
   {
@@ -103,7 +113,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
     s1p = g.A.data + t1 + kImgDataBytes + (r1 & 31) * 16 + ((r1 & 127) >> 5) * 4;
   }
   const int chunks = gk >> 5;  // 32-value chunks; a step is 4 of them (one per lane of a quad)
-  const int nsteps = (chunks + 3) >> 2;
+  const int nsteps_all = (chunks + 3) >> 2;
+  const int sections = g.sections, per_section = (nsteps_all + sections - 1) / sections;
+  const int sec_per_cta = sections / ksplit;   // ksplit is 1 or `sections`
 
   auto load_step = [&](int st) {
     GemvStep v;
@@ -130,7 +142,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
     return v;
   };
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc[4];
   auto consume = [&](const GemvStep &cur) {
     const uint32_t S0[2] = {lut[cur.sc0 & 0xFF], lut[(cur.sc0 >> 8) & 0xFF]}, S1[2] = {lut[cur.sc1 & 0xFF], lut[(cur.sc1 >> 8) & 0xFF]};
     const uint32_t ww0[4] = {cur.w0.x, cur.w0.y, cur.w0.z, cur.w0.w}, ww1[4] = {cur.w1.x, cur.w1.y, cur.w1.z, cur.w1.w};
@@ -146,24 +158,37 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
                      bf16x2_mul(decode_pair<3>(b), sb), x26, x37);
     }
   };
-  // Four of the warp's steps are requested before the first is consumed: a 16-row slice is short (k = 4096 is four steps per
-  // warp), so without this every warp would have one step's 1 KiB in flight and wait out a full memory latency per step.
-  // The steps are consumed in their order, so the sums are those of a plain loop.
-  int st = warp;
-  for (; st + 3 * kGemvWarps < nsteps; st += 4 * kGemvWarps) {
-    const GemvStep s0 = load_step(st), s1 = load_step(st + kGemvWarps), s2 = load_step(st + 2 * kGemvWarps), s3 = load_step(st + 3 * kGemvWarps);
-    consume(s0); consume(s1); consume(s2); consume(s3);
+  // Two of the warp's steps are requested before the first is consumed (80 registers, three CTAs per SM).  Measured on one
+  // GPU against one step in flight (64 registers, four CTAs) and four (128 registers, two CTAs): two is best or within 4 % of
+  // the best on every decode shape of a Llama-3-8B layer and of its 2- and 8-way shards; four wins only on long reductions
+  // of few rows and loses 15-25 % on the large matrices, one the other way round.  The steps are consumed in their order, so
+  // the sums are those of a plain loop.
+  for (int sc = krank * sec_per_cta; sc < (krank + 1) * sec_per_cta; ++sc) {
+    const int step0 = sc * per_section, nsteps = min(nsteps_all, step0 + per_section);   // this section's steps: [step0, nsteps)
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    int st = step0 + warp;
+    for (; st + kGemvWarps < nsteps; st += 2 * kGemvWarps) {
+      const GemvStep s0 = load_step(st), s1 = load_step(st + kGemvWarps);
+      consume(s0); consume(s1);
+    }
+    for (; st < nsteps; st += kGemvWarps) consume(load_step(st));
+    // partial sums of this warp and section: c0, c1 -> (row gq, columns 2 q, 2 q + 1); c2, c3 -> row gq + 8
+    float *p = &part[sc * kGemvWarps + warp][0][0];
+    if (ksplit == 1) {
+      p[gq * 8 + 2 * q] = acc[0]; p[gq * 8 + 2 * q + 1] = acc[1];
+      p[(gq + 8) * 8 + 2 * q] = acc[2]; p[(gq + 8) * 8 + 2 * q + 1] = acc[3];
+    } else {
+      sm100::st_peer_f32(p + gq * 8 + 2 * q, 0, acc[0]); sm100::st_peer_f32(p + gq * 8 + 2 * q + 1, 0, acc[1]);
+      sm100::st_peer_f32(p + (gq + 8) * 8 + 2 * q, 0, acc[2]); sm100::st_peer_f32(p + (gq + 8) * 8 + 2 * q + 1, 0, acc[3]);
+    }
   }
-  if (st + kGemvWarps < nsteps) {
-    const GemvStep s0 = load_step(st), s1 = load_step(st + kGemvWarps);
-    consume(s0); consume(s1);
-    st += 2 * kGemvWarps;
+  if (ksplit == 1) {
+    __syncthreads();
+  } else {
+    sm100::cluster_arrive_release();
+    if (krank != 0) return;          // the first CTA stays until every peer has arrived, so the stores above land in live memory
+    sm100::cluster_wait_acquire();
   }
-  for (; st < nsteps; st += kGemvWarps) consume(load_step(st));
-  // partial sums of this warp: c0, c1 -> (row gq, columns 2 q, 2 q + 1); c2, c3 -> row gq + 8
-  part[warp][gq][2 * q] = acc[0]; part[warp][gq][2 * q + 1] = acc[1];
-  part[warp][gq + 8][2 * q] = acc[2]; part[warp][gq + 8][2 * q + 1] = acc[3];
-  __syncthreads();
 
   // ---- epilogue on the slice: thread t < 128 owns (row t % 16, column t / 16) ----
   const Epilogue &e = g.e;
@@ -173,7 +198,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
   if (live) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < kGemvWarps; ++w) s = __fadd_rn(s, part[w][ri][cj]);
+    for (int w = 0; w < sections * kGemvWarps; ++w) s = __fadd_rn(s, part[w][ri][cj]);
     s = __fmul_rn(s, ue ? 65536.f : 256.f);
     float colp = epi_col_part(e, cj);
     if (g.ex.mask & kExNorm) colp = __fmul_rn(colp, colscale[cj]);
@@ -214,7 +239,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const GemvArgs g)
     if (tid == 0) {
       unsigned *ctas = (unsigned *)(g.tp.flags[g.tp.rank] + kFlagCtas);
       const unsigned ticket = atomicAdd(ctas, 1u);
-      last_cta = ticket == gridDim.x - 1;
+      last_cta = ticket == gridDim.x / ksplit - 1;   // one ticket per slice
       if (last_cta) *ctas = 0;
     }
     __syncthreads();
@@ -251,11 +276,20 @@ cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
   a.tp.status = kernel_status_device_ptr();
   a.tp.tag = next_launch_tag();
   a.tp.wait_cycles = tp_wait_limit();
-  const int grid = (g.m + 15) / 16;
-  if (a.A.image) gemv_kernel<2><<<grid, kGemvWarps * 32, 0, s>>>(a);
-  else if (a.A.sld < 0) gemv_kernel<1><<<grid, kGemvWarps * 32, 0, s>>>(a);
-  else gemv_kernel<0><<<grid, kGemvWarps * 32, 0, s>>>(a);
-  return cudaGetLastError();
+  a.sections = g.k >= 8192 ? (g.k >= 12288 ? 4 : 2) : 1;   // by k alone: see the header
+  const int slices = (g.m + 15) / 16;
+  a.ksplit = slices * a.sections <= 2 * device_sms() ? a.sections : 1;   // a cluster per slice only while the CTAs fit the GPU at once
+  void (*kern)(GemvArgs) = a.A.image ? gemv_kernel<2> : a.A.sld < 0 ? gemv_kernel<1> : gemv_kernel<0>;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(slices * a.ksplit, 1, 1);
+  cfg.blockDim = dim3(kGemvWarps * 32, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = a.ksplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = a.ksplit > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 }  // namespace nvb

@@ -258,6 +258,18 @@ class TPDecoderLinears:
                 m.gather = self._gather if collective == "peer" else None
         self.collective = collective
 
+    def check(self) -> None:
+        """Reads the library's kernel status word (this SYNCHRONISES the device: call it at a coarse point such as the end of a
+        forward pass, outside stream capture) and raises if a kernel gave up a bounded wait since the last check -- for this
+        stack that is a rank that waited longer than the barrier's limit (about a second) for its peers in an all-gather: the
+        step's activations are then incomplete on this rank and must not be used."""
+        word = ctypes.c_uint(0)
+        L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(word), 1))
+        if word.value:
+            code, launch = word.value & 0xFFF, word.value >> 12
+            what = "a tensor-parallel barrier ran out of time waiting for a peer" if code == 0x401 else "a kernel gave up a bounded wait"
+            raise RuntimeError(f"{what} (status 0x{code:03x}, launch {launch}): the outputs of that step are incomplete")
+
     def weight_bytes_local(self) -> int:
         return sum(m.image.numel() for layer in self.layers for m in layer)
 

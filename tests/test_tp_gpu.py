@@ -76,6 +76,14 @@ def test_a_barrier_whose_peer_never_arrives_gives_up_and_reports_it():
         assert int(flags[1][0]) == 1 and int(flags[0][1]) == 0                   # our epoch was posted; the peer's never came
         L.check(L.lib.nvfp4a_b200_kernel_status(ctypes.byref(st), 0))
         assert st.value == 0                                                     # the read above cleared the word
+        # the layer stack's own health check turns the same word into an exception (and clears it)
+        from nvfp4effma_b200.tp import TPDecoderLinears
+        stack = TPDecoderLinears(layers=1, hidden=256, intermediate=512, qkv=384, std=0.06)
+        stack.check()
+        L.check(L.lib.nvfp4a_b200_tp_gather(pb, pf, 2, 0, rows, pitch, 0, shard, stream))
+        with pytest.raises(RuntimeError, match="barrier ran out of time"):
+            stack.check()
+        stack.check()
     finally:
         L.lib.nvfp4a_b200_set_wait_limit(2000000000)
     import nvfp4effma_b200 as nf
