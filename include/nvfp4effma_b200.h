@@ -111,6 +111,22 @@ nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha, const nvf
                                      const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
                                      void *const *buffers, void *const *flags, int world, int rank, cudaStream_t stream);
 
+/* The DEFERRED form of the tensor-parallel decode step (1 to 8 BF16 activation vectors; no counterpart in the reference): nobody
+ * waits at the END of a gather.  A rank copies its outputs into the peers' buffers and posts its epoch to them -- by a
+ * nvfp4a_b200_tp_gather_post launch after the GEMV (push = 0; the GEMV may then be the FP4 tensor-core one), or by the mma.sync
+ * GEMV's last CTA (push != 0) -- and goes on.  Instead every nvfp4a_b200_gemv_tc_tp_deferred call waits at the START of its kernel
+ * until every peer has posted the epoch this rank has reached, i.e. until the previous gather is complete here and every peer has
+ * finished the kernel that read the buffer this call overwrites; there the wait hides behind the launch and the kernel's set-up.
+ * A sequence of such calls on alternating buffers (two suffice) needs no other synchronisation between them; it is closed by
+ * nvfp4a_b200_tp_wait, after which the last gathered buffer is complete.  Same buffers / flags / layout rules and the same bounded
+ * wait (0x401) as nvfp4a_b200_gemv_tc_tp; calls of both forms and of nvfp4a_b200_tp_gather may be mixed on one flag array. */
+nvfp4a_status nvfp4a_b200_gemv_tc_tp_deferred(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
+                                              const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
+                                              void *const *buffers, void *const *flags, int world, int rank, int push, cudaStream_t stream);
+nvfp4a_status nvfp4a_b200_tp_gather_post(void *const *buffers, void *const *flags, int world, int rank, int rows, long long row_pitch_bytes,
+                                         long long col_offset_bytes, long long shard_bytes, cudaStream_t stream);
+nvfp4a_status nvfp4a_b200_tp_wait(void *const *flags, int world, int rank, cudaStream_t stream);
+
 /* nvfp4a_gemm_tc / nvfp4a_gemm_tc_ex (beta = 0) with the tensor-parallel all-gather fused in (no counterpart in the reference):
  * as nvfp4a_b200_gemv_tc_tp, for more than 8 tokens.  With BF16 activations the tcgen05 GEMM's epilogue stores every tile of
  * D by TMA into the local buffer and into every peer's (plain TMA stores to peer memory; no multicast, no peer loads), so the

@@ -78,6 +78,9 @@ _PROTOS = {
     "nvfp4a_b200_set_gemv_splits": (_i, [_i]),
     "nvfp4a_b200_last_route": (_i, []),
     "nvfp4a_b200_gemv_tc_tp": (_i, [_i, _i, _i, _f, _T, _T, _i, _T, _i, _T, _E, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _s]),
+    "nvfp4a_b200_gemv_tc_tp_deferred": (_i, [_i, _i, _i, _f, _T, _T, _i, _T, _i, _T, _E, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _i, _s]),
+    "nvfp4a_b200_tp_gather_post": (_i, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _i, C.c_longlong, C.c_longlong, C.c_longlong, _s]),
+    "nvfp4a_b200_tp_wait": (_i, [C.POINTER(C.c_void_p), _i, _i, _s]),
     "nvfp4a_b200_gemm_tc_tp": (_i, [_i, _i, _i, _f, _T, _T, _T, _i, _T, _E, _v, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _s]),
     "nvfp4a_b200_tp_gather": (_i, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _i, C.c_longlong, C.c_longlong, C.c_longlong, _s]),
     "nvfp4a_b200_gemm_ex_static": (_i, _GEMM + [_E, _s]),

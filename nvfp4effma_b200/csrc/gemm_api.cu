@@ -104,6 +104,14 @@ extern "C" nvfp4a_status nvfp4a_b200_tp_gather(void *const *buffers, void *const
 static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t stream) {
   cudaError_t err;
   const bool gemv = g.k == 0 || g.n <= kGemvMaxN;
+  if (g.tp.world > 1 && g.tp.deferred) {
+    // The deferred tensor-parallel form: the mma.sync GEMV waits at its start and (bit 1) pushes at its end; the FP4 tensor-core
+    // GEMV only waits, so with bit 1 unset either may run and the caller's nvfp4a_b200_tp_gather_post follows.
+    if (!(gemv && gemv_supports(g))) return fail(NVFP4A_NOT_SUPPORTED, "%s: the deferred tensor-parallel form takes 1 to 8 BF16 activation vectors", fn);
+    if (!(g.tp.deferred & 2) && g.k > 0 && forced_route() != 2 && gemv_fp4_supports(g)) { g_last_route = 3; return cuda_fail(launch_gemv_fp4(g, stream), fn); }
+    g_last_route = 2;
+    return cuda_fail(launch_gemv(g, stream), fn);
+  }
   if (forced_route() == 1) { g_last_route = 1; err = launch_gemm_generic(g, stream); }
   else if (gemv && g.k > 0 && forced_route() != 2 && gemv_fp4_supports(g)) { g_last_route = 3; err = launch_gemv_fp4(g, stream); }
   else if (gemv && gemv_supports(g)) { g_last_route = 2; err = launch_gemv(g, stream); }
@@ -532,6 +540,31 @@ extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp(int m, int n, int k, float alpha
   EpilogueEx x;
   if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
   if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered; use nvfp4a_gemv_tc_ex and nvfp4a_b200_tp_gather", fn);
+  if (nvfp4a_status st = check_tp_layout(fn, D, ldd, m, (x.mask & kExSwiglu) != 0, tp.local_base, world)) return st;
+  return gemv_tc_run(fn, m, n, k, alpha, A, B, ldb, 0.f, nullptr, 0, D, ldd, bias, x, stream, world > 1 ? &tp : nullptr);
+}
+
+// The same with the wait moved from the end of this kernel to the start of the next one (see TpPush::deferred).
+extern "C" nvfp4a_status nvfp4a_b200_gemv_tc_tp_deferred(int m, int n, int k, float alpha, const nvfp4a_tensor *A, const nvfp4a_tensor *B, int ldb,
+                                                         const nvfp4a_tensor *D, int ldd, const nvfp4a_tensor *bias, const nvfp4a_epilogue *ex,
+                                                         void *const *buffers, void *const *flags, int world, int rank, int push, cudaStream_t stream) {
+  const char *fn = "nvfp4a_b200_gemv_tc_tp_deferred";
+  clear_error();
+  if (!buffers || !flags || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(NVFP4A_INVALID_VALUE, "%s: needs buffers, flags and 0 <= rank < world <= %d", fn, kMaxRanks);
+  TpPush tp;
+  memset(&tp, 0, sizeof tp);
+  tp.world = world; tp.rank = rank; tp.deferred = push ? 3 : 1;
+  tp.local_base = (unsigned char *)buffers[rank];
+  for (int p = 0; p < world; ++p) {
+    if (!buffers[p] || !flags[p] || ((uintptr_t)buffers[p] & 15) || ((uintptr_t)flags[p] & 7))
+      return fail(NVFP4A_INVALID_VALUE, "%s: buffer / flag pointer of rank %d is NULL or misaligned", fn, p);
+    tp.delta[p] = (long long)((unsigned char *)buffers[p] - tp.local_base);
+    tp.flags[p] = (unsigned long long *)flags[p];
+  }
+  EpilogueEx x;
+  if (nvfp4a_status st = make_epilogue_ex(fn, ex, m, 0.f, ldd, &x)) return st;
+  if (x.mask & kExOut2) return fail(NVFP4A_NOT_SUPPORTED, "%s: the second output is not gathered", fn);
   if (nvfp4a_status st = check_tp_layout(fn, D, ldd, m, (x.mask & kExSwiglu) != 0, tp.local_base, world)) return st;
   return gemv_tc_run(fn, m, n, k, alpha, A, B, ldb, 0.f, nullptr, 0, D, ldd, bias, x, stream, world > 1 ? &tp : nullptr);
 }

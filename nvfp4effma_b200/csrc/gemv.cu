@@ -90,6 +90,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 3) gemv_kernel(const GemvArgs
     const uint32_t h = __float_as_uint(s) >> 16;
     lut[tid] = h | (h << 16);
   }
+  // Tensor-parallel layers in the deferred form: the activations (and the buffer this kernel writes) belong to this kernel only
+  // once every peer has posted the previous gather; the weights do not, so a first step's weights could be requested before.
+  if (g.tp.world > 1 && (g.tp.deferred & 1)) tp_wait_posts(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status, g.tp.tag, g.tp.wait_cycles);
   if ((g.ex.mask & kExNorm) && warp < gn) {
     const float s = warp_norm_scale(g.ex, warp, lane);
     if (lane == 0) colscale[warp] = s;
@@ -204,19 +207,20 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 3) gemv_kernel(const GemvArgs
     if (g.ex.mask & kExNorm) colp = __fmul_rn(colp, colscale[cj]);
     v = epi_value(e, i, cj, s, epi_scale(e, epi_row_part(e, i), colp));
   }
+  auto store_d = [&](size_t idx, float val) { store_dense(e.d_dtype, e.d, idx, val); };
   if (!(g.ex.mask & (kExSwiglu | kExOut2))) {
-    if (live) { store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + i, v); amax = fabsf(v); }
+    if (live) { store_d((size_t)cj * e.ldd + i, v); amax = fabsf(v); }
   } else {
     if (tid < 128) vtile[cj][ri] = v;
     __syncthreads();
     if (g.ex.mask & kExSwiglu) {
       if (live && ri < 8) {
         const float h = silu_mul(vtile[cj][ri], vtile[cj][ri + 8]);
-        store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + (i0 >> 1) + ri, h);
+        store_d((size_t)cj * e.ldd + (i0 >> 1) + ri, h);
         amax = fabsf(h);
       }
     } else if (live) {
-      store_dense(e.d_dtype, e.d, (size_t)cj * e.ldd + i, v);
+      store_d((size_t)cj * e.ldd + i, v);
       amax = fabsf(v);
     }
     if (g.ex.mask & kExOut2) {
@@ -230,7 +234,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 3) gemv_kernel(const GemvArgs
     }
   }
   if (e.amax && tid < 128) warp_amax_commit(e.amax, amax);
-  if (g.tp.world > 1) {
+  if (g.tp.world > 1 && (g.tp.deferred == 0 || (g.tp.deferred & 2))) {
     // All-gather fused into this kernel: the CTA that finishes last copies the rank's outputs (n rows of the activation
     // buffer, just written and still in L2) into every peer's buffer with 16-byte stores and joins the ranks' barrier.
     __shared__ int last_cta;
@@ -255,9 +259,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 3) gemv_kernel(const GemvArgs
         for (int p = 0; p < g.tp.world; ++p)
           if (p != g.tp.rank) *(uint4 *)(src + g.tp.delta[p]) = x;
       }
-      __threadfence_system();
-      __syncthreads();
-      tp_barrier_cta(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status, g.tp.tag, g.tp.wait_cycles);
+      __syncthreads();   // the flags' release stores order every thread's copies (see tp_barrier_cta)
+      // deferred form: tell the peers and leave; the next kernel of every rank waits for the posts at its start
+      if (g.tp.deferred & 2) tp_post_epoch(g.tp.flags, g.tp.world, g.tp.rank);
+      else tp_barrier_cta(g.tp.flags, g.tp.world, g.tp.rank, g.tp.status, g.tp.tag, g.tp.wait_cycles);
     }
   }
 }
@@ -285,6 +290,8 @@ cudaError_t launch_gemv(const GemmArgs &g, cudaStream_t s) {
   cfg.gridDim = dim3(slices * a.ksplit, 1, 1);
   cfg.blockDim = dim3(kGemvWarps * 32, 1, 1);
   cfg.stream = s;
+  // (No programmatic dependent launch here: measured on the decode step of a 32-layer stack it costs 5-7 us per layer, this
+  // kernel's CTAs taking their places on the SMs while the FP4 GEMV before or after them still needs whole SMs.)
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = a.ksplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;

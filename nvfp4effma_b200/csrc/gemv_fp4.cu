@@ -36,6 +36,7 @@
 #include <atomic>
 #include "operands.cuh"
 #include "sm100.cuh"
+#include "tp_barrier.cuh"
 
 namespace nvb {
 
@@ -54,6 +55,9 @@ struct GemvFp4Args {
   EpilogueEx ex;
   unsigned *status;
   unsigned tag;        // this launch's tag in the status word
+  int tp_world, tp_rank;                       // > 1: wait for the peers' posts before the activations are read (TpPush::deferred bit 0)
+  unsigned long long *tp_flags[kMaxRanks];
+  long long tp_wait_cycles;
   int stages;          // ring depth (2..6), chosen by the host from the shared memory left beside the pieces
   int piece_bytes;     // shared memory of the activation pieces: chunks per CTA x piece rows x 128
 };
@@ -150,6 +154,8 @@ gemv_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   fence_proxy_async_smem();
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   pdl_wait();
+  // tensor-parallel layers in the deferred form: the activations are complete once every peer has posted the previous gather
+  if (g.tp_world > 1) tp_wait_posts(g.tp_flags, g.tp_world, g.tp_rank, g.status, g.tag, g.tp_wait_cycles);
   // the decomposition warps ask for their activations first: the loads fly while the barrier below gathers the CTA
   const int t2 = threadIdx.x - 64, nvec = nloc * 32;  // vectors of 8 consecutive k; at most 2 per thread and token
   uint4 xq[NTOK][2];
@@ -537,6 +543,10 @@ cudaError_t launch_gemv_fp4(const GemmArgs &g, cudaStream_t s) {
   a.e = g.e; a.ex = g.x;
   a.status = kernel_status_device_ptr();
   a.tag = next_launch_tag();
+  if (g.tp.world > 1 && (g.tp.deferred & 1)) {
+    a.tp_world = g.tp.world; a.tp_rank = g.tp.rank; a.tp_wait_cycles = tp_wait_limit();
+    for (int p = 0; p < g.tp.world; ++p) a.tp_flags[p] = g.tp.flags[p];
+  }
   a.ktiles = (g.k + kImgK - 1) / kImgK;
   a.a_image = g.A.image;
   CUtensorMap ta, ts;

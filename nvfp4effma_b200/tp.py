@@ -116,17 +116,19 @@ def _local_gemm(x, layer, out):
     return out
 
 
-def _fused_call(entry, x, layer, out, buffer_ptrs, flag_ptrs, rank):
+def _fused_call(entry, x, layer, out, buffer_ptrs, flag_ptrs, rank, push=1):
     """``nvfp4a_b200_gemv_tc_tp`` / ``nvfp4a_b200_gemm_tc_tp``: ``out`` (a view into this rank's peer-mapped buffer) is also
     written into every peer's buffer and the ranks meet in a barrier."""
-    gemv = entry == "gemv"
+    gemv = entry in ("gemv", "gemv_deferred")
+    deferred = entry == "gemv_deferred"
     x = A.matrix(x, 64, "x") if gemv else (x if x.is_contiguous() and x.data_ptr() % 16 == 0 else x.contiguous())
     a, b, d = _image_tensor(layer.image, layer.global_scale, layer.flags, layer.scale_max), A.dense_tensor(x), A.dense_tensor(out)
     bias = A.dense_tensor(layer.bias) if layer.bias is not None else None
     ex = _swiglu_descriptor(layer.swiglu)
-    tail = (_ptr_array(buffer_ptrs), _ptr_array(flag_ptrs), len(buffer_ptrs), rank, A.stream())
+    tail = (_ptr_array(buffer_ptrs), _ptr_array(flag_ptrs), len(buffer_ptrs), rank) + ((int(push),) if deferred else ()) + (A.stream(),)
     if gemv:
-        st = L.lib.nvfp4a_b200_gemv_tc_tp(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), x.stride(0), ctypes.byref(d),
+        fn = L.lib.nvfp4a_b200_gemv_tc_tp_deferred if deferred else L.lib.nvfp4a_b200_gemv_tc_tp
+        st = fn(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), x.stride(0), ctypes.byref(d),
                                           out.stride(0), A.ref(bias), ctypes.byref(ex), *tail)
     else:
         st = L.lib.nvfp4a_b200_gemm_tc_tp(layer.rows, x.shape[0], layer.in_features, 1.0, ctypes.byref(a), ctypes.byref(b), ctypes.byref(d), out.stride(0),
@@ -160,6 +162,15 @@ class PeerGather:
     def push(self, slot: int, T: int, M: int, col0: int, cols: int):
         _tp_gather(self.buf_ptrs[slot], self.flag_ptrs, self.rank, T, M * 2, col0 * 2, cols * 2)
 
+    def post(self, slot: int, T: int, M: int, col0: int, cols: int):
+        """The deferred form of ``push``: copy and post, no wait."""
+        L.check(L.lib.nvfp4a_b200_tp_gather_post(_ptr_array(self.buf_ptrs[slot]), _ptr_array(self.flag_ptrs), self.world, self.rank, T, M * 2, col0 * 2,
+                                                 cols * 2, A.stream()))
+
+    def wait(self):
+        """Closes a sequence of deferred calls (``nvfp4a_b200_gemv_tc_tp_deferred``): after it the last gathered buffer is complete."""
+        L.check(L.lib.nvfp4a_b200_tp_wait(_ptr_array(self.flag_ptrs), self.world, self.rank, A.stream()))
+
 
 class TPLinear:
     """One rank's part of ``y = x @ W.T + bias`` (optionally ``silu(gate) * up`` of interleaved gate / up rows).
@@ -168,9 +179,13 @@ class TPLinear:
     replicated ``x`` [T, K] (bfloat16) and returns the full ``y``; ``forward_local`` returns this rank's columns only."""
 
     def __init__(self, weight: NVFP4Tensor, bias: Optional[torch.Tensor] = None, *, group=None, swiglu: bool = False, replicate: bool = False,
-                 gather: Optional["PeerGather"] = None, fused_decode: bool = False, fused_prefill: bool = True):
-        """``fused_decode``: up to 8 tokens, the GEMV kernel itself copies the rank's outputs to the peers and joins the
-        barrier (``nvfp4a_b200_gemv_tc_tp``) instead of a second launch; measured slower at 2 GPUs, so off by default."""
+                 gather: Optional["PeerGather"] = None, fused_decode=False, fused_prefill: bool = True):
+        """``fused_decode`` (up to 8 tokens): ``"deferred"`` -- GEMV, then a launch that copies the rank's outputs to the peers and
+        posts the rank's epoch without waiting; the wait for the peers moves to the start of the NEXT GEMV
+        (``nvfp4a_b200_gemv_tc_tp_deferred`` + ``nvfp4a_b200_tp_gather_post``; a sequence is closed by ``PeerGather.wait``);
+        ``"deferred_push"`` -- the same with the copy and the post done by the GEMV's last CTA; ``True`` -- the GEMV's last CTA
+        copies the rank's outputs and joins the barrier itself (``nvfp4a_b200_gemv_tc_tp``); ``False`` -- GEMV, then the gather
+        launch with its barrier.  The two forms with a fused copy measured slower than their two-launch counterparts."""
         self.group = group
         self.gather = gather
         self.fused_decode = fused_decode
@@ -198,7 +213,8 @@ class TPLinear:
             out = torch.empty((T, self.rows // (2 if self.swiglu else 1)), dtype=torch.bfloat16, device=x.device)
         return _local_gemv(x, self, out) if T <= 8 else _local_gemm(x, self, out)
 
-    def forward(self, x: torch.Tensor, slot: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, slot: int = 0, close: bool = True) -> torch.Tensor:
+        """``close = False`` (deferred form only): the caller goes on with another deferred call or ``PeerGather.wait``."""
         if self.world == 1:
             return self.forward_local(x)
         if self.gather is None:
@@ -206,7 +222,16 @@ class TPLinear:
         T, nl, M = x.shape[0], self.rows // (2 if self.swiglu else 1), self.out_features
         y = self.gather.view(slot, T, M)
         mine = y[:, self.rank * nl:(self.rank + 1) * nl]
-        if T <= 8 and self.fused_decode:   # the GEMV's last CTA stores to every rank and joins the barrier itself
+        if T <= 8 and self.fused_decode in ("deferred", "deferred_push"):
+            if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
+                raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
+            push = self.fused_decode == "deferred_push"
+            _fused_call("gemv_deferred", x, self, mine, self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank, push=push)
+            if not push:
+                self.gather.post(slot, T, M, self.rank * nl, nl)
+            if close:
+                self.gather.wait()
+        elif T <= 8 and self.fused_decode:   # the GEMV's last CTA stores to every rank and joins the barrier itself
             if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.in_features:
                 raise ValueError(f"x must be bfloat16 [T, {self.in_features}]")
             _fused_call("gemv", x, self, mine, self.gather.buf_ptrs[slot], self.gather.flag_ptrs, self.rank)
@@ -229,13 +254,14 @@ class TPDecoderLinears:
 
     def __init__(self, layers: int = 32, hidden: int = 4096, intermediate: int = 14336, qkv: int = 6144, *, group=None, seed: int = 4,
                  device="cuda", std: float = 0.02, replicate: bool = False, collective: str = "peer", max_tokens: int = 4096,
-                 fused_decode: bool = False, fused_prefill: bool = True):
+                 fused_decode=False, fused_prefill: bool = True):
         """``collective``: "peer" = the library's all-gather over peer-mapped buffers, "nccl" = ``all_gather_into_tensor``."""
         self.hidden, self.layers = hidden, []
         multi = dist.is_initialized() and dist.get_world_size(group) > 1 and not replicate
         self.collective = collective if multi else "none"
         gather = PeerGather(group, max_tokens * max(hidden, intermediate, qkv), device) if multi and collective == "peer" else None
         self.max_tokens = max_tokens
+        self.fused_decode = fused_decode
         self._gather = gather
         from .api import quantize
         for layer in range(layers):
@@ -280,12 +306,17 @@ class TPDecoderLinears:
         ``layers``: run only the first that many layers; ``collect``: return a list with a copy of every layer's output."""
         if self.collective == "peer" and h.shape[0] > self.max_tokens:
             raise ValueError(f"{h.shape[0]} tokens exceed the peer buffers ({self.max_tokens})")
+        deferred = self.collective == "peer" and h.shape[0] <= 8 and self.fused_decode in ("deferred", "deferred_push")
         outs, y = [], h
         for qkv, o, gate_up, down in self.layers[:layers]:   # the four collectives of a layer alternate between the two peer buffers
-            a = qkv(h, 0)[:, :self.hidden]
-            y = down(gate_up(o(a, 1), 0), 1)
+            a = qkv(h, 0, close=False)[:, :self.hidden]
+            y = down(gate_up(o(a, 1, close=False), 0, close=False), 1, close=False)
             if collect:
+                if deferred:
+                    self._gather.wait()
                 outs.append(y.clone())
+        if deferred and not collect:
+            self._gather.wait()   # the last gather is complete, and every peer is done with both buffers
         return outs if collect else y
 
     __call__ = forward

@@ -104,6 +104,8 @@ kw = dict(layers=2, hidden=256, intermediate=512, qkv=512, std=0.06)
 peer, nccl, solo = TPDecoderLinears(collective="peer", max_tokens=64, **kw), TPDecoderLinears(collective="nccl", **kw), TPDecoderLinears(replicate=True, **kw)
 fused = TPDecoderLinears(collective="peer", max_tokens=64, fused_decode=True, **kw)
 unfused = TPDecoderLinears(collective="peer", max_tokens=64, fused_prefill=False, **kw)
+deferred = TPDecoderLinears(collective="peer", max_tokens=64, fused_decode="deferred", **kw)
+deferred_push = TPDecoderLinears(collective="peer", max_tokens=64, fused_decode="deferred_push", **kw)
 ok = peer.collective == "peer" and nccl.collective == "nccl"
 for rep in range(2):
     for T in (1, 5, 48):
@@ -111,7 +113,18 @@ for rep in range(2):
         x = torch.randn((T, 256), generator=g).cuda().bfloat16()
         want = solo(x, collect=True)
         same = lambda got: all(torch.equal(g, w) for g, w in zip(got, want))
-        ok = ok and all(same(stack(x, collect=True)) for stack in (peer, nccl, fused, unfused))
+        ok = ok and all(same(stack(x, collect=True)) for stack in (peer, nccl, fused, unfused, deferred, deferred_push))
+        ok = ok and torch.equal(deferred(x).clone(), want[-1])   # the whole step with one closing wait
+# the deferred decode step replayed as a CUDA graph: the epochs live on the device, so every replay synchronises anew
+x = torch.randn((3, 256), generator=torch.Generator(device="cpu").manual_seed(9)).cuda().bfloat16()
+want = solo(x)
+out = deferred(x); torch.cuda.synchronize()
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph):
+    out = deferred(x)
+for _ in range(5):
+    graph.replay()
+    ok = ok and torch.equal(out.clone(), want)
 from nvfp4effma_b200 import workloads
 ok = ok and workloads.kernel_status() == 0
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
