@@ -68,10 +68,11 @@ int nvfp4a_b200_set_quant_fused(int on);
  * counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_tile_n(int bn);
 
-/* The W4A4 GEMM's CTA-pair form (tcgen05.mma.cta_group::2 on 256 x 256 tiles; taken for m > 128, n > 128 and block scales in
- * aligned 512-byte tiles or images on both operands): -1 = automatic (at present: never -- the single-CTA form is the
- * faster one), 0 = never, 1 = wherever it applies.  Results are bit-identical either way.  Tuning / test aid, no
- * counterpart in the reference.  Returns 0, or -1 for another value. */
+/* The W4A4 GEMM's CTA-pair kernel (tcgen05.mma.cta_group::2 on 256 x 256 tiles, csrc/gemm_w4a4_pair.cu; it takes a 16-bit D that
+ * TMA can store, beta = 0, no bias, one global per operand, and block scales in aligned 512-byte tiles or images on both
+ * operands): -1 = automatic (m, n >= 256 and its rounds of 256 x 256 tiles over the SM pairs estimated no dearer than the
+ * single-CTA kernel's rounds; 4096^3: 31 us against 49 us on single CTAs), 0 = never, 1 = wherever it applies.  Results are bit-identical either way.
+ * Tuning / test aid, no counterpart in the reference.  Returns 0, or -1 for another value. */
 int nvfp4a_b200_set_pair(int mode);
 
 /* Orientation of the W4A4 GEMM on the tensor cores: 1 = B of the call (tokens) on the MMA's M side whenever D is a 16-bit

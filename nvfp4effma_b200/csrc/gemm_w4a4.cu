@@ -1,3 +1,7 @@
+// The single-CTA W4A4 kernel: the route for what the CTA-pair kernel (gemm_w4a4_pair.cu, the default for large problems with a
+// 16-bit D and tiled scales) does not take -- FP32 D, beta * C, bias, per-row globals, linear or unaligned block scales, small
+// shapes.  (The PAIR template parameter of this file predates that kernel and is no longer instantiated.)
+//
 // NVFP4 x NVFP4 (W4A4) GEMM on the 5th-generation tensor cores: tcgen05.mma kind::mxf4nvf4 with 1 x 16 UE4M3 block scales
 // (scale_vec::4X), FP32 accumulators in tensor memory, operands fed by TMA through a multi-stage mbarrier ring, persistent
 // tile scheduling, epilogue (global scales, bias, beta * C, amax, output rounding) straight out of tensor memory.
