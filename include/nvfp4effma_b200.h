@@ -19,7 +19,9 @@ nvfp4a_status nvfp4a_b200_codec_selftest(unsigned long long first, unsigned long
 /* Kernel route of the GEMM entry points (no counterpart in the reference, which picks kernels from per-architecture
  * tables): 0 = automatic (GEMV for n <= 8, tcgen05 GEMMs where the operand formats have a tensor-core form, CUDA cores
  * otherwise), 1 = always the CUDA-core kernel, whose results are bit-identical to the reference's tiled kernels, 2 = automatic
- * but with the mma.sync GEMV in place of the FP4 tensor-core GEMV (n <= 2).
+ * but with the mma.sync GEMV in place of the FP4 tensor-core GEMV (n <= 2), 3 = automatic but INT8 activations keep the exact
+ * integer block sums of the DP4A kernel instead of the tensor-core W4A8 GEMM (which takes a call's scratch from the stream's
+ * memory pool and agrees with the exact definition within the FP32 accumulation bound).
  * Process-wide, not thread-safe; meant for tests and debugging.  Returns the previous value. */
 int nvfp4a_b200_set_route(int route);
 

@@ -22,7 +22,8 @@ static bool aligned(const void *p, unsigned a) { return ((uintptr_t)p & (a - 1))
 static bool dense_dt(nvfp4a_dtype t) { return t >= NVFP4A_BF16 && t <= NVFP4A_FP32; }
 
 // Route override (nvfp4a_b200_set_route): 0 = automatic, 1 = always the exact CUDA-core kernel, 2 = automatic without the
-// FP4 tensor-core GEMV.  The environment variable NVFP4A_B200_ROUTE=generic sets the initial value to 1.
+// FP4 tensor-core GEMV, 3 = automatic without the tensor-core W4A8 GEMM (INT8 activations then keep the exact integer block sums
+// of the DP4A kernel).  The environment variable NVFP4A_B200_ROUTE=generic sets the initial value to 1.
 static std::atomic<int> g_route{-1};
 static int forced_route() {
   int r = g_route.load();
@@ -91,8 +92,11 @@ static nvfp4a_status check_epilogue_operands(const char *fn, int m, float beta, 
 }
 
 // kernel the last GEMM call of this thread launched (nvfp4a_b200_last_route): 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core
-// GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8 activations
+// GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8 activations,
+// 8 W4A8 on the W4A16 tcgen05 kernel (INT8 activations as three BF16 planes)
 static thread_local int g_last_route = 0;
+// set around the call of an entry that must not allocate (nvfp4a_b200_gemm_ex_static)
+static thread_local int g_no_alloc = 0;
 
 // The workspace of nvfp4a_gemm_tc_ex holds the RMSNorm column scales of up to kWorkspaceTokens tokens while a call runs (a
 // small kernel fills it before the GEMM, a memset restores the zeros after it); the other tensor-core calls leave it alone.
@@ -118,6 +122,7 @@ static nvfp4a_status dispatch(const char *fn, const GemmArgs &g, cudaStream_t st
   else if (gemv && g.k > 0 && gemv_blocked_supports(g)) { g_last_route = 6; err = launch_gemv_blocked(g, stream); }
   else if (!gemv && gemm_w4a4_supports(g)) { g_last_route = 4; err = launch_gemm_w4a4(g, stream); }
   else if (!gemv && gemm_w4a16_supports(g)) { g_last_route = 5; err = launch_gemm_w4a16(g, stream); }
+  else if (!gemv && forced_route() != 3 && gemm_w4a8_tc_supports(g)) { g_last_route = 8; err = launch_gemm_w4a8_tc(g, stream); }
   else if (!gemv && gemm_dp4a_supports(g)) { g_last_route = 7; err = launch_gemm_dp4a(g, stream); }
   else { g_last_route = 1; err = launch_gemm_generic(g, stream); }
   if (err == cudaSuccess && g.tp.world > 1 && g_last_route != 2) {
@@ -190,6 +195,7 @@ static nvfp4a_status gemm_run(const char *fn, int m, int n, int k, float alpha, 
   g.B = make_b(B, ldb, ldsb, k, false);
   g.e = make_epilogue(alpha, A, B, beta, C, ldc, D, ldd, bias);
   g.x = ex;
+  g.no_alloc = g_no_alloc;
   if (args_out) *args_out = g;
   if (validate_only || args_out) return NVFP4A_OK;
   return dispatch(fn, g, stream);
@@ -321,7 +327,10 @@ nvfp4a_status gemm_ex_with_scales(const char *fn, int m, int n, int k, float alp
     if (nvfp4a_status st = cuda_fail(launch_norm_scales(x, n, colscales, stream), fn)) return st;
     x.colscales = colscales;
   }
-  return gemm_run(fn, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, x, stream);
+  g_no_alloc = 1;   // this path serves the entry that allocates nothing: kernels that take scratch from the memory pool step aside
+  const nvfp4a_status st = gemm_run(fn, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, x, stream);
+  g_no_alloc = 0;
+  return st;
 }
 
 }  // namespace nvb
@@ -330,7 +339,7 @@ using namespace nvb;
 
 extern "C" int nvfp4a_b200_set_route(int route) {
   const int old = forced_route();
-  g_route = route == 2 ? 2 : (route ? 1 : 0);
+  g_route = (route == 2 || route == 3) ? route : (route ? 1 : 0);
   return old;
 }
 

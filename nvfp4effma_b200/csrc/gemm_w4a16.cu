@@ -17,7 +17,15 @@
 //               A tile.  To keep scale * 2^126 inside BF16, weights are carried as a * sa * 2^-Z (Z = 8 for E4M3, 16 for
 //               UE5M3 scales) and the accumulator is multiplied by 2^Z in the epilogue.
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag and the kernel status word.
+//
+// INT8 activations (W4A8, FP32 scale per 16 values) run on the same kernel with PLANES = 3: an activation is the FP32 value
+// x = q * s_b (one rounding: within the accumulation bound of the exact definition, not bit-identical to the integer block sums
+// of the DP4A kernels), split exactly into three BF16 terms x = t1 + t2 + t3 (8 + 8 + 8 significant bits) by a small kernel
+// that runs first.  The terms lie side by side as [token][3][k]; a stage then holds one expanded weight tile and the three
+// activation tiles of its 64 values of k, and the MMA issuer accumulates weight x t1, weight x t2, weight x t3 into the same
+// accumulator -- three times the tensor-core work per expanded weight tile, which is what this kernel otherwise lacks.
 #include <atomic>
+#include <cuda_bf16.h>
 #include "operands.cuh"
 #include "sm100.cuh"
 
@@ -43,10 +51,10 @@ struct alignas(64) PeerMaps {
   int n;
 };
 
-template <int BN>
+template <int BN, int PLANES = 1>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr int kABytes = 128 * 128, kBBytes = BN * 128, kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = PLANES == 3 ? 3 : BN == 256 ? 4 : 6;
+  static constexpr int kABytes = 128 * 128, kPlaneBytes = BN * 128, kBBytes = PLANES * kPlaneBytes, kStageBytes = kABytes + kBBytes;
   static constexpr int kStagingBytes = 8192;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + 1024 /* scale table */ + BN * 4 /* column scales */ + 256;
 };
@@ -73,17 +81,29 @@ __device__ __forceinline__ uint32_t decode_pair(uint32_t w) {
   return mag | sgn;
 }
 
+// four MMAs of K = 16 over one 128-byte-row stage without a commit (elected lane of a converged warp): the first and second
+// activation plane of a stage; the third goes through mma4_f16_commit_elect
+__device__ __forceinline__ void mma4_f16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p, q, t;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.eq.u32 t, %3, %3;\n\telect.sync _|q, 0xFFFFFFFF;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %3, t;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %3, t;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %10, %3, t;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_desc + 2), "l"(b_desc + 2), "l"(a_desc + 4), "l"(b_desc + 4),
+                 "l"(a_desc + 6), "l"(b_desc + 6) : "memory");
+}
+
 // what a conversion thread fetches for one stage: the 64 nibbles and 4 scale bytes of its row
 struct RawRow {
   uint4 w0, w1;
   uint32_t sc;
 };
 
-template <int BN>
+template <int BN, int PLANES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ PeerMaps peers,
                   const W4A16Args g) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PLANES>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -141,7 +161,10 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
         const int s = it % kStages;
         if (!__all_sync(0xFFFFFFFFu, wait(&empty[s], ((it / kStages) & 1) ^ 1, kStWaitEmpty))) goto done;
         mbar_arrive_expect_tx_elect(&full[s], C::kBBytes);
-        tma_load_2d_elect(smem_u32(smem + (size_t)s * C::kStageBytes + C::kABytes), &tmap_b, ks * 128, tn * BN, smem_u32(&full[s]));
+#pragma unroll
+        for (int p = 0; p < PLANES; ++p)   // plane p of a token's row starts 2 k bytes after plane p - 1
+          tma_load_2d_elect(smem_u32(smem + (size_t)s * C::kStageBytes + C::kABytes + p * C::kPlaneBytes), &tmap_b, p * 2 * gk + ks * 128, tn * BN,
+                            smem_u32(&full[s]));
       }
     }
   } else if (warp == 1) {
@@ -162,7 +185,13 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
         if (!__all_sync(0xFFFFFFFFu, wait(&full[s], (it / kStages) & 1, kStWaitFullA))) goto done;
         tc_fence_after();
         const uint64_t da = da0 + (uint32_t)s * (uint32_t)(C::kStageBytes >> 4), db = da + (C::kABytes >> 4);
-        mma4_f16_commit_elect(d_tmem, da, db, idesc, (uint32_t)(ks != 0), &empty[s]);
+        if (PLANES == 3) {
+          mma4_f16_elect(d_tmem, da, db, idesc, (uint32_t)(ks != 0));
+          mma4_f16_elect(d_tmem, da, db + (C::kPlaneBytes >> 4), idesc, 1u);
+          mma4_f16_commit_elect(d_tmem, da, db + 2 * (C::kPlaneBytes >> 4), idesc, 1u, &empty[s]);
+        } else {
+          mma4_f16_commit_elect(d_tmem, da, db, idesc, (uint32_t)(ks != 0), &empty[s]);
+        }
       }
       tc_commit_elect(&tmem_full[acc]);
     }
@@ -172,6 +201,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
     const float *const ga = g.e.ga;
     const int ga_stride = g.e.ga_stride;
     const float gf = g.e.gf, alpha = g.e.alpha, beta = g.e.beta;
+    const float gb0 = g.e.gb ? __ldg(g.e.gb) : 1.f;   // B's global: dense B has none, INT8 B one for the tensor (a multiply by 1 is exact)
     const void *const cptr = g.e.c, *const biasptr = g.e.bias;
     const int ldc = g.e.ldc, c_dtype = g.e.c_dtype, bias_dtype = g.e.bias_dtype;
     uint8_t *const dptr = (uint8_t *)g.e.d;
@@ -200,7 +230,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
       const float rowp = row_ok ? __fmul_rn(alpha, ga ? ga[(size_t)i * ga_stride] : 1.f) : 0.f;
       const float bias = (row_ok && biasptr) ? load_dense(bias_dtype, biasptr, i) : 0.f;
       const float w2 = (row_ok && (mask & kExOut2)) ? load_dense(w2_dtype, w2ptr, i) : 0.f;
-      const float s_plain = __fmul_rn(rowp, gf);   // ((alpha gA) * 1) * gf: B is dense, its column part is 1
+      const float s_plain = __fmul_rn(__fmul_rn(rowp, gb0), gf);   // ((alpha gA) * gB) * gf
       if (mask & kExNorm) {  // column scales of this token tile (the previous tile's are no longer in use: see the barrier below)
         named_barrier(1, 128);
         if (colscales) {  // computed before the launch, one float per token
@@ -266,7 +296,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_const
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const float a = __fmul_rn(__uint_as_float(r[jj]), zf);
-          const float s = (mask & kExNorm) ? __fmul_rn(__fmul_rn(rowp, colscale[c * 32 + jj]), gf) : s_plain;
+          const float s = (mask & kExNorm) ? __fmul_rn(__fmul_rn(rowp, __fmul_rn(gb0, colscale[c * 32 + jj])), gf) : s_plain;
           float v = __fmul_rn(a, s);
           if (biasptr) v = __fadd_rn(v, bias);
           if (beta != 0.f && row_ok && jj < nvalid) v = __fmaf_rn(beta, load_dense(c_dtype, cptr, (size_t)(j0 + jj) * ldc + i), v);
@@ -459,21 +489,49 @@ done:
   }
 }
 
-template <int BN>
+template <int BN, int PLANES = 1>
 cudaError_t launch_cfg(const CUtensorMap &tb, const CUtensorMap &td, const PeerMaps &pm, const W4A16Args &a, cudaStream_t s) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PLANES>;
   static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN, PLANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev & 63] = true;
   }
   const int tiles = ((a.m + 127) / 128) * ((a.n + BN - 1) / BN);
   const int grid = tiles < device_sms() ? tiles : device_sms();
-  gemm_w4a16_kernel<BN><<<grid, kThreads, C::kSmemBytes, s>>>(tb, td, pm, a);
+  gemm_w4a16_kernel<BN, PLANES><<<grid, kThreads, C::kSmemBytes, s>>>(tb, td, pm, a);
   return cudaGetLastError();
+}
+
+// INT8 activations q [n][ld] with one FP32 scale per 16 values -> three BF16 planes [n][3][k] with t1 + t2 + t3 = fl(q * s) exactly.
+// One thread per 8 values: 8 bytes in, three 16-byte stores out.
+__global__ void __launch_bounds__(256) w4a8_planes_kernel(const int8_t *__restrict__ q, int ld, const float *__restrict__ sc, int lds, int n, int k,
+                                                          uint16_t *__restrict__ planes) {
+  const long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x, per_row = k >> 3;
+  if (v >= per_row * n) return;
+  const int j = (int)(v / per_row), c = (int)(v - (long long)j * per_row);   // token, group of 8 values
+  const uint2 raw = *(const uint2 *)(q + (size_t)j * ld + 8 * c);
+  const float s = sc[(size_t)j * lds + (c >> 1)];
+  uint32_t t[3][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int qi = (int)(int8_t)(((i < 4 ? raw.x : raw.y) >> (8 * (i & 3))) & 0xFFu);
+    float r = __fmul_rn((float)qi, s);
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      const float tp = __bfloat162float(__float2bfloat16_rn(r));   // 8 significant bits, round to nearest even
+      const uint32_t h = __float_as_uint(tp) >> 16;
+      if (i & 1) t[p][i >> 1] |= h << 16;
+      else t[p][i >> 1] = h;
+      r = __fsub_rn(r, tp);   // exact: the remainder has at most 16, then 8 significant bits
+    }
+  }
+  uint16_t *row = planes + (size_t)j * 3 * k + 8 * c;
+#pragma unroll
+  for (int p = 0; p < 3; ++p) *(uint4 *)(row + (size_t)p * k) = make_uint4(t[p][0], t[p][1], t[p][2], t[p][3]);
 }
 
 }  // namespace
@@ -490,6 +548,46 @@ bool gemm_w4a16_supports(const GemmArgs &g) {
   if (g.B.dtype != NVFP4A_BF16 || g.k < 64 || ((uintptr_t)g.B.data & 15) || g.B.ld % 8) return false;
   if (!g.A.image && (((uintptr_t)g.A.data & 15) || g.A.ld % 32 || ((uintptr_t)g.A.sc & 1))) return false;
   return true;
+}
+
+// W4A8 on the tensor cores (see the header): from 64 tokens and 128 weight rows up, where the planes' set-up pays.  The call
+// allocates the planes from the stream's memory pool (stream-ordered: capturable, no synchronisation) and frees them after the GEMM.
+bool gemm_w4a8_tc_supports(const GemmArgs &g) {
+  if (g.B.dtype != NVFP4A_INT8 || g.k < 64 || g.n < 64 || g.m < 128 || g.no_alloc || g.tp.world > 1 || g.e.gb_stride) return false;
+  if (((uintptr_t)g.B.data & 7) || g.B.ld % 8 || !g.B.s8 || ((uintptr_t)g.B.s8 & 3)) return false;
+  if (!g.A.image && (((uintptr_t)g.A.data & 15) || g.A.ld % 32 || ((uintptr_t)g.A.sc & 1))) return false;
+  return true;
+}
+
+cudaError_t launch_gemm_w4a8_tc(const GemmArgs &g, cudaStream_t s) {
+  W4A16Args a;
+  memset(&a, 0, sizeof a);
+  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.A = g.A;
+  a.e = g.e; a.x = g.x;
+  a.status = kernel_status_device_ptr();
+  a.tag = next_launch_tag();
+  uint16_t *planes = nullptr;
+  cudaError_t e = cudaMallocAsync((void **)&planes, (size_t)g.n * 3 * g.k * sizeof(uint16_t), s);
+  if (e != cudaSuccess) return e;
+  const long long groups = (long long)g.n * (g.k >> 3);
+  w4a8_planes_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, s>>>((const int8_t *)g.B.data, g.B.ld, g.B.s8, g.B.lds8, g.n, g.k, planes);
+  e = cudaGetLastError();
+  CUtensorMap tb, td;
+  memset(&td, 0, sizeof td);
+  if (e == cudaSuccess && !make_tmap_bytes(&tb, planes, (uint64_t)g.k * 6, (uint64_t)g.n, (uint64_t)g.k * 6, 128)) e = cudaErrorInvalidValue;
+  if (e == cudaSuccess) {
+    const int esz = dense_bytes(g.e.d_dtype);
+    const bool glu = (g.x.mask & kExSwiglu) != 0;
+    const int drows = glu ? g.m / 2 : g.m;
+    a.d_tma = ((uintptr_t)g.e.d & 15) == 0 && ((size_t)g.e.ldd * esz) % 16 == 0 && ((size_t)drows * esz) % 16 == 0 &&
+              make_tmap_dense(&td, g.e.d, esz, (uint64_t)drows, (uint64_t)g.n, (uint64_t)g.e.ldd * esz, glu ? 64 : 128, esz == 2 ? 32 : 16);
+    PeerMaps pm;
+    memset(&pm, 0, sizeof pm);
+    e = launch_cfg<128, 3>(tb, td, pm, a, s);
+  }
+  const cudaError_t ef = cudaFreeAsync(planes, s);
+  return e != cudaSuccess ? e : ef;
 }
 
 cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s) {

@@ -59,6 +59,7 @@ struct GemmArgs {
   Epilogue e;
   EpilogueEx x;
   TpPush tp;   // tensor-parallel GEMV: D also goes to the peers, then the ranks' barrier (world <= 1: off)
+  int no_alloc;   // the call must not allocate (nvfp4a_b200_gemm_ex_static): routes that take scratch from the stream's memory pool step aside
 };
 
 // kernels (each returns the launch error)
@@ -78,6 +79,8 @@ bool gemm_dp4a_supports(const GemmArgs &g);
 cudaError_t launch_gemm_w4a16(const GemmArgs &g, cudaStream_t s);    // tcgen05 kind::f16 with weights expanded to BF16 in smem
 bool gemm_w4a16_supports(const GemmArgs &g);
 bool gemm_w4a16_pushes(const GemmArgs &g);
+cudaError_t launch_gemm_w4a8_tc(const GemmArgs &g, cudaStream_t s);  // INT8 activations as three BF16 planes on the same tcgen05 kernel
+bool gemm_w4a8_tc_supports(const GemmArgs &g);
 // s_j of every token (the RMSNorm column scale of the extended epilogue) -> out[0 .. n)
 cudaError_t launch_norm_scales(const EpilogueEx &x, int n, float *out, cudaStream_t s);
 cudaError_t launch_image_build(const Fp4Operand &src, int rows, int k, uint8_t *image, cudaStream_t s);

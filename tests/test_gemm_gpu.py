@@ -473,17 +473,27 @@ def test_gemv_with_block_scaled_activations_uses_the_dp4a_kernel(bt):
 
 
 def test_w4a8_dp4a_gemm_is_bit_exact_in_the_tiled_order():
-    """INT8 activations, n > 8: the DP4A GEMM (route 7) sums blocks in the reference's tiled order, so D and amax equal the
-    oracle's bit for bit; tails in m and n, padded leading dimensions, every output type, bias, beta, alpha."""
-    for i, (m, n, k) in enumerate([(128, 128, 64), (130, 9, 128), (517, 300, 1024), (1000, 129, 576), (64, 2048, 256)]):
-        for fa in (0, SW, AM | PR):
-            c = Case(m, n, k, L.INT8, OUTS[i % 3], OUTS[(i + 1) % 3] if i % 2 else -1, L.BF16 if i % 2 else -1, 1.25, 0.5 if i % 2 else 1.0, fa=fa)
-            h = build_case(c, 1300 + i)
-            exp = oracle_case(c, h)
-            got, amax = run_gemm(c, h)
-            assert L.lib.nvfp4a_b200_last_route() == 7, c
-            assert np.array_equal(got.view(np.uint8), exp["D"].view(np.uint8)), c
-            assert amax == exp["amax"], c
+    """INT8 activations, n > 8, with the tensor-core W4A8 GEMM switched off (nvfp4a_b200_set_route(3)): the DP4A GEMM (route 7)
+    sums blocks in the reference's tiled order, so D and amax equal the oracle's bit for bit; tails in m and n, padded leading
+    dimensions, every output type, bias, beta, alpha.  The default route on the same inputs stays within the bound."""
+    old = L.lib.nvfp4a_b200_set_route(3)
+    try:
+        for i, (m, n, k) in enumerate([(128, 128, 64), (130, 9, 128), (517, 300, 1024), (1000, 129, 576), (64, 2048, 256)]):
+            for fa in (0, SW, AM | PR):
+                c = Case(m, n, k, L.INT8, OUTS[i % 3], OUTS[(i + 1) % 3] if i % 2 else -1, L.BF16 if i % 2 else -1, 1.25, 0.5 if i % 2 else 1.0, fa=fa)
+                h = build_case(c, 1300 + i)
+                exp = oracle_case(c, h, want_ref=True)
+                got, amax = run_gemm(c, h)
+                assert L.lib.nvfp4a_b200_last_route() == 7, c
+                assert np.array_equal(got.view(np.uint8), exp["D"].view(np.uint8)), c
+                assert amax == exp["amax"], c
+                L.lib.nvfp4a_b200_set_route(0)
+                got, amax = run_gemm(c, h)
+                assert L.lib.nvfp4a_b200_last_route() == (8 if m >= 128 and n >= 64 else 7), c
+                check_bound(c, h, got, amax, exp)
+                L.lib.nvfp4a_b200_set_route(3)
+    finally:
+        L.lib.nvfp4a_b200_set_route(old)
 
 
 def test_gemm_dual_forward_dgrad_and_wgrad():
@@ -596,3 +606,26 @@ def test_grouped_gemm_gives_every_group_the_bytes_of_its_own_gemm(bt):
     got = host(dD).view(np.uint16)
     assert np.array_equal(got, want)          # groups bit for bit; padding, the empty group and rows 41 .. 44 untouched
     assert float(host(damax)[0]) == amax
+
+
+def test_w4a8_on_the_tensor_cores_and_the_exact_route_beside_it():
+    """INT8 activations, more than 8 tokens: by default the W4A16 tcgen05 kernel on the activations split into three BF16 planes
+    (route 8; within the FP32 accumulation bound of the exact definition: one rounding of q * s_b per activation); with
+    nvfp4a_b200_set_route(3) the DP4A kernel (route 7), bit-identical to the reference's tiled order.  Tails in m, n and k, padded
+    leading dimensions, bias, beta * C, every output type."""
+    sizes = [(128, 64, 64), (300, 200, 320), (1000, 77, 192), (2048, 512, 1024), (515, 130, 4160)]
+    for i, (m, n, k) in enumerate(sizes):
+        c = Case(m, n, k, L.INT8, OUTS[i % 3], OUTS[i % 3] if i % 2 else -1, L.BF16 if i % 3 == 1 else -1, 1.25 if i % 2 else 1.0, 0.5 if i % 2 else 0.0)
+        h = build_case(c, 4300 + i)
+        exp = oracle_case(c, h, want_ref=True)
+        got, amax = run_gemm(c, h)
+        assert L.lib.nvfp4a_b200_last_route() == 8, c
+        check_bound(c, h, got, amax, exp)
+        old = L.lib.nvfp4a_b200_set_route(3)
+        try:
+            got, amax = run_gemm(c, h)
+            assert L.lib.nvfp4a_b200_last_route() == 7, c
+        finally:
+            L.lib.nvfp4a_b200_set_route(old)
+        assert np.array_equal(got, exp["D"]) and amax == exp["amax"], c
+    assert kernel_status() == 0
