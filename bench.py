@@ -604,15 +604,22 @@ def bench_mlp(args, L, W, dev, rank, world, dist, stream, peaks, traffic):
                                      ctypes.byref(t_bg), ctypes.byref(ex_gu), W.stream_ptr()))
 
     ms_gu8 = time_steps(gate_up_w4a8, 3, 1, stream, dist, world) / 3
+    route8 = L.lib.nvfp4a_b200_last_route()
+    old = L.lib.nvfp4a_b200_set_route(3)   # the same call on the exact DP4A kernel
+    ms_gu8x = time_steps(gate_up_w4a8, 3, 1, stream, dist, world) / 3
+    L.lib.nvfp4a_b200_set_route(old)
     return {"metric": "mlp_w4a16_tflops", "unit": "TFLOP/s", "value": tf(f_gu + f_dn, ms_gu + ms_dn) * world, "tokens": T,
             "gate_up": {"m": 2 * I, "k": H, "epilogue": "RMSNorm column scale + bias + SwiGLU + amax", "ms": ms_gu, "tflops": tf(f_gu, ms_gu)},
             "down": {"m": H, "k": I, "epilogue": "bias + second output * w2 + sums of squares + amax", "ms": ms_dn, "tflops": tf(f_dn, ms_dn)},
-            "gate_up_w4a8": {"entry": "nvfp4a_gemm_ex, INT8 activations", "kernel": "DP4A tiled GEMM (exact block sums, CUDA cores)", "ms": ms_gu8,
-                             "tflops": tf(f_gu, ms_gu8)},
+            "gate_up_w4a8": {"entry": "nvfp4a_gemm_ex, INT8 activations",
+                             "kernel": {8: "W4A16 tcgen05 kernel on three BF16 planes of the activations (within the accumulation bound)",
+                                        7: "DP4A tiled GEMM (exact block sums, CUDA cores)"}.get(route8, str(route8)),
+                             "ms": ms_gu8, "tflops": tf(f_gu, ms_gu8), "includes": "the planes' allocation from the stream's pool and their conversion kernel",
+                             "exact_dp4a": {"ms": ms_gu8x, "tflops": tf(f_gu, ms_gu8x), "how": "nvfp4a_b200_set_route(3): bit-identical to the reference's tiled order"}},
             "roofline": {"bound": "tensor", "achieved": tf(f_gu + f_dn, ms_gu + ms_dn), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": tf(f_gu + f_dn, ms_gu + ms_dn) / peaks["bf16_tflops"], "traffic": traffic.get("mlp_w4a16_dram_bytes"),
                          "traffic_note": "one gate / up launch plus one down launch"},
-            "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1 + 5}
+            "config": {"workload": "llama3_8b_mlp_w4a16_2048_tokens", "entry": "nvfp4a_gemm_tc_ex"}, "_launches": 2 * (steps + 3) * 3 + 1 + 5 + 4 + 4}
 
 
 def bench_tp(args, dev, rank, world, dist, stream, peaks, L):
