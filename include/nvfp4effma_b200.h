@@ -85,7 +85,8 @@ int nvfp4a_b200_set_swap(int mode);
 
 /* The kernel the calling thread's last GEMM / GEMV call launched: 1 CUDA cores, 2 mma.sync GEMV, 3 FP4 tensor-core GEMV, 4 W4A4
  * tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8
- * activations; 0 before any call.  Test aid, no counterpart in the reference. */
+ * activations, 8 W4A8 on the W4A16 tcgen05 kernel (INT8 activations as three BF16 planes); 0 before any call.  Test aid, no
+ * counterpart in the reference. */
 int nvfp4a_b200_last_route(void);
 
 /* Pins the number of k ranges (CTAs per cluster) of the FP4 tensor-core GEMV: 0 = by problem size, else 1, 2, 4 or 8; a
