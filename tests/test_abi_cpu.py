@@ -120,7 +120,11 @@ def test_tensor_parallel_entries_reject_layouts_the_push_cannot_move():
         D = L.Tensor(d_addr, L.BF16, None, 0, None, None, 0, 0)
         return L.lib.nvfp4a_b200_gemm_tc_tp(m, 64, 256, 1.0, A, B, D, ldd, None, None, ws, bufs, flags, world, 0, None)
 
-    for call in (gemv, gemm):
+    def gemv_deferred(d_addr, m, ldd, world=2):
+        D = L.Tensor(d_addr, L.BF16, None, 0, None, None, 0, 0)
+        return L.lib.nvfp4a_b200_gemv_tc_tp_deferred(m, 1, 256, 1.0, A, B, 256, D, ldd, None, None, bufs, flags, world, 0, 1, None)
+
+    for call in (gemv, gemm, gemv_deferred):
         assert call(0x100002, 128, 256) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # base
         assert call(0x100000, 128, 260) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # pitch: 520 bytes
         assert call(0x100000, 132, 256) == L.INVALID_VALUE and b"16 bytes" in L.lib.nvfp4a_last_error()     # shard row: 264 bytes
@@ -129,3 +133,22 @@ def test_tensor_parallel_entries_reject_layouts_the_push_cannot_move():
     D = L.Tensor(0x100000, L.BF16, None, 0, None, None, 0, 0)
     assert L.lib.nvfp4a_b200_gemv_tc_tp(128, 1, 256, 1.0, A, B, 256, D, 256, None, None, bufs, bad_flags, 2, 0, None) == L.INVALID_VALUE
     assert L.lib.nvfp4a_b200_set_wait_limit(10) == -1 and L.lib.nvfp4a_b200_set_wait_limit(2000000000) == 0
+    # the deferred form's other two entries: argument checks before any device is touched
+    assert L.lib.nvfp4a_b200_tp_wait(None, 2, 0, None) == L.INVALID_VALUE
+    assert L.lib.nvfp4a_b200_tp_wait(flags, 9, 0, None) == L.INVALID_VALUE and L.lib.nvfp4a_b200_tp_wait(flags, 2, 2, None) == L.INVALID_VALUE
+    post = L.lib.nvfp4a_b200_tp_gather_post
+    assert post(bufs, flags, 2, 0, 1, 512, 8, 256, None) == L.INVALID_VALUE        # column offset not a multiple of 16
+    assert post(bufs, flags, 2, 0, 1, 512, 384, 256, None) == L.INVALID_VALUE      # the shard leaves the row
+    assert post(None, flags, 2, 0, 1, 512, 0, 256, None) == L.INVALID_VALUE
+
+
+def test_route_and_launch_knobs_take_their_documented_values():
+    """The process-wide knobs of include/nvfp4effma_b200.h (no device needed): routes 0 .. 3, programmatic launch on / off, the
+    one-read quantizer on / off; each setter returns what its header says."""
+    old = L.lib.nvfp4a_b200_set_route(3)
+    assert L.lib.nvfp4a_b200_set_route(2) == 3 and L.lib.nvfp4a_b200_set_route(1) == 2 and L.lib.nvfp4a_b200_set_route(0) == 1
+    L.lib.nvfp4a_b200_set_route(old)
+    assert L.lib.nvfp4a_b200_set_pdl(0) == 0 and L.lib.nvfp4a_b200_set_pdl(1) == 0
+    assert L.lib.nvfp4a_b200_set_pair(2) == -1 and L.lib.nvfp4a_b200_set_pair(-1) == 0
+    assert L.lib.nvfp4a_b200_set_gemv_splits(3) == -1 and L.lib.nvfp4a_b200_set_gemv_splits(0) == 0
+    assert L.lib.nvfp4a_b200_last_launch() >= 0
