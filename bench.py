@@ -516,7 +516,28 @@ def run_ours(args, rank, world, local_rank):
                                           kernel=routes.get(route_image), timing="CUDA graph of 48 calls, median of 7 replays",
                                           plain_operand={"entry": "nvfp4a_gemm (linear scales)", "us_per_call": ms_gp * 1e3,
                                                          "gbs": gbytes / (ms_gp * 1e-3) / 1e9, "kernel": routes.get(route_plain)})
-        del ws, tws, imgs
+        # W4A8 decode beside it: 4096 x 4096 weights, 8 INT8 activation vectors (gemv_blocked_kernel: exact DP4A block sums)
+        m8 = k8 = 4096
+        w8 = [W.quantize_decode_factor(W.randn_bf16(m8, k8, 0.02, 330 + s + 1000 * rank, dev)) for s in range(16)]   # 151 MB > L2
+        x8 = W.randn_bf16(8, k8, 1.0, 401 + rank, dev)
+        xq = torch.empty(8, k8, dtype=torch.int8, device=dev)
+        xsc = torch.empty(8, k8 // 16, dtype=torch.float32, device=dev)
+        src8, dst8 = W.tensor(x8, L.BF16), W.tensor(xq, L.INT8, xsc, 0)
+        L.check(L.lib.nvfp4a_quantize(ctypes.byref(src8), k8, ctypes.byref(dst8), k8, 8, k8, W.stream_ptr()))
+        t_xq, t_w8 = W.tensor(xq, L.INT8, xsc, k8 // 16), [w.tensor() for w in w8]
+        y8 = torch.empty(8 * m8, dtype=torch.bfloat16, device=dev)
+        t_y8 = W.tensor(y8, L.BF16)
+
+        def gemv_int8(i):
+            L.check(L.lib.nvfp4a_gemm(m8, 8, k8, 1.0, ctypes.byref(t_w8[i % 16]), k8, ctypes.byref(t_xq), k8, 0.0, None, 0, ctypes.byref(t_y8), m8, None,
+                                      W.stream_ptr()))
+
+        ms_g8, n3 = time_graph(gemv_int8, 48, 7, 8, dist, world)
+        launches += n3
+        b8 = m8 * k8 // 2 + m8 * k8 // 16
+        extra["gemv_8192_b1"]["w4a8_4096_b8"] = {"entry": "nvfp4a_gemm, INT8 activations, 8 vectors, 4096 x 4096", "kernel": "gemv_blocked_kernel (DP4A, exact block sums)",
+                                                 "us_per_call": ms_g8 * 1e3, "gbs": b8 / (ms_g8 * 1e-3) / 1e9, "frac": b8 / (ms_g8 * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        del ws, tws, imgs, w8, t_w8
     # ---- quantization 8192^2 BF16 -> NVFP4, swizzled scales: 3 inputs = 403 MB > L2 ----
     if only in ("all", "quant"):
         nx = 3

@@ -107,19 +107,27 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQAr
     uint32_t sc[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) load_chunk(rows4[q], c, w[q], sc[q]);
+    // decode the four rows' chunks once, then walk the activation vectors: a vector's 32 values and two scales are read from
+    // shared memory once per chunk and serve all four rows (read per row, shared memory set the pace: 16 bytes of it per weight byte)
+    float sa[4][2];
+    uint32_t a0[4][4], a1[4][4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float sa0 = scale_to_f32(sc[q] & 0xFFu, ue_a), sa1 = scale_to_f32(sc[q] >> 8, ue_a);
-      const uint32_t a0[4] = {dec4(w[q].x), dec4(w[q].x >> 16), dec4(w[q].y), dec4(w[q].y >> 16)};
-      const uint32_t a1[4] = {dec4(w[q].z), dec4(w[q].z >> 16), dec4(w[q].w), dec4(w[q].w >> 16)};
+      sa[q][0] = scale_to_f32(sc[q] & 0xFFu, ue_a); sa[q][1] = scale_to_f32(sc[q] >> 8, ue_a);
+      a0[q][0] = dec4(w[q].x); a0[q][1] = dec4(w[q].x >> 16); a0[q][2] = dec4(w[q].y); a0[q][3] = dec4(w[q].y >> 16);
+      a1[q][0] = dec4(w[q].z); a1[q][1] = dec4(w[q].z >> 16); a1[q][2] = dec4(w[q].w); a1[q][3] = dec4(w[q].w >> 16);
+    }
 #pragma unroll
-      for (int j = 0; j < kMaxN; ++j) {
-        if (j >= gn) break;
-        const uint4 x0 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c), x1 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c + 16);
-        const int p0 = dp4a(a0[3], x0.w, dp4a(a0[2], x0.z, dp4a(a0[1], x0.y, dp4a(a0[0], x0.x, 0))));
-        const int p1 = dp4a(a1[3], x1.w, dp4a(a1[2], x1.z, dp4a(a1[1], x1.y, dp4a(a1[0], x1.x, 0))));
-        acc[q][j] = __fmaf_rn(__fmul_rn((float)p0, sa0), xs[j * nb + 2 * c], acc[q][j]);
-        acc[q][j] = __fmaf_rn(__fmul_rn((float)p1, sa1), xs[j * nb + 2 * c + 1], acc[q][j]);
+    for (int j = 0; j < kMaxN; ++j) {
+      if (j >= gn) break;
+      const uint4 x0 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c), x1 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c + 16);
+      const float xs0 = xs[j * nb + 2 * c], xs1 = xs[j * nb + 2 * c + 1];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int p0 = dp4a(a0[q][3], x0.w, dp4a(a0[q][2], x0.z, dp4a(a0[q][1], x0.y, dp4a(a0[q][0], x0.x, 0))));
+        const int p1 = dp4a(a1[q][3], x1.w, dp4a(a1[q][2], x1.z, dp4a(a1[q][1], x1.y, dp4a(a1[q][0], x1.x, 0))));
+        acc[q][j] = __fmaf_rn(__fmul_rn((float)p0, sa[q][0]), xs0, acc[q][j]);
+        acc[q][j] = __fmaf_rn(__fmul_rn((float)p1, sa[q][1]), xs1, acc[q][j]);
       }
     }
   }
