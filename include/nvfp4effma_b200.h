@@ -89,6 +89,11 @@ int nvfp4a_b200_set_swap(int mode);
  * counterpart in the reference. */
 int nvfp4a_b200_last_route(void);
 
+/* The tensor-core W4A8 GEMM keeps the memory of its activation planes (6 bytes per INT8 activation of the largest call so far) in
+ * a memory pool of its own per device, so that later calls allocate in microseconds and without synchronising.  This call gives
+ * the current device's pool memory that is not in use back to the system (no counterpart in the reference). */
+nvfp4a_status nvfp4a_b200_trim_scratch(void);
+
 /* Pins the number of k ranges (CTAs per cluster) of the FP4 tensor-core GEMV: 0 = by problem size, else 1, 2, 4 or 8; a
  * value the problem cannot use (shared memory for the activation digit planes, k / 256) makes that GEMV step aside for the
  * mma.sync one.  A pinned value also lifts the size threshold below which the automatic choice prefers the mma.sync GEMV.  Tuning / test aid, no counterpart in the reference.  Returns 0, or -1 for another value. */

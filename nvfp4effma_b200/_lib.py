@@ -90,6 +90,7 @@ _PROTOS = {
     "nvfp4a_b200_set_quant_fused": (_i, [_i]),
     "nvfp4a_b200_set_wait_limit": (_i, [C.c_longlong]),
     "nvfp4a_b200_set_pdl": (_i, [_i]),
+    "nvfp4a_b200_trim_scratch": (_i, []),
 }
 EXPORTS = tuple(_PROTOS)
 

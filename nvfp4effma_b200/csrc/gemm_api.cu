@@ -345,6 +345,11 @@ extern "C" int nvfp4a_b200_set_route(int route) {
 
 extern "C" int nvfp4a_b200_last_route(void) { return g_last_route; }
 
+extern "C" nvfp4a_status nvfp4a_b200_trim_scratch(void) {
+  clear_error();
+  return cuda_fail(trim_planes_pool(), "nvfp4a_b200_trim_scratch");
+}
+
 extern "C" int nvfp4a_b200_set_gemv_splits(int splits) {
   if (splits < 0 || splits > 8 || (splits & (splits - 1))) return -1;
   set_gemv_fp4_splits(splits);

@@ -550,8 +550,46 @@ bool gemm_w4a16_supports(const GemmArgs &g) {
   return true;
 }
 
+// The planes' memory comes from a pool of this library's own, one per device, that keeps what it has been given (release threshold
+// at the maximum): a stream-ordered allocation from it costs microseconds and synchronises nothing, whereas the device's default
+// pool hands its memory back at every synchronisation, so that a caller who synchronises once per step would pay a fresh
+// allocation per call.  The pool holds the largest planes buffer in use so far until nvfp4a_b200_trim_scratch or process exit.
+static std::atomic<cudaMemPool_t> g_planes_pool[64];
+static cudaError_t planes_pool(cudaMemPool_t *pool) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  cudaMemPool_t p = g_planes_pool[dev & 63].load();
+  if (!p) {
+    cudaMemPoolProps props;
+    memset(&props, 0, sizeof props);
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    e = cudaMemPoolCreate(&p, &props);
+    if (e != cudaSuccess) return e;
+    unsigned long long keep = ~0ull;
+    cudaMemPoolSetAttribute(p, cudaMemPoolAttrReleaseThreshold, &keep);
+    cudaMemPool_t expected = nullptr;
+    if (!g_planes_pool[dev & 63].compare_exchange_strong(expected, p)) {   // another thread was first: use its pool
+      cudaMemPoolDestroy(p);
+      p = expected;
+    }
+  }
+  *pool = p;
+  return cudaSuccess;
+}
+cudaError_t trim_planes_pool() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  cudaMemPool_t p = g_planes_pool[dev & 63].load();
+  return p ? cudaMemPoolTrimTo(p, 0) : cudaSuccess;
+}
+
 // W4A8 on the tensor cores (see the header): from 64 tokens and 128 weight rows up, where the planes' set-up pays.  The call
-// allocates the planes from the stream's memory pool (stream-ordered: capturable, no synchronisation) and frees them after the GEMM.
+// takes the planes from the pool above (stream-ordered: capturable, no synchronisation) and gives them back after the GEMM.
 bool gemm_w4a8_tc_supports(const GemmArgs &g) {
   if (g.B.dtype != NVFP4A_INT8 || g.k < 64 || g.n < 64 || g.m < 128 || g.no_alloc || g.tp.world > 1 || g.e.gb_stride) return false;
   if (((uintptr_t)g.B.data & 7) || g.B.ld % 8 || !g.B.s8 || ((uintptr_t)g.B.s8 & 3)) return false;
@@ -568,7 +606,10 @@ cudaError_t launch_gemm_w4a8_tc(const GemmArgs &g, cudaStream_t s) {
   a.status = kernel_status_device_ptr();
   a.tag = next_launch_tag();
   uint16_t *planes = nullptr;
-  cudaError_t e = cudaMallocAsync((void **)&planes, (size_t)g.n * 3 * g.k * sizeof(uint16_t), s);
+  cudaMemPool_t pool;
+  cudaError_t e = planes_pool(&pool);
+  if (e != cudaSuccess) return e;
+  e = cudaMallocFromPoolAsync((void **)&planes, (size_t)g.n * 3 * g.k * sizeof(uint16_t), pool, s);
   if (e != cudaSuccess) return e;
   const long long groups = (long long)g.n * (g.k >> 3);
   w4a8_planes_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, s>>>((const int8_t *)g.B.data, g.B.ld, g.B.s8, g.B.lds8, g.n, g.k, planes);

@@ -81,6 +81,7 @@ bool gemm_w4a16_supports(const GemmArgs &g);
 bool gemm_w4a16_pushes(const GemmArgs &g);
 cudaError_t launch_gemm_w4a8_tc(const GemmArgs &g, cudaStream_t s);  // INT8 activations as three BF16 planes on the same tcgen05 kernel
 bool gemm_w4a8_tc_supports(const GemmArgs &g);
+cudaError_t trim_planes_pool();   // gives the W4A8 planes' pool memory of the current device back to the system
 // s_j of every token (the RMSNorm column scale of the extended epilogue) -> out[0 .. n)
 cudaError_t launch_norm_scales(const EpilogueEx &x, int n, float *out, cudaStream_t s);
 cudaError_t launch_image_build(const Fp4Operand &src, int rows, int k, uint8_t *image, cudaStream_t s);

@@ -629,3 +629,31 @@ def test_w4a8_on_the_tensor_cores_and_the_exact_route_beside_it():
             L.lib.nvfp4a_b200_set_route(old)
         assert np.array_equal(got, exp["D"]) and amax == exp["amax"], c
     assert kernel_status() == 0
+    # the planes' pool: trimmed, refilled by the next call; and the whole call (allocation, conversion, GEMM, free) inside a CUDA graph
+    assert L.lib.nvfp4a_b200_trim_scratch() == 0
+    c = Case(300, 200, 320, L.INT8, L.BF16, -1, -1, 1.0, 0.0)
+    h = build_case(c, 4390)
+    want, _ = run_gemm(c, h)
+    assert L.lib.nvfp4a_b200_last_route() == 8
+    dA = DevFp4(h["A"])
+    keepB, tB = device_b(c, h)
+    dD = dev(h["Dinit"])
+    tA, tD = dA.tensor(), tensor(dD, c.dt)
+
+    def call():
+        st = L.lib.nvfp4a_gemm(c.m, c.n, c.k, c.alpha, ctypes.byref(tA), h["lda"], ctypes.byref(tB), h["ldb"], 0.0, None, 0, ctypes.byref(tD), h["ldd"],
+                               None, stream())
+        assert st == 0, L.lib.nvfp4a_last_error()
+
+    call()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    fresh = dev(h["Dinit"])
+    for _ in range(3):
+        dD.copy_(fresh)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(host(dD).view(np.uint16), want.view(np.uint16))
+    assert kernel_status() == 0
