@@ -5,7 +5,7 @@
 // (src/gemv_nvfp4effma.cuh:26-234 there); the order of the FP32 additions over k is this kernel's own, so results agree
 // with the exact definition within the FP32 accumulation bound.
 //
-// One CTA owns 32 consecutive rows; the activations (int8, n x k bytes) and their block scales (FP32) are staged once per
+// One CTA owns 32 (or, for matrices of few rows, 16) consecutive rows; the activations (int8, n x k bytes) and their block scales (FP32) are staged once per
 // CTA in shared memory.  A warp takes a row at a time: lane l reads the 16-byte weight chunks l, l + 32, ... of the row
 // (two blocks each), so a warp load covers 512 contiguous bytes; the n <= 8 dot products of a chunk reuse its decoded
 // weights.  The lanes' sums are added by an xor butterfly; the CTA's 32 x n results then run the plain or extended epilogue.
@@ -16,7 +16,7 @@ namespace nvb {
 
 namespace {
 
-constexpr int kRows = 32, kWarps = 8, kMaxN = 8;
+constexpr int kWarps = 8, kMaxN = 8;   // a CTA owns kWarps * R rows: R = 4 rows per warp, or 2 when the matrix has few rows
 constexpr int kSmemLimit = 200 * 1024;
 
 struct GemvQArgs {
@@ -44,9 +44,11 @@ __device__ __forceinline__ uint32_t dec4(uint32_t h) {
 }
 __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 
+template <int R>
 __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQArgs g) {
+  constexpr int kRows = kWarps * R;
   extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ float vtile[kMaxN][kRows];
+  __shared__ float vtile[kMaxN][32];
   __shared__ float colscale[kMaxN];
   const int gm = g.m, gn = g.n, gk = g.k, nb = gk >> 4;
   int8_t *xq = (int8_t *)smem;                       // [n][k]
@@ -94,25 +96,25 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQAr
       sc = __ldg((const uint16_t *)(asc + sp.at(row, 2 * c)));
     }
   };
-  float acc[4][kMaxN];
+  float acc[R][kMaxN];
 #pragma unroll
-  for (int q = 0; q < 4; ++q)
+  for (int q = 0; q < R; ++q)
 #pragma unroll
     for (int j = 0; j < kMaxN; ++j) acc[q][j] = 0.f;
-  int rows4[4];
+  int rows4[R];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) rows4[q] = min(i0 + warp + kWarps * q, gm - 1);
+  for (int q = 0; q < R; ++q) rows4[q] = min(i0 + warp + kWarps * q, gm - 1);
   for (int c = lane; c < nchunks; c += 32) {
-    uint4 w[4];
-    uint32_t sc[4];
+    uint4 w[R];
+    uint32_t sc[R];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) load_chunk(rows4[q], c, w[q], sc[q]);
+    for (int q = 0; q < R; ++q) load_chunk(rows4[q], c, w[q], sc[q]);
     // decode the four rows' chunks once, then walk the activation vectors: a vector's 32 values and two scales are read from
     // shared memory once per chunk and serve all four rows (read per row, shared memory set the pace: 16 bytes of it per weight byte)
-    float sa[4][2];
-    uint32_t a0[4][4], a1[4][4];
+    float sa[R][2];
+    uint32_t a0[R][4], a1[R][4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < R; ++q) {
       sa[q][0] = scale_to_f32(sc[q] & 0xFFu, ue_a); sa[q][1] = scale_to_f32(sc[q] >> 8, ue_a);
       a0[q][0] = dec4(w[q].x); a0[q][1] = dec4(w[q].x >> 16); a0[q][2] = dec4(w[q].y); a0[q][3] = dec4(w[q].y >> 16);
       a1[q][0] = dec4(w[q].z); a1[q][1] = dec4(w[q].z >> 16); a1[q][2] = dec4(w[q].w); a1[q][3] = dec4(w[q].w >> 16);
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQAr
       const uint4 x0 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c), x1 = *(const uint4 *)(xq + (size_t)j * gk + 32 * c + 16);
       const float xs0 = xs[j * nb + 2 * c], xs1 = xs[j * nb + 2 * c + 1];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < R; ++q) {
         const int p0 = dp4a(a0[q][3], x0.w, dp4a(a0[q][2], x0.z, dp4a(a0[q][1], x0.y, dp4a(a0[q][0], x0.x, 0))));
         const int p1 = dp4a(a1[q][3], x1.w, dp4a(a1[q][2], x1.z, dp4a(a1[q][1], x1.y, dp4a(a1[q][0], x1.x, 0))));
         acc[q][j] = __fmaf_rn(__fmul_rn((float)p0, sa[q][0]), xs0, acc[q][j]);
@@ -132,7 +134,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQAr
     }
   }
 #pragma unroll
-  for (int q = 0; q < 4; ++q)
+  for (int q = 0; q < R; ++q)
 #pragma unroll
     for (int j = 0; j < kMaxN; ++j) {
       float a = acc[q][j];
@@ -145,7 +147,7 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_blocked_kernel(const GemvQAr
   // ---- epilogue: thread t owns (row t % 32, column t / 32) ----
   const Epilogue &e = g.e;
   const int ri = tid & 31, cj = tid >> 5, i = i0 + ri;
-  const bool live = i < gm && cj < gn;
+  const bool live = ri < kRows && i < gm && cj < gn;
   float v = 0.f, amax = 0.f;
   if (live) {
     float colp = epi_col_part(e, cj);
@@ -200,11 +202,16 @@ cudaError_t launch_gemv_blocked(const GemmArgs &g, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemv_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    cudaError_t e = cudaFuncSetAttribute(gemv_blocked_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_blocked_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     attr_set[dev & 63] = true;
   }
-  gemv_blocked_kernel<<<(g.m + kRows - 1) / kRows, kWarps * 32, smem_bytes(g), s>>>(a);
+  // 32 rows per CTA give every SM a CTA from about 4700 rows up; below that, 16 rows per CTA put twice as many warps on the
+  // SMs (4096 x 4096, 8 vectors: 17.2 -> 14.1 us; at 8192 rows the doubled staging of the activations costs more than it brings).
+  // A row's sum does not depend on the choice: a warp walks its rows' chunks in the same order either way.
+  if ((g.m + 31) / 32 >= device_sms()) gemv_blocked_kernel<4><<<(g.m + 31) / 32, kWarps * 32, smem_bytes(g), s>>>(a);
+  else gemv_blocked_kernel<2><<<(g.m + 15) / 16, kWarps * 32, smem_bytes(g), s>>>(a);
   return cudaGetLastError();
 }
 
