@@ -95,6 +95,8 @@ static nvfp4a_status check_epilogue_operands(const char *fn, int m, float beta, 
 // GEMV, 4 W4A4 tcgen05 GEMM, 5 W4A16 tcgen05 GEMM, 6 DP4A GEMV for INT8 / NVFP4 activations, 7 DP4A GEMM for INT8 activations,
 // 8 W4A8 on the W4A16 tcgen05 kernel (INT8 activations as three BF16 planes)
 static thread_local int g_last_route = 0;
+// (defined in gemm_dp4a.cu) the DP4A GEMM over groups of tokens: nvfp4a_gemm_grouped with INT8 activations
+cudaError_t launch_gemm_dp4a_grouped(const GemmArgs &g, const int *seg, int groups, cudaStream_t s);
 // set around the call of an entry that must not allocate (nvfp4a_b200_gemm_ex_static)
 static thread_local int g_no_alloc = 0;
 
@@ -400,7 +402,12 @@ extern "C" nvfp4a_status nvfp4a_gemm_grouped(int groups, int m, int k, int rows,
   // the checks of nvfp4a_gemm with A taken as [groups * m][k]; an empty problem returns before anything is filled in
   if (nvfp4a_status st = gemm_run(fn, m, rows, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, none, stream, false, groups, &g)) return st;
   if (m == 0 || rows == 0) return NVFP4A_OK;
-  // Every group runs the CUDA-core kernel in the reference's tiled order: the bytes of nvfp4a_gemm's tiled kernel for that group.
+  // Every group runs a CUDA-core kernel in the reference's tiled order: the bytes of nvfp4a_gemm's tiled kernel for that group.
+  // INT8 activations take the 128 x 128 DP4A kernel, everything else the generic one.
+  if (forced_route() != 1 && gemm_dp4a_supports(g)) {
+    g_last_route = 7;
+    return cuda_fail(launch_gemm_dp4a_grouped(g, seg, groups, stream), "nvfp4a_gemm_grouped: kernel launch");
+  }
   g_last_route = 1;
   return cuda_fail(launch_gemm_grouped(g, seg, groups, stream), "nvfp4a_gemm_grouped: kernel launch");
 }

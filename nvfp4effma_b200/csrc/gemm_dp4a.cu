@@ -35,7 +35,10 @@ __device__ __forceinline__ uint32_t dec4(uint32_t h) {
   return (pos & ~mask) | (neg & mask);
 }
 
-__global__ void __launch_bounds__(256) gemm_dp4a_kernel(const GemmArgs g) {
+// GROUPED (nvfp4a_gemm_grouped with INT8 activations): A stacks `groups` weights of g.m rows, group q owns the tokens
+// [seg[q], seg[q + 1]); blockIdx.y counts token tiles over the groups in order, each group's last tile partial.
+template <bool GROUPED>
+__global__ void __launch_bounds__(256) gemm_dp4a_kernel(GemmArgs g, const int *__restrict__ seg, int groups) {
   extern __shared__ __align__(16) uint8_t dyn[];
   __shared__ __align__(16) uint32_t a_s[TM][TK / 4 + 1];   // int8 x 4 per word, one padding word per row
   __shared__ __align__(16) uint32_t b_s[TN][TK / 4 + 1];
@@ -44,8 +47,22 @@ __global__ void __launch_bounds__(256) gemm_dp4a_kernel(const GemmArgs g) {
   float *vt = (float *)dyn;                                   // [TN][TM + 1]
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;  // outputs: rows 8 ty .., tokens 8 tx ..
+  int j0 = blockIdx.y * TN, ro = 0;   // ro: first row of this group's weight in the stacked A (and in its per-row globals, bias)
+  if (GROUPED) {
+    int t = blockIdx.y, q = 0, lo = 0, hi = 0;
+    for (; q < groups; ++q) {
+      lo = seg[q]; hi = seg[q + 1];
+      const int tiles = (hi - lo + TN - 1) / TN;
+      if (t < tiles) break;
+      t -= tiles;
+    }
+    if (q == groups || hi > g.n) return;   // past the last group's tiles (the grid is sized for the worst case), or seg beyond `rows`
+    j0 = lo + t * TN;
+    g.n = hi;
+    ro = q * g.m;
+  }
   const int gm = g.m, gn = g.n, gk = g.k;
-  const int i0 = blockIdx.x * TM, j0 = blockIdx.y * TN;
+  const int i0 = blockIdx.x * TM;
   const bool ue_a = g.A.ue != 0;
   const int8_t *const bdata = (const int8_t *)g.B.data;
   const int ldb = g.B.ld, lds8 = g.B.lds8;
@@ -61,7 +78,7 @@ __global__ void __launch_bounds__(256) gemm_dp4a_kernel(const GemmArgs g) {
 
   // staging assignment: thread t stages 32 values (two blocks) of A row t / 2 and of B token t / 2, half t % 2 of the k step
   const int sr = tid >> 1, sh = tid & 1;
-  const int arow = min(i0 + sr, gm - 1), bcol = min(j0 + sr, gn - 1);
+  const int arow = ro + min(i0 + sr, gm - 1), bcol = min(j0 + sr, gn - 1);
   uint4 aw, bw0, bw1;
   float asc0, asc1, bsc0, bsc1;
   auto fetch = [&](int k0) {
@@ -139,7 +156,7 @@ __global__ void __launch_bounds__(256) gemm_dp4a_kernel(const GemmArgs g) {
   const int ri = tid & 127, i = i0 + ri;
   const bool row_ok = i < gm;
   const int mask = g.x.mask;
-  const float rowp = row_ok ? epi_row_part(e, i) : 0.f;
+  const float rowp = row_ok ? epi_row_part(e, ro + i) : 0.f;
   float amax = 0.f;
   // pass 1: v = epilogue value (before the output rounding), written back for the neighbours' use
   for (int c = tid >> 7; c < TN; c += 2) {
@@ -148,7 +165,13 @@ __global__ void __launch_bounds__(256) gemm_dp4a_kernel(const GemmArgs g) {
     if (row_ok && j < gn) {
       float colp = epi_col_part(e, j);
       if (mask & kExNorm) colp = __fmul_rn(colp, colscale[c]);
-      v = epi_value(e, i, j, vt[c * (TM + 1) + ri], epi_scale(e, rowp, colp));
+      if (GROUPED) {   // bias is stacked like A, C like D
+        v = __fmul_rn(vt[c * (TM + 1) + ri], epi_scale(e, rowp, colp));
+        if (e.bias) v = __fadd_rn(v, load_dense(e.bias_dtype, e.bias, ro + i));
+        if (e.beta != 0.f) v = __fmaf_rn(e.beta, load_dense(e.c_dtype, e.c, (size_t)j * e.ldc + i), v);
+      } else {
+        v = epi_value(e, i, j, vt[c * (TM + 1) + ri], epi_scale(e, rowp, colp));
+      }
     }
     vt[c * (TM + 1) + ri] = v;
   }
@@ -186,17 +209,34 @@ bool gemm_dp4a_supports(const GemmArgs &g) {
   return g.B.dtype == NVFP4A_INT8 && g.k >= 64 && ((uintptr_t)g.B.data & 15) == 0 && g.B.ld % 16 == 0;
 }
 
-cudaError_t launch_gemm_dp4a(const GemmArgs &g, cudaStream_t s) {
+static cudaError_t dp4a_prepare() {
   static std::atomic<bool> attr_set[64];   // zero-initialised; set once per device (a repeated cudaFuncSetAttribute is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_dp4a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_dp4a_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_dp4a_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev & 63] = true;
   }
+  return cudaSuccess;
+}
+
+cudaError_t launch_gemm_dp4a(const GemmArgs &g, cudaStream_t s) {
+  const cudaError_t e = dp4a_prepare();
+  if (e != cudaSuccess) return e;
   const dim3 grid((g.m + TM - 1) / TM, (g.n + TN - 1) / TN);
-  gemm_dp4a_kernel<<<grid, 256, kSmemBytes, s>>>(g);
+  gemm_dp4a_kernel<false><<<grid, 256, kSmemBytes, s>>>(g, nullptr, 0);
+  return cudaGetLastError();
+}
+
+// g.m = rows of ONE group's weight, g.n = the bound `rows` on seg[groups]; every group may end in a partial tile
+cudaError_t launch_gemm_dp4a_grouped(const GemmArgs &g, const int *seg, int groups, cudaStream_t s) {
+  const cudaError_t e = dp4a_prepare();
+  if (e != cudaSuccess) return e;
+  const dim3 grid((g.m + TM - 1) / TM, (g.n + TN - 1) / TN + groups);
+  if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+  gemm_dp4a_kernel<true><<<grid, 256, kSmemBytes, s>>>(g, seg, groups);
   return cudaGetLastError();
 }
 

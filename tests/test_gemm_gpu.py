@@ -550,10 +550,13 @@ def test_grouped_gemm_gives_every_group_the_bytes_of_its_own_gemm(bt):
     """nvfp4a_gemm_grouped (reference include/nvfp4effma.h:104-116): three experts of 40 weight rows stacked in A, the row counts
     of B per expert in a device array (one expert empty, rows past seg[groups] left alone); every group's rows of D are the
     bytes the oracle's tiled order gives for that group's own GEMM -- bias, beta * C and per-row globals of the stacked A included."""
+    for groups, m, k, rows, seg in ((3, 40, 192, 45, [0, 19, 19, 41]), (3, 200, 256, 300, [0, 130, 130, 290])):
+        _grouped_case(bt, groups, m, k, rows, np.array(seg, np.int32))
+
+
+def _grouped_case(bt, groups, m, k, rows, seg):
     from util import rand_fp4, rand_q8
-    rng = np.random.default_rng(4100 + bt)
-    groups, m, k, rows = 3, 40, 192, 45
-    seg = np.array([0, 19, 19, 41], np.int32)
+    rng = np.random.default_rng(4100 + bt + m)
     lda, ldb, ldd = k + 64, k + 64, m + 8
     A = rand_fp4(rng, groups * m, k, ld=lda, ld_scale=k // 16 + 4, flags=O.PER_ROW, glob=0.375)
     if bt == L.NVFP4:
@@ -602,9 +605,10 @@ def test_grouped_gemm_gives_every_group_the_bytes_of_its_own_gemm(bt):
     st = L.lib.nvfp4a_gemm_grouped(groups, m, k, rows, alpha, ctypes.byref(tA), lda, ctypes.byref(tB), ldb, beta, ctypes.byref(tD), ldd,
                                    ctypes.byref(tD), ldd, ctypes.byref(tbias), ctypes.c_void_p(dseg.data_ptr()), stream())
     assert st == 0, L.lib.nvfp4a_last_error()
+    assert L.lib.nvfp4a_b200_last_route() == (7 if bt == L.INT8 else 1)   # INT8: the 128 x 128 DP4A kernel, else the generic one
     torch.cuda.synchronize()
     got = host(dD).view(np.uint16)
-    assert np.array_equal(got, want)          # groups bit for bit; padding, the empty group and rows 41 .. 44 untouched
+    assert np.array_equal(got, want)          # groups bit for bit; padding, the empty group and the rows past seg[groups] untouched
     assert float(host(damax)[0]) == amax
 
 
