@@ -661,3 +661,40 @@ def test_w4a8_on_the_tensor_cores_and_the_exact_route_beside_it():
         torch.cuda.synchronize()
         assert np.array_equal(host(dD).view(np.uint16), want.view(np.uint16))
     assert kernel_status() == 0
+
+
+def test_gemv_long_reductions_in_sections():
+    """The mma.sync GEMV cuts k >= 8192 into 2 and k >= 12288 into 4 sections; a matrix of few rows gives each section to a
+    CTA of a cluster (partial sums through distributed shared memory), a taller one walks them in one CTA.  Both against the
+    float64 reference within the bound, images and plain operands, 1 to 8 activation vectors, tails in m; and the two forms
+    agree bit for bit on the rows they share (a row's sum depends on k alone)."""
+    old = L.lib.nvfp4a_b200_set_route(2)   # keep the FP4 tensor-core GEMV out of it
+    try:
+        for i, (m, n, k) in enumerate([(300, 1, 8192), (130, 5, 14336), (1300, 3, 14336), (77, 8, 12288), (2500, 2, 8192)]):
+            c = Case(m, n, k, L.BF16, OUTS[i % 3], -1, L.BF16 if i % 2 else -1, 1.25 if i % 2 else 1.0, 0.0, fa=SW if i % 2 else 0)
+            h = build_case(c, 4700 + i)
+            exp = oracle_case(c, h, want_ref=True)
+            got, amax = run_gemm(c, h)
+            assert L.lib.nvfp4a_b200_last_route() == 2, c
+            check_bound(c, h, got, amax, exp)
+            got_tc, amax_tc = run_tc(c, h, gemv=True)
+            assert L.lib.nvfp4a_b200_last_route() == 2, c
+            check_bound(c, h, got_tc, amax_tc, exp)
+        # the same rows as part of a short matrix (cluster per slice) and of a tall one (one CTA per slice): identical bytes
+        k = 14336
+        tall = Case(1600, 2, k, L.BF16, L.FP32, -1, -1, 1.0, 0.0)
+        h = build_case(tall, 4750)
+        got_tall, _ = run_gemm(tall, h)
+        short = Case(160, 2, k, L.BF16, L.FP32, -1, -1, 1.0, 0.0)
+        hs = dict(h)
+        A = h["A"]
+        As = O.Fp4(160, k, ld=A.ld, ld_scale=A.ld_scale, flags=A.flags, scale_max=A.scale_max, glob=0.0)
+        As.data[:], As.scales[:], As.glob[:] = A.data[:160 * A.ld // 2], A.scales[:160 * A.ld_scale], A.glob
+        hs["A"] = As
+        got_short, _ = run_gemm(short, hs)
+        a = values(got_tall, tall, h)[:, :160]
+        b = values(got_short, short, hs)
+        assert np.array_equal(a, b)
+    finally:
+        L.lib.nvfp4a_b200_set_route(old)
+    assert kernel_status() == 0
