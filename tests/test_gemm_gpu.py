@@ -698,3 +698,27 @@ def test_gemv_long_reductions_in_sections():
     finally:
         L.lib.nvfp4a_b200_set_route(old)
     assert kernel_status() == 0
+
+
+def test_blocked_gemv_with_sixteen_and_thirty_two_rows_per_cta():
+    """The DP4A GEMV for INT8 / NVFP4 activations gives a CTA 16 rows while the matrix would leave SMs without a CTA and 32 rows
+    from about 4700 rows up: both against the float64 reference within the bound, and bit for bit against each other on shared rows."""
+    for bt in (L.INT8, L.NVFP4):
+        outs = {}
+        for m in (4800, 160):
+            c = Case(m, 3, 320, bt, L.FP32, -1, -1, 1.0, 0.0)
+            h = build_case(c, 4800 + bt)          # the same seed: the short matrix is not a prefix of the tall one, so each is checked alone
+            exp = oracle_case(c, h, want_ref=True)
+            got, amax = run_gemm(c, h)
+            assert L.lib.nvfp4a_b200_last_route() == 6, c
+            check_bound(c, h, got, amax, exp)
+            outs[m] = (c, h, got)
+        # shared rows: the first 160 rows of the tall matrix as a matrix of their own (16 rows per CTA)
+        c, h, got_tall = outs[4800]
+        A = h["A"]
+        As = O.Fp4(160, c.k, ld=A.ld, ld_scale=A.ld_scale, flags=A.flags, scale_max=A.scale_max, glob=0.0)
+        As.data[:], As.scales[:], As.glob[:] = A.data[:160 * A.ld // 2], A.scales[:160 * A.ld_scale], A.glob
+        cs = Case(160, 3, 320, bt, L.FP32, -1, -1, 1.0, 0.0)
+        hs = dict(h, A=As)
+        got_short, _ = run_gemm(cs, hs)
+        assert np.array_equal(values(got_tall, c, h)[:, :160], values(got_short, cs, hs))
